@@ -1,0 +1,167 @@
+/*
+ * dcn_b200 -- C ABI of the B200 (sm_100a) forward of deformable convolution
+ * v1 / v2 (modulated).  Plain pointers and sizes only; no tensor-library types.
+ *
+ * All functions return 0 on success and a negative DCN_ERR_* code otherwise;
+ * dcn_last_error() then holds a message for the calling thread.  Nothing here
+ * allocates device memory except where a function says so: scratch memory is
+ * sized by dcn_fwd_workspace_bytes() and handed in by the caller.  All work is
+ * enqueued on the caller's stream and nothing synchronises unless stated.
+ * There is no CPU path: every entry fails if the device cannot run sm_100a code.
+ */
+#ifndef DCN_B200_H_
+#define DCN_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DCN_ABI_VERSION 1
+
+enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1 };
+
+/* Arithmetic of the contraction.  AUTO picks BF16 for bf16 tensors and FFMA for
+ * fp32 tensors.  BF16 = tcgen05 kind::f16 tensor-core MMA with fp32 accumulation
+ * in tensor memory; FFMA = fp32 fused multiply-add on the SIMT cores. */
+enum { DCN_MATH_AUTO = 0, DCN_MATH_FFMA = 1, DCN_MATH_TF32X3 = 2, DCN_MATH_BF16 = 3 };
+
+enum {
+  DCN_OK = 0,
+  DCN_ERR_ARG = -1,        /* shape / pointer / enum rejected (message says which) */
+  DCN_ERR_UNSUPPORTED = -2,/* valid in the reference, not built here (message says what) */
+  DCN_ERR_WORKSPACE = -3,  /* workspace missing, too small or misaligned */
+  DCN_ERR_CUDA = -4,       /* a CUDA runtime call failed (message carries its text) */
+  DCN_ERR_DEVICE = -5      /* no device, or the device is not compute capability 10.x */
+};
+
+/* Kernel families a call can be routed to (reported by dcn_fwd_plan). */
+enum { DCN_PATH_TCGEN05 = 1, DCN_PATH_SIMT_TILED = 2, DCN_PATH_SIMT_DIRECT = 3 };
+
+/* Epilogue applied to output channels [act_lo, act_hi) after bias. */
+enum { DCN_ACT_NONE = 0, DCN_ACT_SIGMOID = 1 };
+
+/*
+ * One forward problem.  Tensor layouts are the reference's:
+ *   input  [N, C, H, W]            element strides in_stride[4] (NCHW-contiguous or
+ *                                  channels-last; anything else is rejected)
+ *   offset [N, dg*2*kh*kw, Ho, Wo] (y, x) interleaved per tap, contiguous per sample,
+ *                                  sample stride offset_batch_stride elements (0 = dense).
+ *                                  NULL = all-zero offsets (an ordinary convolution).
+ *   mask   [N, dg*kh*kw, Ho, Wo]   same rules; NULL = 1 everywhere (the v1 operator).
+ *   weight [Co, C/groups, kh, kw]  contiguous
+ *   bias   [Co] or NULL
+ *   output [N, Co, Ho, Wo]         contiguous per sample, sample stride out_batch_stride
+ *                                  elements (0 = dense)
+ * with Ho = (H + 2*pad_h - (dil_h*(kh-1)+1)) / stride_h + 1 (same for Wo), as in
+ * mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:87-90.  All tensors share `dtype`.
+ */
+typedef struct DcnFwdParams {
+  const void *input;
+  const void *offset;
+  const void *mask;
+  const void *weight;
+  const void *bias;
+  void *output;
+  int32_t dtype;      /* DCN_DTYPE_* */
+  int32_t math_mode;  /* DCN_MATH_*  */
+  int64_t N, C, H, W, Co;
+  int32_t kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int32_t groups, deform_groups;
+  int64_t in_stride[4];
+  int64_t offset_batch_stride, mask_batch_stride, out_batch_stride;
+  int32_t act, act_lo, act_hi; /* DCN_ACT_* on output channels [act_lo, act_hi) */
+  int32_t device;              /* CUDA device ordinal the pointers live on */
+} DcnFwdParams;
+
+/* What a call will do; filled by dcn_fwd_plan without touching the device. */
+typedef struct DcnPlanInfo {
+  int32_t path;           /* DCN_PATH_* */
+  int32_t launches;       /* kernels dcn_fwd enqueues for this problem */
+  int32_t stages_input;   /* 1 if the input is first restaged to channels-last bf16 */
+  int32_t tile_m, tile_n, tile_k;
+  int32_t grid, block;    /* of the main kernel */
+  int64_t smem_bytes;     /* dynamic shared memory of the main kernel */
+  int64_t Ho, Wo;
+  size_t workspace_bytes;
+} DcnPlanInfo;
+
+int dcn_abi_version(void);
+const char *dcn_last_error(void);
+
+int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info);
+int dcn_fwd_workspace_bytes(const DcnFwdParams *p, size_t *bytes);
+
+/*
+ * Enqueue the forward on `stream` (a cudaStream_t).  `workspace` is device
+ * memory of at least dcn_fwd_workspace_bytes() bytes, 256-byte aligned; its
+ * contents are scratch, except that its first 4 bytes receive a status word
+ * (0 = ok) that dcn_read_status() returns.
+ *
+ * Replaces the body of modulated_deform_conv_forward
+ * (mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:62-138, :395-412) and of
+ * deform_conv_forward (mmcv/ops/csrc/pytorch/deform_conv.cpp:140-260) together
+ * with the gather kernels they launch
+ * (mmcv/ops/csrc/common/cuda/modulated_deform_conv_cuda_kernel.cuh:186-245,
+ *  mmcv/ops/csrc/common/cuda/deform_conv_cuda_kernel.cuh:190-241).
+ */
+int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
+            void *stream);
+
+/* Synchronises `stream`, then returns the status word the last dcn_fwd on this
+ * workspace left: 0 ok; non-zero = a bounded device-side wait gave up
+ * (the kernel returned early, the output is not valid). */
+int dcn_read_status(const void *workspace, void *stream, int32_t *status);
+
+/*
+ * The two reference entry points with flat arguments, in the reference's own
+ * argument order and meaning.  `elem` is DCN_DTYPE_*; sizes are in elements.
+ *
+ * dcn_modulated_deform_conv_forward is what a binding of
+ *   modulated_deform_conv_forward(input, weight, bias, ones, offset, mask, output,
+ *     columns, kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w, dilation_h,
+ *     dilation_w, group, deformable_group, with_bias)
+ * (mmcv/ops/csrc/pytorch/pybind.cpp:157-162, :641-648) calls; the reference's
+ * scratch handles `ones` and `columns` have no counterpart because no column
+ * buffer exists.
+ */
+int dcn_modulated_deform_conv_forward(
+    const void *input, const void *weight, const void *bias, const void *offset,
+    const void *mask, void *output, int32_t elem, int64_t batch, int64_t channels,
+    int64_t height, int64_t width, int64_t channels_out, int32_t kernel_h,
+    int32_t kernel_w, int32_t stride_h, int32_t stride_w, int32_t pad_h,
+    int32_t pad_w, int32_t dilation_h, int32_t dilation_w, int32_t group,
+    int32_t deformable_group, int32_t with_bias, int32_t device, void *workspace,
+    size_t workspace_bytes, void *stream);
+
+/*
+ * dcn_deform_conv_forward is what a binding of
+ *   deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW, dH,
+ *     padW, padH, dilationW, dilationH, group, deformable_group, im2col_step)
+ * (mmcv/ops/csrc/pytorch/pybind.cpp:38-42, :525-530) calls.  Width comes before
+ * height in the scalar arguments, as in the reference.  im2col_step is accepted
+ * and only validated (batch % im2col_step == 0): there is no column buffer to chunk.
+ */
+int dcn_deform_conv_forward(
+    const void *input, const void *weight, const void *offset, void *output,
+    int32_t elem, int64_t batch, int64_t channels, int64_t height, int64_t width,
+    int64_t channels_out, int32_t kW, int32_t kH, int32_t dW, int32_t dH,
+    int32_t padW, int32_t padH, int32_t dilationW, int32_t dilationH,
+    int32_t group, int32_t deformable_group, int32_t im2col_step, int32_t device,
+    void *workspace, size_t workspace_bytes, void *stream);
+
+/* Workspace size for the two flat entry points (same arguments, no pointers). */
+int dcn_forward_workspace_bytes(int32_t elem, int32_t modulated, int64_t batch,
+                                int64_t channels, int64_t height, int64_t width,
+                                int64_t channels_out, int32_t kernel_h,
+                                int32_t kernel_w, int32_t stride_h, int32_t stride_w,
+                                int32_t pad_h, int32_t pad_w, int32_t dilation_h,
+                                int32_t dilation_w, int32_t group,
+                                int32_t deformable_group, size_t *bytes);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DCN_B200_H_ */

@@ -1,0 +1,191 @@
+"""Stand-in for the reference's compiled extension module, for this path only.
+
+Exposes the five functions that the reference's Python wrappers look up on
+``mmcv._ext`` (``mmcv/ops/modulated_deform_conv.py:17-19``,
+``mmcv/ops/deform_conv.py:19-22``) with the positional order and keyword names
+of the reference's module definition (``mmcv/ops/csrc/pytorch/pybind.cpp:525-545,
+641-656``).  The two forwards call the CUDA library through its C ABI; the three
+backward entries exist so that the wrappers import, and raise.
+"""
+import ctypes
+import os
+
+import torch
+
+from . import _lib
+
+_FP32_MATH = {'ffma': _lib.MATH_FFMA, 'tf32x3': _lib.MATH_TF32X3}
+_fp32_math = os.environ.get('DCN_B200_FP32_MATH', 'ffma').lower()
+_check_status = os.environ.get('DCN_B200_CHECK_STATUS', '0') == '1'
+
+
+def set_fp32_math(mode: str) -> None:
+    """Contraction arithmetic for fp32 tensors: 'ffma' or 'tf32x3'."""
+    global _fp32_math
+    if mode not in _FP32_MATH:
+        raise ValueError(f'unknown fp32 math mode {mode!r}')
+    _fp32_math = mode
+
+
+def set_check_status(flag: bool) -> None:
+    """Read the device status word after every call (synchronises)."""
+    global _check_status
+    _check_status = bool(flag)
+
+
+def _dtype_code(t):
+    if t.dtype == torch.float32:
+        return _lib.DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return _lib.DTYPE_BF16
+    raise RuntimeError(f'dcn_b200: unsupported dtype {t.dtype} (float32 and bfloat16 only)')
+
+
+def _require_cuda(**tensors):
+    dev = None
+    for name, t in tensors.items():
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError(f'dcn_b200: {name} must be a CUDA tensor (this build has no '
+                               'CPU implementation)')
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f'dcn_b200: {name} is on {t.device}, expected {dev}')
+    return dev
+
+
+def _ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def forward(input, offset, mask, weight, bias, output, stride, padding, dilation,
+            groups, deform_groups, math_mode=None, act=_lib.ACT_NONE, act_range=(0, 0),
+            offset_batch_stride=0, mask_batch_stride=0, out_batch_stride=0):
+    """Launch one forward on the current stream.  offset=None means an ordinary
+    convolution, mask=None the unmodulated (v1) operator.  Returns the plan path."""
+    lib = _lib.load()
+    dev = _require_cuda(input=input, offset=offset, mask=mask, weight=weight, bias=bias,
+                        output=output)
+    code = _dtype_code(input)
+    for name, t in (('offset', offset), ('mask', mask), ('weight', weight), ('bias', bias),
+                    ('output', output)):
+        if t is not None and t.dtype != input.dtype:
+            raise RuntimeError(f'dcn_b200: {name} has dtype {t.dtype}, input has {input.dtype}')
+    if math_mode is None:
+        math_mode = _lib.MATH_AUTO if code == _lib.DTYPE_BF16 else _FP32_MATH[_fp32_math]
+    p = _lib.DcnFwdParams()
+    p.input, p.offset, p.mask = _ptr(input), _ptr(offset), _ptr(mask)
+    p.weight, p.bias, p.output = _ptr(weight), _ptr(bias), _ptr(output)
+    p.dtype, p.math_mode = code, math_mode
+    p.N, p.C, p.H, p.W = input.shape
+    p.Co = weight.shape[0]
+    p.kh, p.kw = weight.shape[2], weight.shape[3]
+    p.stride_h, p.stride_w = stride
+    p.pad_h, p.pad_w = padding
+    p.dil_h, p.dil_w = dilation
+    p.groups, p.deform_groups = groups, deform_groups
+    for i, s in enumerate(input.stride()):
+        p.in_stride[i] = s
+    p.offset_batch_stride = offset_batch_stride
+    p.mask_batch_stride = mask_batch_stride
+    p.out_batch_stride = out_batch_stride
+    p.act, p.act_lo, p.act_hi = act, act_range[0], act_range[1]
+    p.device = dev.index if dev.index is not None else torch.cuda.current_device()
+    nbytes = ctypes.c_size_t(0)
+    _lib.check(lib.dcn_fwd_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
+    with torch.cuda.device(dev):
+        ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dcn_fwd(ctypes.byref(p), _ptr(ws), nbytes.value, stream))
+        if _check_status:
+            st = ctypes.c_int32(0)
+            _lib.check(lib.dcn_read_status(_ptr(ws), stream, ctypes.byref(st)))
+            if st.value != 0:
+                raise RuntimeError(f'dcn_b200: device-side wait {st.value} timed out; the '
+                                   'output is not valid')
+    return ws
+
+
+def _input_layout(x):
+    if x.is_contiguous() or x.is_contiguous(memory_format=torch.channels_last):
+        return x
+    return x.contiguous()
+
+
+def modulated_deform_conv_forward(input, weight, bias, ones, offset, mask, output, columns,
+                                  kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w,
+                                  dilation_h, dilation_w, group, deformable_group, with_bias):
+    """Same contract as the reference entry of this name
+    (mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:395-412): writes the result into
+    ``output`` in place; ``ones`` and ``columns`` are accepted and left untouched."""
+    if weight.size(2) != kernel_h or weight.size(3) != kernel_w:
+        raise RuntimeError(f"Input shape and kernel shape won't match: ({kernel_h} x {kernel_w} "
+                           f'vs {weight.size(2)} x {weight.size(3)}).')
+    if input.size(1) != weight.size(1) * group:
+        raise RuntimeError(f"Input shape and kernel channels won't match: ({input.size(1)} vs "
+                           f'{weight.size(1) * group}).')
+    if not output.is_contiguous():
+        raise RuntimeError('dcn_b200: output must be contiguous')
+    b = bias.contiguous() if (with_bias and bias is not None and bias.numel() > 0) else None
+    if with_bias and b is None:
+        raise RuntimeError('dcn_b200: with_bias is set but bias is empty')
+    forward(_input_layout(input), offset.contiguous(), mask.contiguous(), weight.contiguous(), b,
+            output, (stride_h, stride_w), (pad_h, pad_w), (dilation_h, dilation_w), group,
+            deformable_group)
+
+
+def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW, dH, padW,
+                        padH, dilationW, dilationH, group, deformable_group, im2col_step):
+    """Same contract as the reference entry of this name
+    (mmcv/ops/csrc/pytorch/deform_conv.cpp:140-260), including its contiguity and shape
+    checks (:45-138, :145-166); ``im2col_step`` is validated and otherwise unused."""
+    for name, t in (('input', input), ('offset', offset), ('weight', weight),
+                    ('output', output)):
+        if not t.is_cuda:
+            raise RuntimeError(f'{name} must be a CUDA tensor (this build has no CPU '
+                               'implementation)')
+        if not t.is_contiguous():
+            raise RuntimeError(f'{name} must be contiguous')
+    if weight.dim() != 4:
+        raise RuntimeError('4D weight tensor (nOutputPlane,nInputPlane,kH,kW) expected, but got: '
+                           f'{weight.dim()}')
+    if weight.size(2) != kH or weight.size(3) != kW:
+        raise RuntimeError('kernel size should be consistent with weight, but got '
+                           f'kH: {kH} kW: {kW} weight.size(2): {weight.size(2)}, '
+                           f'weight.size(3): {weight.size(3)}')
+    if input.dim() != 4:
+        raise RuntimeError(f'4D input tensor expected but got: {input.dim()}')
+    n_in = weight.size(1) * group
+    if input.size(1) != n_in:
+        raise RuntimeError(f'invalid number of input planes, expected: {n_in}, but got: '
+                           f'{input.size(1)}')
+    if input.size(2) < kH or input.size(3) < kW:
+        raise RuntimeError('input image is smaller than kernel')
+    ho = (input.size(2) + 2 * padH - (dilationH * (kH - 1) + 1)) // dH + 1 if dH > 0 else 0
+    wo = (input.size(3) + 2 * padW - (dilationW * (kW - 1) + 1)) // dW + 1 if dW > 0 else 0
+    if dH > 0 and dW > 0 and ho >= 1 and wo >= 1:
+        if offset.size(2) != ho or offset.size(3) != wo:
+            raise RuntimeError(f'invalid spatial size of offset, expected height: {ho} width: '
+                               f'{wo}, but got height: {offset.size(2)} width: {offset.size(3)}')
+        if offset.size(1) != deformable_group * 2 * kH * kW:
+            raise RuntimeError('invalid number of channels of offset')
+    if offset.size(0) != input.size(0):
+        raise RuntimeError('invalid batch size of offset')
+    if im2col_step <= 0 or input.size(0) % im2col_step != 0:
+        raise RuntimeError('batch size must be divisible by im2col_step')
+    forward(input, offset, None, weight, None, output, (dH, dW), (padH, padW),
+            (dilationH, dilationW), group, deformable_group)
+
+
+def _no_backward(name):
+    def fn(*args, **kwargs):
+        raise RuntimeError(f'dcn_b200: {name} is not implemented (forward-only build)')
+    fn.__name__ = name
+    return fn
+
+
+modulated_deform_conv_backward = _no_backward('modulated_deform_conv_backward')
+deform_conv_backward_input = _no_backward('deform_conv_backward_input')
+deform_conv_backward_parameters = _no_backward('deform_conv_backward_parameters')

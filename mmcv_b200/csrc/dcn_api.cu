@@ -1,0 +1,387 @@
+// C-ABI layer: argument checks (the reference's own, plus what a raw-pointer interface
+// needs), kernel selection, workspace layout and launch sequencing.
+//
+// Checks restated from the reference:
+//   kernel size / channel consistency .. mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:80-85
+//   positive kernel/stride/dilation, C % deformable_group, output size >= 1,
+//   input >= kernel (v1) ............... mmcv/ops/csrc/pytorch/deform_conv.cpp:45-138
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "dcn_internal.cuh"
+
+namespace dcn {
+size_t tc_smem_bytes(const TcPlan &tp, int T);
+
+namespace {
+
+thread_local char g_err[512] = "";
+
+int fail(int code, const char *fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+constexpr size_t kMaxSmemOptin = 232448;  // 227 KiB per block on sm_100
+constexpr int kSmCountFallback = 148;
+
+struct DeviceInfo {
+  bool probed = false;
+  int err = 0;
+  int sms = 0;
+  int cc_major = 0;
+  size_t tc_smem_set = 0;
+};
+DeviceInfo g_dev[64];
+std::mutex g_mu;
+
+size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+size_t esize(int dtype) { return dtype == DCN_DTYPE_F32 ? 4 : 2; }
+
+int build_geom(const DcnFwdParams *p, Geom *g) {
+  if (!p) return fail(DCN_ERR_ARG, "params is NULL");
+  if (p->dtype != DCN_DTYPE_F32 && p->dtype != DCN_DTYPE_BF16)
+    return fail(DCN_ERR_UNSUPPORTED, "unsupported element type %d (fp32 and bf16 only)", p->dtype);
+  if (p->math_mode < DCN_MATH_AUTO || p->math_mode > DCN_MATH_BF16)
+    return fail(DCN_ERR_ARG, "unknown math mode %d", p->math_mode);
+  if (p->kh <= 0 || p->kw <= 0)
+    return fail(DCN_ERR_ARG, "kernel size should be greater than zero, but got kH: %d kW: %d",
+                p->kh, p->kw);
+  if (p->stride_h <= 0 || p->stride_w <= 0)
+    return fail(DCN_ERR_ARG, "stride should be greater than zero, but got dH: %d dW: %d",
+                p->stride_h, p->stride_w);
+  if (p->dil_h <= 0 || p->dil_w <= 0)
+    return fail(DCN_ERR_ARG, "dilation should be greater than 0, but got dilationH: %d dilationW: %d",
+                p->dil_h, p->dil_w);
+  if (p->pad_h < 0 || p->pad_w < 0) return fail(DCN_ERR_ARG, "padding must be non-negative");
+  if (p->N < 0 || p->C <= 0 || p->H <= 0 || p->W <= 0 || p->Co <= 0)
+    return fail(DCN_ERR_ARG, "tensor sizes must be positive (N=%lld C=%lld H=%lld W=%lld Co=%lld)",
+                (long long)p->N, (long long)p->C, (long long)p->H, (long long)p->W,
+                (long long)p->Co);
+  if (p->groups <= 0 || p->deform_groups <= 0)
+    return fail(DCN_ERR_ARG, "group and deformable_group must be positive");
+  if (p->C % p->groups != 0 || p->Co % p->groups != 0)
+    return fail(DCN_ERR_ARG, "Input shape and kernel channels won't match: (%lld vs groups %d).",
+                (long long)p->C, p->groups);
+  if (p->C % p->deform_groups != 0)
+    return fail(DCN_ERR_ARG, "input channels must divide deformable group size");
+  const long long Ho = (p->H + 2LL * p->pad_h - (p->dil_h * (p->kh - 1LL) + 1)) / p->stride_h + 1;
+  const long long Wo = (p->W + 2LL * p->pad_w - (p->dil_w * (p->kw - 1LL) + 1)) / p->stride_w + 1;
+  if ((p->H + 2LL * p->pad_h - (p->dil_h * (p->kh - 1LL) + 1)) < 0 ||
+      (p->W + 2LL * p->pad_w - (p->dil_w * (p->kw - 1LL) + 1)) < 0 || Ho < 1 || Wo < 1)
+    return fail(DCN_ERR_ARG,
+                "Given input size: (%lld x %lld x %lld). Calculated output size: (%lld x %lld x "
+                "%lld). Output size is too small",
+                (long long)p->C, (long long)p->H, (long long)p->W, (long long)p->Co, Ho, Wo);
+  const long long lim = 2147483647LL;
+  if (p->N > lim || p->C > lim || p->H > lim || p->W > lim || p->Co > lim || Ho * Wo > lim ||
+      p->H * p->W * p->C > lim || (long long)p->kh * p->kw > 4096)
+    return fail(DCN_ERR_UNSUPPORTED, "a per-sample tensor exceeds 2^31 elements");
+  memset(g, 0, sizeof(*g));
+  g->N = (int)p->N; g->C = (int)p->C; g->H = (int)p->H; g->W = (int)p->W; g->Co = (int)p->Co;
+  g->Ho = (int)Ho; g->Wo = (int)Wo;
+  g->kh = p->kh; g->kw = p->kw; g->T = p->kh * p->kw;
+  g->stride_h = p->stride_h; g->stride_w = p->stride_w;
+  g->pad_h = p->pad_h; g->pad_w = p->pad_w; g->dil_h = p->dil_h; g->dil_w = p->dil_w;
+  g->groups = p->groups; g->dg = p->deform_groups;
+  g->Cg = g->C / g->groups; g->Cog = g->Co / g->groups; g->cpdg = g->C / g->dg;
+  g->P = (long long)g->N * Ho * Wo;
+  g->in_sn = p->in_stride[0]; g->in_sc = p->in_stride[1];
+  g->in_sh = p->in_stride[2]; g->in_sw = p->in_stride[3];
+  const bool nchw = g->in_sw == 1 && g->in_sh == g->W && g->in_sc == (long long)g->H * g->W &&
+                    (g->N <= 1 || g->in_sn >= (long long)g->C * g->H * g->W);
+  const bool nhwc = g->in_sc == 1 && g->in_sw == g->C && g->in_sh == (long long)g->W * g->C &&
+                    (g->N <= 1 || g->in_sn >= (long long)g->C * g->H * g->W);
+  if (!nchw && !nhwc && !(g->C == 1 && g->in_sw == 1 && g->in_sh == g->W))
+    return fail(DCN_ERR_ARG, "input must be NCHW-contiguous or channels-last");
+  g->off_sn = p->offset_batch_stride ? p->offset_batch_stride : (long long)g->dg * 2 * g->T * Ho * Wo;
+  g->msk_sn = p->mask_batch_stride ? p->mask_batch_stride : (long long)g->dg * g->T * Ho * Wo;
+  g->out_sn = p->out_batch_stride ? p->out_batch_stride : (long long)g->Co * Ho * Wo;
+  g->act = p->act; g->act_lo = p->act_lo; g->act_hi = p->act_hi;
+  if (g->act != DCN_ACT_NONE && g->act != DCN_ACT_SIGMOID)
+    return fail(DCN_ERR_ARG, "unknown activation %d", g->act);
+  return DCN_OK;
+}
+
+bool input_is_cl_bf16(const DcnFwdParams *p, const Geom &g) {
+  return p->dtype == DCN_DTYPE_BF16 && g.in_sc == 1 && g.in_sw == g.C &&
+         g.in_sh == (long long)g.W * g.C && g.in_sn == (long long)g.H * g.W * g.C;
+}
+
+// Decide whether the tensor-core kernel can take the problem and with what tiling.
+bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
+  const int math = p->math_mode == DCN_MATH_AUTO
+                       ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_FFMA)
+                       : p->math_mode;
+  if (math != DCN_MATH_BF16) return false;
+  if (g.Cg % kBK != 0 || g.cpdg % 8 != 0) return false;
+  if ((long long)g.N * g.H * g.W >= 2147483647LL) return false;
+  memset(tp, 0, sizeof(*tp));
+  tp->NT = (g.Cog + 255) / 256;
+  const int per = (g.Cog + tp->NT - 1) / tp->NT;
+  tp->BN = (per + 31) / 32 * 32;
+  tp->KC = g.Cg / kBK;
+  tp->S = tp->KC * g.T;
+  int ndgc = 1;
+  for (int grp = 0; grp < g.groups; ++grp)
+    for (int cc = 0; cc < tp->KC; ++cc) {
+      const int c0 = grp * g.Cg + cc * kBK;
+      const int lo = c0 / g.cpdg, hi = (c0 + kBK - 1) / g.cpdg;
+      const int nd = (hi < g.dg ? hi : g.dg - 1) - lo + 1;
+      if (nd > ndgc) ndgc = nd;
+    }
+  tp->ndgc = ndgc;
+  tp->a_stages = 4;
+  int cols = 32;
+  while (cols < 2 * tp->BN) cols *= 2;
+  tp->tmem_cols = cols;
+  for (int b = 8; b >= 2; --b) {
+    tp->b_stages = b;
+    tp->smem = tc_smem_bytes(*tp, g.T);
+    if (tp->smem <= kMaxSmemOptin) break;
+  }
+  if (tp->smem > kMaxSmemOptin) return false;
+  const long long mtiles = (g.P + kBM - 1) / kBM;
+  tp->items = mtiles * g.groups * tp->NT;
+  tp->grid = (int)(tp->items < sms ? tp->items : sms);
+  return true;
+}
+
+void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPlan &tp,
+                      Workspace *ws) {
+  memset(ws, 0, sizeof(*ws));
+  size_t off = 256;
+  if (tc) {
+    ws->wtile_off = off;
+    ws->wtile_bytes = (size_t)g.groups * tp.NT * tp.S * tp.BN * 128;
+    off = align_up(off + ws->wtile_bytes, 256);
+    if (!input_is_cl_bf16(p, g)) {
+      ws->xcl_off = off;
+      ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * 2;
+      off = align_up(off + ws->xcl_bytes, 256);
+    }
+  }
+  ws->total = off;
+}
+
+int probe_device(int device, DeviceInfo **out) {
+  if (device < 0 || device >= 64) return fail(DCN_ERR_ARG, "device ordinal %d out of range", device);
+  std::lock_guard<std::mutex> lk(g_mu);
+  DeviceInfo &d = g_dev[device];
+  if (!d.probed) {
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail(DCN_ERR_DEVICE, "no usable CUDA device %d: %s (there is no CPU path)", device,
+                  cudaGetErrorString(e));
+    }
+    d.sms = prop.multiProcessorCount;
+    d.cc_major = prop.major;
+    d.probed = true;
+  }
+  if (d.cc_major != 10)
+    return fail(DCN_ERR_DEVICE, "device %d is compute capability %d.x; this library is sm_100a only",
+                device, d.cc_major);
+  *out = &d;
+  return DCN_OK;
+}
+
+struct Plan {
+  Geom g;
+  bool tc;
+  TcPlan tp;
+  Workspace ws;
+  int launches;
+  bool stage;
+};
+
+int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
+  int rc = build_geom(p, &pl->g);
+  if (rc) return rc;
+  if (p->math_mode == DCN_MATH_TF32X3)
+    return fail(DCN_ERR_UNSUPPORTED, "the 3xTF32 contraction is not built yet; use FFMA");
+  pl->tc = plan_tc(p, pl->g, sms, &pl->tp);
+  if (!pl->tc && p->math_mode == DCN_MATH_BF16)
+    return fail(DCN_ERR_UNSUPPORTED,
+                "bf16 tensor-core contraction needs C/groups %% 64 == 0 and C/deformable_group %% 8 "
+                "== 0 (got C/groups=%d, C/deformable_group=%d)", pl->g.Cg, pl->g.cpdg);
+  layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);
+  pl->stage = pl->tc && pl->ws.xcl_bytes != 0;
+  pl->launches = pl->tc ? (3 + (pl->stage ? 1 : 0)) : 2;  // status clear + prep + main
+  return DCN_OK;
+}
+
+}  // namespace
+}  // namespace dcn
+
+using namespace dcn;
+
+extern "C" {
+
+int dcn_abi_version(void) { return DCN_ABI_VERSION; }
+const char *dcn_last_error(void) { return g_err; }
+
+int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
+  if (!info) return fail(DCN_ERR_ARG, "info is NULL");
+  Plan pl;
+  int rc = make_plan(p, kSmCountFallback, &pl);
+  if (rc) return rc;
+  memset(info, 0, sizeof(*info));
+  info->path = pl.tc ? DCN_PATH_TCGEN05 : DCN_PATH_SIMT_DIRECT;
+  info->launches = pl.launches;
+  info->stages_input = pl.stage ? 1 : 0;
+  info->tile_m = pl.tc ? kBM : 1;
+  info->tile_n = pl.tc ? pl.tp.BN : 1;
+  info->tile_k = pl.tc ? kBK : 1;
+  info->grid = pl.tc ? pl.tp.grid : 0;
+  info->block = pl.tc ? kTcThreads : 256;
+  info->smem_bytes = pl.tc ? (int64_t)pl.tp.smem : 0;
+  info->Ho = pl.g.Ho;
+  info->Wo = pl.g.Wo;
+  info->workspace_bytes = pl.ws.total;
+  return DCN_OK;
+}
+
+int dcn_fwd_workspace_bytes(const DcnFwdParams *p, size_t *bytes) {
+  if (!bytes) return fail(DCN_ERR_ARG, "bytes is NULL");
+  Plan pl;
+  int rc = make_plan(p, kSmCountFallback, &pl);
+  if (rc) return rc;
+  *bytes = pl.ws.total;
+  return DCN_OK;
+}
+
+int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream) {
+  if (!p) return fail(DCN_ERR_ARG, "params is NULL");
+  DeviceInfo *dev = nullptr;
+  int rc = probe_device(p->device, &dev);
+  if (rc) return rc;
+  Plan pl;
+  rc = make_plan(p, dev->sms, &pl);
+  if (rc) return rc;
+  if (!p->input || !p->weight || !p->output)
+    return fail(DCN_ERR_ARG, "input, weight and output pointers must be non-NULL");
+  if (!workspace || workspace_bytes < pl.ws.total)
+    return fail(DCN_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", pl.ws.total,
+                workspace ? workspace_bytes : (size_t)0);
+  if (((uintptr_t)workspace & 255) != 0)
+    return fail(DCN_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  cudaError_t e = cudaSetDevice(p->device);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  cudaStream_t s = (cudaStream_t)stream;
+  uint8_t *ws = (uint8_t *)workspace;
+  int *status = (int *)(ws + pl.ws.status_off);
+  Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
+  e = launch_clear_status(status, s);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+  if (pl.g.P == 0) return DCN_OK;
+  if (!pl.tc) {
+    e = launch_simt_direct(pl.g, ptrs, p->dtype, s);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "SIMT kernel launch: %s", cudaGetErrorString(e));
+    return DCN_OK;
+  }
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (dev->tc_smem_set < pl.tp.smem) {
+      e = tc_set_attributes(kMaxSmemOptin);
+      if (e != cudaSuccess)
+        return fail(DCN_ERR_CUDA, "cudaFuncSetAttribute(shared memory): %s", cudaGetErrorString(e));
+      dev->tc_smem_set = kMaxSmemOptin;
+    }
+  }
+  const __nv_bfloat16 *xcl = (const __nv_bfloat16 *)p->input;
+  if (pl.stage) {
+    __nv_bfloat16 *dst = (__nv_bfloat16 *)(ws + pl.ws.xcl_off);
+    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, s);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
+    xcl = dst;
+  }
+  e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, ws + pl.ws.wtile_off, s);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
+  e = launch_tc_bf16(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, s);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
+  return DCN_OK;
+}
+
+int dcn_read_status(const void *workspace, void *stream, int32_t *status) {
+  if (!workspace || !status) return fail(DCN_ERR_ARG, "workspace and status must be non-NULL");
+  cudaError_t e = cudaMemcpyAsync(status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                  (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+  return DCN_OK;
+}
+
+static void fill_dense(DcnFwdParams *q, int32_t elem, int64_t batch, int64_t channels,
+                       int64_t height, int64_t width, int64_t channels_out, int32_t device) {
+  memset(q, 0, sizeof(*q));
+  q->dtype = elem;
+  q->math_mode = DCN_MATH_AUTO;
+  q->N = batch; q->C = channels; q->H = height; q->W = width; q->Co = channels_out;
+  q->in_stride[0] = channels * height * width;
+  q->in_stride[1] = height * width;
+  q->in_stride[2] = width;
+  q->in_stride[3] = 1;
+  q->device = device;
+}
+
+int dcn_modulated_deform_conv_forward(
+    const void *input, const void *weight, const void *bias, const void *offset,
+    const void *mask, void *output, int32_t elem, int64_t batch, int64_t channels,
+    int64_t height, int64_t width, int64_t channels_out, int32_t kernel_h, int32_t kernel_w,
+    int32_t stride_h, int32_t stride_w, int32_t pad_h, int32_t pad_w, int32_t dilation_h,
+    int32_t dilation_w, int32_t group, int32_t deformable_group, int32_t with_bias,
+    int32_t device, void *workspace, size_t workspace_bytes, void *stream) {
+  if (!offset || !mask) return fail(DCN_ERR_ARG, "offset and mask must be non-NULL");
+  if (with_bias && !bias) return fail(DCN_ERR_ARG, "with_bias is set but bias is NULL");
+  DcnFwdParams q;
+  fill_dense(&q, elem, batch, channels, height, width, channels_out, device);
+  q.input = input; q.weight = weight; q.bias = with_bias ? bias : nullptr;
+  q.offset = offset; q.mask = mask; q.output = output;
+  q.kh = kernel_h; q.kw = kernel_w; q.stride_h = stride_h; q.stride_w = stride_w;
+  q.pad_h = pad_h; q.pad_w = pad_w; q.dil_h = dilation_h; q.dil_w = dilation_w;
+  q.groups = group; q.deform_groups = deformable_group;
+  return dcn_fwd(&q, workspace, workspace_bytes, stream);
+}
+
+int dcn_deform_conv_forward(const void *input, const void *weight, const void *offset,
+                            void *output, int32_t elem, int64_t batch, int64_t channels,
+                            int64_t height, int64_t width, int64_t channels_out, int32_t kW,
+                            int32_t kH, int32_t dW, int32_t dH, int32_t padW, int32_t padH,
+                            int32_t dilationW, int32_t dilationH, int32_t group,
+                            int32_t deformable_group, int32_t im2col_step, int32_t device,
+                            void *workspace, size_t workspace_bytes, void *stream) {
+  if (!offset) return fail(DCN_ERR_ARG, "offset must be non-NULL");
+  if (im2col_step <= 0 || (batch > 0 && batch % im2col_step != 0))
+    return fail(DCN_ERR_ARG, "batch size must be divisible by im2col_step");
+  if (height < kH || width < kW) return fail(DCN_ERR_ARG, "input image is smaller than kernel");
+  DcnFwdParams q;
+  fill_dense(&q, elem, batch, channels, height, width, channels_out, device);
+  q.input = input; q.weight = weight; q.offset = offset; q.output = output;
+  q.kh = kH; q.kw = kW; q.stride_h = dH; q.stride_w = dW; q.pad_h = padH; q.pad_w = padW;
+  q.dil_h = dilationH; q.dil_w = dilationW; q.groups = group; q.deform_groups = deformable_group;
+  return dcn_fwd(&q, workspace, workspace_bytes, stream);
+}
+
+int dcn_forward_workspace_bytes(int32_t elem, int32_t modulated, int64_t batch, int64_t channels,
+                                int64_t height, int64_t width, int64_t channels_out,
+                                int32_t kernel_h, int32_t kernel_w, int32_t stride_h,
+                                int32_t stride_w, int32_t pad_h, int32_t pad_w,
+                                int32_t dilation_h, int32_t dilation_w, int32_t group,
+                                int32_t deformable_group, size_t *bytes) {
+  (void)modulated;
+  DcnFwdParams q;
+  fill_dense(&q, elem, batch, channels, height, width, channels_out, 0);
+  q.kh = kernel_h; q.kw = kernel_w; q.stride_h = stride_h; q.stride_w = stride_w;
+  q.pad_h = pad_h; q.pad_w = pad_w; q.dil_h = dilation_h; q.dil_w = dilation_w;
+  q.groups = group; q.deform_groups = deformable_group;
+  return dcn_fwd_workspace_bytes(&q, bytes);
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+// Internal declarations shared by the kernels and the C-ABI layer.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "dcn_b200.h"
+
+namespace dcn {
+
+// Geometry of one forward problem as the kernels see it (all by value).
+struct Geom {
+  int N, C, H, W, Co, Ho, Wo;
+  int kh, kw, T;  // T = kh*kw taps
+  int stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  int groups, dg;
+  int Cg, Cog, cpdg;  // channels per conv group, outputs per group, channels per deform group
+  long long P;        // N*Ho*Wo output pixels
+  long long in_sn, in_sc, in_sh, in_sw;  // input element strides
+  long long off_sn, msk_sn, out_sn;      // per-sample strides of offset/mask/output
+  int act, act_lo, act_hi;
+};
+
+struct Ptrs {
+  const void *input, *offset, *mask, *weight, *bias;
+  void *output;
+};
+
+// Workspace layout (byte offsets from the workspace base).
+struct Workspace {
+  size_t status_off;   // 256 B: status word
+  size_t wtile_off;    // swizzled weight tiles (tcgen05 path)
+  size_t wtile_bytes;
+  size_t xcl_off;      // channels-last bf16 copy of the input (tcgen05 path)
+  size_t xcl_bytes;
+  size_t total;
+};
+
+// tcgen05 path configuration decided on the host.
+struct TcPlan {
+  int BN;         // accumulator columns per tile (multiple of 16, <= 256)
+  int NT;         // n-tiles per conv group
+  int KC;         // 64-channel chunks per conv group
+  int S;          // k-stages per tile = KC*T
+  int ndgc;       // max deform groups touched by one 64-channel chunk
+  int a_stages, b_stages;
+  int tmem_cols;  // power of two >= 2*BN
+  long long items;  // tiles*groups*NT
+  int grid;
+  size_t smem;
+};
+
+enum { kTcThreads = 448, kTcProducerWarps = 8, kBM = 128, kBK = 64 };
+
+// One sampling tap: bilinear corner weights (already multiplied by the modulation
+// mask, and zero for corners outside the plane) and the integer position of the
+// top-left corner.  Follows dmcn_im2col_bilinear
+// (mmcv/ops/csrc/common/cuda/modulated_deform_conv_cuda_kernel.cuh:80-108) and the
+// sampling gate of its caller (same file, :237-239).  A position that is NaN or
+// outside (-1, H) x (-1, W) yields four zero weights.
+__device__ __forceinline__ void tap_weights(float off_h, float off_w, float m,
+                                            int h_base, int w_base, int H, int W,
+                                            float4 &wt, int &h_low, int &w_low) {
+  const float h_im = (float)h_base + off_h;
+  const float w_im = (float)w_base + off_w;
+  wt = make_float4(0.f, 0.f, 0.f, 0.f);
+  h_low = 0;
+  w_low = 0;
+  if (h_im > -1.f && w_im > -1.f && h_im < (float)H && w_im < (float)W) {
+    const float hf = floorf(h_im), wf = floorf(w_im);
+    h_low = (int)hf;
+    w_low = (int)wf;
+    const float lh = h_im - hf, lw = w_im - wf;
+    const float hh = 1.f - lh, hw = 1.f - lw;
+    const bool top = h_low >= 0, left = w_low >= 0;
+    const bool bot = h_low + 1 <= H - 1, right = w_low + 1 <= W - 1;
+    wt.x = (top && left) ? hh * hw * m : 0.f;
+    wt.y = (top && right) ? hh * lw * m : 0.f;
+    wt.z = (bot && left) ? lh * hw * m : 0.f;
+    wt.w = (bot && right) ? lh * lw * m : 0.f;
+  }
+}
+
+__device__ __forceinline__ float ld_as_float(const float *p, long long i) { return p[i]; }
+__device__ __forceinline__ float ld_as_float(const __nv_bfloat16 *p, long long i) {
+  return __bfloat162float(p[i]);
+}
+__device__ __forceinline__ void st_from_float(float *p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void st_from_float(__nv_bfloat16 *p, long long i, float v) {
+  p[i] = __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float apply_act(const Geom &g, int co, float v) {
+  if (g.act == DCN_ACT_SIGMOID && co >= g.act_lo && co < g.act_hi)
+    v = 1.f / (1.f + __expf(-v));
+  return v;
+}
+
+// Launchers (each enqueues on `stream` and returns the CUDA error of the launch).
+cudaError_t launch_simt_direct(const Geom &g, const Ptrs &p, int dtype, cudaStream_t s);
+cudaError_t launch_simt_tiled(const Geom &g, const Ptrs &p, int dtype, cudaStream_t s);
+size_t simt_tiled_smem(const Geom &g);
+bool simt_tiled_supported(const Geom &g);
+
+cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype,
+                                  __nv_bfloat16 *xcl, cudaStream_t s);
+cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight,
+                                int dtype, void *wtiles, cudaStream_t s);
+cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
+                           const __nv_bfloat16 *xcl, const void *wtiles, int *status,
+                           cudaStream_t s);
+cudaError_t tc_set_attributes(size_t smem);
+cudaError_t launch_clear_status(int *status, cudaStream_t s);
+
+}  // namespace dcn

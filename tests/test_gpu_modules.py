@@ -1,0 +1,82 @@
+"""The layer classes and functions under the reference's names, on the GPU."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from conftest import fp32_close, golden_cases, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+
+def test_reference_known_answer_v2_pack(kat):
+    # the reference's own DCNv2 test construction (its test file, lines 51-85), forward part
+    from mmcv_b200.ops import ModulatedDeformConv2dPack
+    x = torch.tensor(kat['v2_input'], device='cuda')
+    dcn = ModulatedDeformConv2dPack(1, 1, kernel_size=(2, 2), stride=1, padding=1,
+                                    deform_groups=1, bias=False).cuda()
+    dcn.weight.data.fill_(1.)
+    y = dcn(x)
+    assert np.allclose(y.detach().cpu().numpy(), kat['v2_expected'], 1e-2)
+    assert np.allclose(y.detach().cpu().numpy(), kat['v2_ref_out'], rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize('batch,step', [(10, 2), (1, 2)])
+def test_reference_known_answer_v1_pack(kat, batch, step):
+    from mmcv_b200.ops import DeformConv2dPack
+    x = torch.tensor(np.repeat(kat['v1_input'], batch, axis=0), device='cuda')
+    m = DeformConv2dPack(in_channels=1, out_channels=1, kernel_size=2, stride=1, padding=0,
+                         im2col_step=step)
+    m.conv_offset.weight.data = torch.tensor(kat['v1_offset_weight'])
+    m.conv_offset.bias.data = torch.tensor(kat['v1_offset_bias'])
+    m.weight.data = torch.tensor(kat['v1_deform_weight'])
+    m.cuda()
+    y = m(x).detach().cpu().numpy()
+    assert np.allclose(y, np.repeat(kat['v1_expected'], batch, axis=0), 1e-3)
+
+
+def test_v1_batch_not_divisible_by_step():
+    from mmcv_b200.ops import DeformConv2dPack
+    m = DeformConv2dPack(1, 1, 2, im2col_step=3).cuda()
+    with pytest.raises(AssertionError, match='batch size must be divisible by im2col_step'):
+        m(torch.zeros(10, 1, 3, 3, device='cuda'))
+
+
+def test_functional_v2_matches_fixture():
+    from mmcv_b200.ops import modulated_deform_conv2d
+    m, t = golden_cases().get('v2_s2_d2_dg4_int')
+    c = lambda v: None if v is None else v.cuda()
+    y = modulated_deform_conv2d(c(t['x']), c(t['offset']), c(t['mask']), c(t['weight']),
+                                c(t['bias']), m['stride'], m['padding'], m['dilation'],
+                                m['groups'], m['deform_groups'])
+    ok, frac = fp32_close(y, t['out'])
+    assert ok, frac
+
+
+def test_functional_v1_small_input_is_padded():
+    from mmcv_b200.ops import DeformConv2d
+    torch.manual_seed(0)
+    layer = DeformConv2d(2, 3, 3, padding=1).cuda()
+    x = torch.randn(1, 2, 2, 2, device='cuda')        # smaller than the 3x3 kernel
+    off = torch.randn(1, 18, 2, 2, device='cuda') * 0.5
+    y = layer(x, off)
+    assert y.shape == (1, 3, 2, 2)
+    import torch.nn.functional as F
+    xp, op = F.pad(x, (0, 1, 0, 1)).cpu(), F.pad(off, (0, 1, 0, 1)).cpu()
+    ref = oracle.best_forward(xp, op, None, layer.weight.detach().cpu(), None, 1, 1, 1, 1, 1)
+    ok, frac = fp32_close(y, ref[:, :, :2, :2])
+    assert ok, frac
+
+
+def test_autocast_dtype_follows_offset():
+    from mmcv_b200.ops import ModulatedDeformConv2dPack
+    torch.manual_seed(1)
+    dcn = ModulatedDeformConv2dPack(64, 64, 3, padding=1).cuda()
+    dcn.conv_offset.weight.data.normal_(0, 0.01)
+    x = torch.randn(2, 64, 20, 20, device='cuda')
+    with torch.autocast('cuda', dtype=torch.bfloat16):
+        y = dcn(x)
+    assert y.dtype == torch.bfloat16
+    y32 = dcn(x)
+    assert y32.dtype == torch.float32
+    assert rel_l2(y.float().cpu(), y32.detach().cpu()) < 5e-2
