@@ -110,6 +110,14 @@ int dcn_fwd_workspace_bytes(const DcnFwdParams *p, size_t *bytes);
 int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
             void *stream);
 
+/* Measurement aid: dcn_fwd with every kernel bracketed by CUDA events on `stream`.
+ * Waits for the work to finish and reports the device time of each launch in
+ * milliseconds: ms[0] channels-last restaging of the input, ms[1] weight tiling,
+ * ms[2] the main kernel (0 for a launch the plan does not contain).  Creates and
+ * destroys four CUDA events; otherwise the same contract as dcn_fwd. */
+int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
+                     void *stream, float ms[3]);
+
 /* Synchronises `stream`, then returns the status word the last dcn_fwd on this
  * workspace left: 0 ok; non-zero = a bounded device-side wait gave up
  * (the kernel returned early, the output is not valid). */

@@ -257,7 +257,8 @@ int dcn_fwd_workspace_bytes(const DcnFwdParams *p, size_t *bytes) {
   return DCN_OK;
 }
 
-int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream) {
+static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream,
+                   cudaEvent_t *ev) {
   if (!p) return fail(DCN_ERR_ARG, "params is NULL");
   DeviceInfo *dev = nullptr;
   int rc = probe_device(p->device, &dev);
@@ -265,7 +266,7 @@ int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void
   Plan pl;
   rc = make_plan(p, dev->sms, &pl);
   if (rc) return rc;
-  if (!p->input || !p->weight || !p->output)
+  if (pl.g.P != 0 && (!p->input || !p->weight || !p->output))
     return fail(DCN_ERR_ARG, "input, weight and output pointers must be non-NULL");
   if (!workspace || workspace_bytes < pl.ws.total)
     return fail(DCN_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", pl.ws.total,
@@ -280,10 +281,16 @@ int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void
   Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
   e = launch_clear_status(status, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
-  if (pl.g.P == 0) return DCN_OK;
+  if (ev) cudaEventRecord(ev[0], s);
+  if (pl.g.P == 0) {
+    if (ev) for (int i = 1; i < 4; ++i) cudaEventRecord(ev[i], s);
+    return DCN_OK;
+  }
   if (!pl.tc) {
+    if (ev) { cudaEventRecord(ev[1], s); cudaEventRecord(ev[2], s); }
     e = launch_simt_direct(pl.g, ptrs, p->dtype, s);
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "SIMT kernel launch: %s", cudaGetErrorString(e));
+    if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;
   }
   {
@@ -302,11 +309,42 @@ int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
     xcl = dst;
   }
+  if (ev) cudaEventRecord(ev[1], s);
   e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, ws + pl.ws.wtile_off, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
+  if (ev) cudaEventRecord(ev[2], s);
   e = launch_tc_bf16(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
+  if (ev) cudaEventRecord(ev[3], s);
   return DCN_OK;
+}
+
+int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream) {
+  return run_fwd(p, workspace, workspace_bytes, stream, nullptr);
+}
+
+int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream,
+                     float ms[3]) {
+  if (!ms) return fail(DCN_ERR_ARG, "ms is NULL");
+  if (!p) return fail(DCN_ERR_ARG, "params is NULL");
+  cudaError_t e = cudaSetDevice(p->device);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  cudaEvent_t ev[4];
+  for (int i = 0; i < 4; ++i) {
+    e = cudaEventCreate(&ev[i]);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
+  }
+  int rc = run_fwd(p, workspace, workspace_bytes, stream, ev);
+  if (rc == DCN_OK) {
+    e = cudaEventSynchronize(ev[3]);
+    if (e != cudaSuccess) rc = fail(DCN_ERR_CUDA, "event synchronize: %s", cudaGetErrorString(e));
+    for (int i = 0; i < 3 && rc == DCN_OK; ++i) {
+      ms[i] = 0.f;
+      cudaEventElapsedTime(&ms[i], ev[i], ev[i + 1]);
+    }
+  }
+  for (int i = 0; i < 4; ++i) cudaEventDestroy(ev[i]);
+  return rc;
 }
 
 int dcn_read_status(const void *workspace, void *stream, int32_t *status) {
