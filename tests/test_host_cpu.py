@@ -135,19 +135,29 @@ def test_module_interface_matches_reference_contract():
 
 
 def test_state_dict_key_upgrade():
-    # checkpoints older than version 2 name the offset branch "<layer>_offset"
-    from mmcv_b200.ops import ModulatedDeformConv2dPack
-    sd = ModulatedDeformConv2dPack(4, 4, 3, padding=1).state_dict()
-    wrapped = torch.nn.Sequential()
-    wrapped.add_module('conv2', ModulatedDeformConv2dPack(4, 4, 3, padding=1))
-    legacy = {}
-    for k, v in sd.items():
-        if k.startswith('conv_offset.'):
-            legacy['conv2_offset.' + k.split('.', 1)[1]] = v + 1
-        else:
-            legacy['conv2.' + k] = v
-    wrapped.load_state_dict(legacy, strict=False)  # parent sees the old names as unexpected
-    assert torch.equal(wrapped.conv2.conv_offset.weight, sd['conv_offset.weight'] + 1)
+    # checkpoints older than version 2 name the offset branch "<layer>_offset"; the layer
+    # renames those keys when it is handed the dict (same rule as the reference layer)
+    from mmcv_b200.ops import DeformConv2dPack, ModulatedDeformConv2dPack
+    for cls in (ModulatedDeformConv2dPack, DeformConv2dPack):
+        layer = cls(4, 4, 3, padding=1)
+        sd = layer.state_dict()
+        legacy = {}
+        for k, v in sd.items():
+            if k.startswith('conv_offset.'):
+                legacy['conv2_offset.' + k.split('.', 1)[1]] = v + 1
+            else:
+                legacy['conv2.' + k] = v
+        missing, unexpected, errors = [], [], []
+        layer._load_from_state_dict(legacy, 'conv2.', {}, True, missing, unexpected, errors)
+        assert 'conv2.conv_offset.weight' in legacy and 'conv2_offset.weight' not in legacy
+        layer.conv_offset._load_from_state_dict(legacy, 'conv2.conv_offset.', {}, True, missing,
+                                                unexpected, errors)
+        assert not missing and not errors
+        assert torch.equal(layer.conv_offset.weight, sd['conv_offset.weight'] + 1)
+        # a version-2 dict is left alone
+        legacy2 = {'conv2_offset.weight': sd['conv_offset.weight']}
+        layer._load_from_state_dict(legacy2, 'conv2.', {'version': 2}, False, [], [], [])
+        assert 'conv2_offset.weight' in legacy2
 
 
 @pytest.mark.skipif(not os.path.isdir('/root/reference/mmcv'), reason='no reference checkout')
