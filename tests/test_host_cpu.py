@@ -140,7 +140,7 @@ def test_state_dict_key_upgrade():
     from mmcv_b200.ops import DeformConv2dPack, ModulatedDeformConv2dPack
     for cls in (ModulatedDeformConv2dPack, DeformConv2dPack):
         layer = cls(4, 4, 3, padding=1)
-        sd = layer.state_dict()
+        sd = {k: v.clone() for k, v in layer.state_dict().items()}
         legacy = {}
         for k, v in sd.items():
             if k.startswith('conv_offset.'):
