@@ -1,0 +1,397 @@
+#!/usr/bin/env python
+"""Benchmark of the deformable-convolution forward (DCNv2) on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--workload c5|c2|c3] [--batch B]
+
+One step = one forward over one batch of synthetic input.  The default workload is the
+large-batch DCNv2 layer (N=256, C_in=C_out=256, 128x128, 3x3, deform_groups=8, bias,
+bf16); with G GPUs the batch is split into G contiguous shards (strong scaling, no
+collective on the data path).  Prints one JSON line on rank 0.
+"""
+import argparse
+import ctypes
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: N, C, H, W, Co, k, stride, pad, dil, groups, dg, offset sigma, mask, bias, int_frac, mask sigma
+    'c5': dict(N=256, C=256, H=128, W=128, Co=256, k=3, s=1, p=1, d=1, g=1, dg=8, sigma=2.0,
+               mask=True, bias=True, int_frac=0.0, msigma=1.0,
+               desc='DCNv2 N=256 C=256 128x128 3x3 s1 p1 dg=8 bias bf16'),
+    'c2': dict(N=8, C=256, H=100, W=168, Co=256, k=3, s=1, p=1, d=1, g=1, dg=1, sigma=1.5,
+               mask=False, bias=False, int_frac=0.0, msigma=1.0,
+               desc='DCNv1 N=8 C=256 100x168 3x3 s1 p1 dg=1 bf16'),
+    'c3': dict(N=4, C=512, H=64, W=64, Co=512, k=3, s=2, p=2, d=2, g=1, dg=4, sigma=8.0,
+               mask=True, bias=True, int_frac=0.05, msigma=2.0,
+               desc='DCNv2 N=4 C=512 64x64 3x3 s2 p2 d2 dg=4 bias bf16'),
+}
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
+# committed ncu summary under profiles/ (None until a capture exists for the workload).
+NCU_TRAFFIC_BYTES = {
+    # 352.8 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
+    # by the batch: traffic grows in proportion to the samples processed
+    'c5': 352.8e6 / 16,
+}
+
+
+def out_size(i, p, d, k, s):
+    return (i + 2 * p - (d * (k - 1) + 1)) // s + 1
+
+
+def flops_and_bytes(wl, n, esize):
+    Ho, Wo = out_size(wl['H'], wl['p'], wl['d'], wl['k'], wl['s']), out_size(wl['W'], wl['p'], wl['d'], wl['k'], wl['s'])
+    T = wl['k'] * wl['k']
+    K = wl['C'] // wl['g'] * T
+    fl = 2.0 * n * wl['Co'] * Ho * Wo * K
+    by = n * wl['C'] * wl['H'] * wl['W'] + n * 2 * wl['dg'] * T * Ho * Wo + wl['Co'] * K + n * wl['Co'] * Ho * Wo
+    if wl['mask']:
+        by += n * wl['dg'] * T * Ho * Wo
+    if wl['bias']:
+        by += wl['Co']
+    return fl, by * esize, Ho, Wo
+
+
+def make_inputs(wl, n0, n1, device, dtype):
+    """Samples [n0, n1) of the workload, seeded per sample so that shards are reproducible."""
+    Ho, Wo = out_size(wl['H'], wl['p'], wl['d'], wl['k'], wl['s']), out_size(wl['W'], wl['p'], wl['d'], wl['k'], wl['s'])
+    T = wl['k'] * wl['k']
+    n = n1 - n0
+    x = torch.empty(n, wl['C'], wl['H'], wl['W'], device=device, dtype=dtype)
+    off = torch.empty(n, wl['dg'] * 2 * T, Ho, Wo, device=device, dtype=dtype)
+    msk = torch.empty(n, wl['dg'] * T, Ho, Wo, device=device, dtype=dtype) if wl['mask'] else None
+    gen = torch.Generator(device=device)
+    for i in range(n):
+        gen.manual_seed(n0 + i)
+        x[i] = torch.randn(x.shape[1:], device=device, generator=gen)
+        o = torch.randn(off.shape[1:], device=device, generator=gen) * wl['sigma']
+        if wl['int_frac']:
+            sel = torch.rand(o.shape, device=device, generator=gen) < wl['int_frac']
+            o = torch.where(sel, o.round(), o)
+        off[i] = o
+        if msk is not None:
+            msk[i] = torch.sigmoid(torch.randn(msk.shape[1:], device=device, generator=gen) * wl['msigma'])
+    gen.manual_seed(12345)
+    fan = wl['C'] // wl['g'] * T
+    bound = (6.0 / fan) ** 0.5      # Kaiming-uniform
+    w = ((torch.rand(wl['Co'], wl['C'] // wl['g'], wl['k'], wl['k'], device=device, generator=gen) * 2 - 1) * bound).to(dtype)
+    b = (torch.rand(wl['Co'], device=device, generator=gen) * 0.2 - 0.1).to(dtype) if wl['bias'] else None
+    return x, off, msk, w, b
+
+
+class ClockSampler:
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,'
+             'clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index):
+        self.f = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
+        try:
+            self.p = subprocess.Popen(['nvidia-smi', '-i', str(index), '--query-gpu=' + self.QUERY,
+                                       '--format=csv,noheader,nounits', '-lms', '100'],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.p = None
+
+    def stop(self):
+        out = {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+        if self.p is None:
+            return out
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, reasons = [], [], set()
+        for line in self.f.read().splitlines():
+            c = [v.strip() for v in line.split(',')]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2]))
+            except ValueError:
+                continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
+                                'sw_power_cap'), c[5:9]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        self.f.close()
+        os.unlink(self.f.name)
+        if sm:
+            sm.sort()
+            # median of the upper half ~ median under load (idle samples bracket the run)
+            load = sm[len(sm) // 2:]
+            out.update(sm_mhz=load[len(load) // 2], sm_max_mhz=max(mx), samples=len(sm))
+        out['reasons'] = sorted(reasons)
+        return out
+
+
+def cpu_reference_sample(wl, seconds_budget=20.0, max_reps=3):
+    """Time the reference CPU implementation (or the C restatement) on a bounded sample of
+    the workload: fp32 arithmetic on the bf16-rounded inputs, N=2 samples per call."""
+    import oracle
+    kind = 'reference' if oracle.have_ref() else 'port'
+    torch.set_num_threads(os.cpu_count() or 1)
+    n = min(2, wl['N'])
+    x, off, msk, w, b = make_inputs(wl, 0, n, torch.device('cpu'), torch.bfloat16)
+    f = lambda t: None if t is None else t.float()
+    args = (f(x), f(off), f(msk), f(w), f(b), wl['s'], wl['p'], wl['d'], wl['g'], wl['dg'])
+    fn = oracle.ref_forward if kind == 'reference' else oracle.port_forward
+    fl, _, Ho, Wo = flops_and_bytes(wl, n, 2)
+    best, spent, reps = None, 0.0, 0
+    while reps < max_reps and spent < seconds_budget:
+        t0 = time.perf_counter()
+        fn(*args)
+        dt = time.perf_counter() - t0
+        spent += dt
+        reps += 1
+        best = dt if best is None else min(best, dt)
+    cores = torch.get_num_threads() if kind == 'reference' else oracle.load_port().dcn_oracle_num_threads()
+    return dict(value=fl / best / 1e12, unit='TFLOP/s', cores=cores, kind=kind,
+                sample=f'{n} of {wl["N"]} samples, fp32 on bf16-rounded inputs, best of {reps} '
+                       f'({best:.3f} s per call; gather is single-threaded in the reference, '
+                       f'GEMM uses all threads)',
+                seconds_per_call=best, pixels_per_s=n * Ho * Wo / best)
+
+
+def run_reference(args, wl, rank, world):
+    if rank != 0:
+        return
+    base = cpu_reference_sample(wl, seconds_budget=1e9, max_reps=1)   # warm the library
+    times = []
+    import oracle
+    kind = base['kind']
+    n = min(2, wl['N'])
+    x, off, msk, w, b = make_inputs(wl, 0, n, torch.device('cpu'), torch.bfloat16)
+    f = lambda t: None if t is None else t.float()
+    a = (f(x), f(off), f(msk), f(w), f(b), wl['s'], wl['p'], wl['d'], wl['g'], wl['dg'])
+    fn = oracle.ref_forward if kind == 'reference' else oracle.port_forward
+    for _ in range(max(0, args.warmup - 1)):
+        fn(*a)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn(*a)
+    total = time.perf_counter() - t0
+    fl, _, Ho, Wo = flops_and_bytes(wl, n, 2)
+    val = fl * args.steps / total / 1e12
+    cb = dict(base, value=val, seconds_per_call=total / args.steps)
+    line = dict(impl='reference', metric='dcnv2_fwd_tflops', value=val, unit='TFLOP/s',
+                n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=total / args.steps * 1e3, higher_is_better=True, scaling='strong',
+                vs_baseline=None, dtype='f32', data='synthetic',
+                config=dict(workload=args.workload + ': ' + wl['desc'],
+                            sample=f'each step = {n} of {wl["N"]} samples on the host CPU'),
+                cpu_baseline=cb,
+                e2e=dict(value=val, unit='TFLOP/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                output_pixels_per_s=n * Ho * Wo * args.steps / total, gpu_launches=0)
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=10)
+    ap.add_argument('--warmup', type=int, default=3)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--workload', default='c5', choices=sorted(WORKLOADS))
+    ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
+    ap.add_argument('--e2e-steps', type=int, default=3)
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+    wl = dict(WORKLOADS[args.workload])
+    if args.batch:
+        wl['N'] = args.batch
+
+    rank = int(os.environ.get('RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+
+    if args.impl == 'reference':
+        run_reference(args, wl, rank, world)
+        return
+
+    import torch.distributed as dist
+    from mmcv_b200 import _ext, _lib
+    from mmcv_b200.ops import deform_conv2d, modulated_deform_conv2d
+    lib = _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: there is no CPU path')
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=dev)
+
+    # contiguous shard of the batch for this rank
+    from mmcv_b200.shard import batch_shard
+    n0, n1 = batch_shard(wl['N'], rank, world)
+    per = (wl['N'] + world - 1) // world
+    n = n1 - n0
+    dtype = torch.bfloat16
+    x, off, msk, w, b = make_inputs(wl, n0, n1, dev, dtype)
+    fl_rank, by_rank, Ho, Wo = flops_and_bytes(wl, n, 2)
+    fl_total, by_total, _, _ = flops_and_bytes(wl, wl['N'], 2)
+    out = torch.empty(n, wl['Co'], Ho, Wo, device=dev, dtype=dtype)
+    st, pd, dl = (wl['s'],) * 2, (wl['p'],) * 2, (wl['d'],) * 2
+
+    # C-ABI parameters for the device-resident measurement (same call the public API makes)
+    def params():
+        p = _lib.DcnFwdParams()
+        p.input, p.offset = x.data_ptr(), off.data_ptr()
+        p.mask = msk.data_ptr() if msk is not None else None
+        p.weight, p.bias = w.data_ptr(), (b.data_ptr() if b is not None else None)
+        p.output = out.data_ptr()
+        p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
+        p.N, p.C, p.H, p.W, p.Co = n, wl['C'], wl['H'], wl['W'], wl['Co']
+        p.kh = p.kw = wl['k']
+        p.stride_h = p.stride_w = wl['s']
+        p.pad_h = p.pad_w = wl['p']
+        p.dil_h = p.dil_w = wl['d']
+        p.groups, p.deform_groups = wl['g'], wl['dg']
+        for i, s in enumerate(x.stride()):
+            p.in_stride[i] = s
+        p.device = local
+        return p
+
+    p = params()
+    info = _lib.DcnPlanInfo()
+    _lib.check(lib.dcn_fwd_plan(ctypes.byref(p), ctypes.byref(info)))
+    ws = torch.empty(max(info.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream(dev)
+    sptr = ctypes.c_void_p(stream.cuda_stream)
+
+    def step():
+        _lib.check(lib.dcn_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel(), sptr))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    stat = ctypes.c_int32(-1)
+    _lib.check(lib.dcn_read_status(ctypes.c_void_p(ws.data_ptr()), sptr, ctypes.byref(stat)))
+    if stat.value != 0:
+        raise SystemExit(f'device status {stat.value}: the kernel gave up a bounded wait')
+
+    # per-kernel device time of the same launches (events between the kernels of a call)
+    kms = [0.0, 0.0, 0.0]
+    reps = max(3, min(args.steps, 10))
+    buf = (ctypes.c_float * 3)()
+    for _ in range(reps):
+        _lib.check(lib.dcn_fwd_profiled(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel(),
+                                        sptr, buf))
+        for i in range(3):
+            kms[i] += buf[i] / reps
+    clocks = sampler.stop() if sampler else None
+
+    # end-to-end through the public API: pinned host -> device, op, device -> pinned host
+    e2e_steps = max(1, min(args.e2e_steps, args.steps))
+    hx, hoff = x.cpu().pin_memory(), off.cpu().pin_memory()
+    hmsk = msk.cpu().pin_memory() if msk is not None else None
+    hout = torch.empty(out.shape, dtype=dtype).pin_memory()
+    h2d = hx.numel() * 2 + hoff.numel() * 2 + (hmsk.numel() * 2 if hmsk is not None else 0)
+    d2h = hout.numel() * 2
+
+    def e2e_step():
+        dx = hx.to(dev, non_blocking=True)
+        doff = hoff.to(dev, non_blocking=True)
+        if hmsk is not None:
+            dm = hmsk.to(dev, non_blocking=True)
+            y = modulated_deform_conv2d(dx, doff, dm, w, b, st, pd, dl, wl['g'], wl['dg'])
+        else:
+            y = deform_conv2d(dx, doff, w, st, pd, dl, wl['g'], wl['dg'], False, 32)
+        hout.copy_(y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(e2e_steps):
+        e2e_step()
+    f1.record(stream)
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / e2e_steps
+
+    t = torch.tensor([ms_total, e2e_ms, kms[0], kms[1], kms[2]], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, e2e_ms, k_stage, k_wt, k_main = t.tolist()
+    ms_step = ms_total / args.steps
+
+    if rank == 0:
+        peaks = {}
+        ppath = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+        if os.path.exists(ppath):
+            peaks = json.load(open(ppath))
+        peak_tf = peaks.get('bf16_tflops', 1590.0)
+        peak_src = 'measured (MEASURED_PEAKS.json bf16_tflops, burst)' if peaks else 'fallback 1.59 PFLOP/s'
+        hbm = peaks.get('hbm_gbs', 6650.0)
+        achieved = fl_rank / (k_main * 1e-3) / 1e12 if k_main > 0 else 0.0
+        roof_ms = max(fl_rank / (peak_tf * 1e12), by_rank / (hbm * 1e9)) * 1e3
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+        traffic = traffic * n if traffic is not None else None
+        line = dict(
+            metric='dcnv2_fwd_tflops', value=fl_total / (ms_step * 1e-3) / 1e12, unit='TFLOP/s',
+            n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step,
+            higher_is_better=True, scaling='strong', vs_baseline=None, dtype='bf16',
+            data='synthetic',
+            config=dict(workload=args.workload + ': ' + wl['desc'], global_batch=wl['N'],
+                        per_gpu_batch=per, parallelism=f'batch-shard x{world}, no collective',
+                        l2='inputs (GBs) larger than L2; no flush needed',
+                        plan=dict(path={1: 'tcgen05', 2: 'simt_tiled', 3: 'simt_direct'}[info.path],
+                                  tile=[info.tile_m, info.tile_n, info.tile_k], grid=info.grid,
+                                  block=info.block, smem_bytes=info.smem_bytes,
+                                  stages_input=bool(info.stages_input))),
+            output_pixels_per_s=wl['N'] * Ho * Wo / (ms_step * 1e-3),
+            layer_roofline=dict(ms=roof_ms, frac=roof_ms / ms_step if world == 1 else None,
+                                flops=fl_rank, compulsory_bytes=by_rank,
+                                note='slower of FLOPs at the bf16 peak and compulsory bytes at HBM '
+                                     'bandwidth, per GPU; frac uses the whole step (all launches)'),
+            kernel_ms=dict(stage_input_cl=k_stage, weight_tiles=k_wt, main=k_main),
+            roofline=dict(bound='tensor', achieved=achieved, peak=peak_tf, unit='TFLOP/s',
+                          frac=achieved / peak_tf, traffic=traffic, peak_source=peak_src,
+                          frac_of_sustained=(achieved / peaks['bf16_tflops_sustained']
+                                             if 'bf16_tflops_sustained' in peaks else None),
+                          kernel='dcn_fwd_tc_bf16'),
+            e2e=dict(value=fl_total / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
+                     h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms,
+                     steps=e2e_steps, api='mmcv_b200.ops.modulated_deform_conv2d'),
+            gpu_launches=args.steps * info.launches,
+            clocks=clocks,
+        )
+        if not args.no_cpu_baseline:
+            line['cpu_baseline'] = cpu_reference_sample(wl)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()
