@@ -118,6 +118,27 @@ int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
 int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
                      void *stream, float ms[3]);
 
+/*
+ * dcn_fwd for callers that can neither pass a workspace nor allocate one: a host that
+ * gives a plugin only input/output buffers and a stream, or a process whose framework
+ * has reserved all device memory so that an allocation made inside a library call fails.
+ * (No counterpart in the reference, whose entry points allocate their column buffer
+ * through the tensor library on every call.)
+ *
+ * The scratch is a fixed DCN_STATIC_SCRATCH_BYTES array inside the library's device
+ * image; problems whose dcn_fwd_workspace_bytes() exceeds it are rejected with
+ * DCN_ERR_WORKSPACE and a message naming both sizes.  The call performs no cudaMalloc,
+ * cudaFree or other allocating routine.  The first call on each device resolves the
+ * array's device address (a one-time runtime query made with that device current), so
+ * make that first call outside any stream capture.  All calls on a device share the
+ * array and it keeps the previous call's contents (the status word is cleared at the
+ * start of every call; everything else is rewritten before use); calls that overlap on
+ * the same GPU race on it and must be serialised by the caller.  If `scratch` is not
+ * NULL it receives the array's device address, which dcn_read_status() accepts.
+ */
+#define DCN_STATIC_SCRATCH_BYTES (32u << 20)
+int dcn_fwd_static_scratch(const DcnFwdParams *p, void *stream, void **scratch);
+
 /* Synchronises `stream`, then returns the status word the last dcn_fwd on this
  * workspace left: 0 ok; non-zero = a bounded device-side wait gave up
  * (the kernel returned early, the output is not valid). */

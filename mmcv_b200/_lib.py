@@ -13,10 +13,12 @@ DTYPE_F32, DTYPE_BF16 = 0, 1
 MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
+STATIC_SCRATCH_BYTES = 32 << 20
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
-           'dcn_fwd_workspace_bytes', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_read_status',
+           'dcn_fwd_workspace_bytes', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
+           'dcn_read_status',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
 
@@ -74,6 +76,7 @@ def load():
     lib.dcn_fwd_workspace_bytes.argtypes = [P(DcnFwdParams), P(sz)]
     lib.dcn_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_fwd_profiled.argtypes = [P(DcnFwdParams), vp, sz, vp, P(ctypes.c_float)]
+    lib.dcn_fwd_static_scratch.argtypes = [P(DcnFwdParams), vp, P(vp)]
     lib.dcn_read_status.argtypes = [vp, vp, P(i32)]
     lib.dcn_modulated_deform_conv_forward.argtypes = (
         [vp] * 6 + [i32] + [i64] * 5 + [i32] * 12 + [vp, sz, vp])

@@ -218,6 +218,10 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
 }
 
 }  // namespace
+
+// Error channel for entry points that live in other translation units.
+int set_error(int code, const char *msg) { return fail(code, "%s", msg); }
+
 }  // namespace dcn
 
 using namespace dcn;

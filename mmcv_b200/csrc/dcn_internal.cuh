@@ -113,4 +113,7 @@ cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int d
 cudaError_t tc_set_attributes(size_t smem);
 cudaError_t launch_clear_status(int *status, cudaStream_t s);
 
+// Records `msg` as the calling thread's dcn_last_error() text and returns `code`.
+int set_error(int code, const char *msg);
+
 }  // namespace dcn
