@@ -139,6 +139,16 @@ int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_by
 #define DCN_STATIC_SCRATCH_BYTES (32u << 20)
 int dcn_fwd_static_scratch(const DcnFwdParams *p, void *stream, void **scratch);
 
+/* Tracing aid.  When the environment variable DCN_B200_COUNTERS=1 is set, the first
+ * block of the tensor-core kernel accumulates the clock cycles its roles spend in each
+ * phase into 24 counters in the workspace header; this call synchronises `stream` and
+ * copies them out.  Index: 0 producer other, 1 tap-table build, 2 producer rendezvous,
+ * 3 wait for a free operand stage, 4 gather+blend, 5 stages produced (count), 6 tables
+ * built (count), 7 publish stage; 8 MMA waits for weights, 9 MMA waits for operand,
+ * 10 MMA waits for a free accumulator, 11 MMA issue; 12 epilogue waits for accumulator,
+ * 13 epilogue work; 14 loader waits for a free stage, 15 loader issue. */
+int dcn_read_counters(const void *workspace, void *stream, uint64_t counters[24]);
+
 /* Synchronises `stream`, then returns the status word the last dcn_fwd on this
  * workspace left: 0 ok; non-zero = a bounded device-side wait gave up
  * (the kernel returned early, the output is not valid). */

@@ -18,7 +18,7 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_fwd_workspace_bytes', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
-           'dcn_read_status',
+           'dcn_read_counters', 'dcn_read_status',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
 
@@ -77,6 +77,7 @@ def load():
     lib.dcn_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_fwd_profiled.argtypes = [P(DcnFwdParams), vp, sz, vp, P(ctypes.c_float)]
     lib.dcn_fwd_static_scratch.argtypes = [P(DcnFwdParams), vp, P(vp)]
+    lib.dcn_read_counters.argtypes = [vp, vp, P(ctypes.c_uint64)]
     lib.dcn_read_status.argtypes = [vp, vp, P(i32)]
     lib.dcn_modulated_deform_conv_forward.argtypes = (
         [vp] * 6 + [i32] + [i64] * 5 + [i32] * 12 + [vp, sz, vp])

@@ -7,6 +7,7 @@
 //   input >= kernel (v1) ............... mmcv/ops/csrc/pytorch/deform_conv.cpp:45-138
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -41,7 +42,14 @@ DeviceInfo g_dev[64];
 std::mutex g_mu;
 
 size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
-size_t esize(int dtype) { return dtype == DCN_DTYPE_F32 ? 4 : 2; }
+
+// Tuning knobs read from the environment (experiments only; defaults are the tuned values).
+int env_int(const char *name, int dflt, int lo, int hi) {
+  const char *v = getenv(name);
+  if (!v || !*v) return dflt;
+  const int x = atoi(v);
+  return x < lo ? lo : (x > hi ? hi : x);
+}
 
 int build_geom(const DcnFwdParams *p, Geom *g) {
   if (!p) return fail(DCN_ERR_ARG, "params is NULL");
@@ -136,17 +144,58 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
       if (nd > ndgc) ndgc = nd;
     }
   tp->ndgc = ndgc;
-  tp->a_stages = 4;
+  tp->blend_packed = env_int("DCN_B200_PACKED_BLEND", 1, 0, 1);
+  tp->producer_warps = env_int("DCN_B200_PRODUCER_WARPS", 16, 8, 16) >= 16 ? 16 : 8;
   int cols = 32;
   while (cols < 2 * tp->BN) cols *= 2;
   tp->tmem_cols = cols;
-  for (int b = 8; b >= 2; --b) {
-    tp->b_stages = b;
-    tp->smem = tc_smem_bytes(*tp, g.T);
-    if (tp->smem <= kMaxSmemOptin) break;
+  // Pipeline depth.  Shared memory the kernel does not take stays L1, and the gather's hit
+  // rate depends on it, so first try to fit the 164 KB shared-memory configuration (92 KB of
+  // L1), deepest A ring first; only then fall back to the largest configuration.
+  {
+    const int a_forced = env_int("DCN_B200_A_STAGES", 0, 0, 8);
+    const int b_forced = env_int("DCN_B200_B_STAGES", 0, 0, 8);
+    const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
+    bool found = false;
+    for (int bi = 0; bi < 2 && !found; ++bi)
+      for (int as = 4; as >= 2 && !found; --as)
+        for (int bs = (bi == 0 ? 2 : 4); bs >= 2 && !found; --bs) {
+          if ((a_forced && as != a_forced) || (b_forced && bs != b_forced)) continue;
+          tp->a_stages = as;
+          tp->b_stages = bs;
+          tp->smem = tc_smem_bytes(*tp, g.T);
+          found = tp->smem <= budgets[bi];
+        }
+    if (!found) {
+      if (!a_forced && !b_forced) return false;
+      tp->a_stages = a_forced ? a_forced : 2;
+      tp->b_stages = b_forced ? b_forced : 2;
+      tp->smem = tc_smem_bytes(*tp, g.T);
+      if (tp->smem > kMaxSmemOptin) return false;
+    }
   }
-  if (tp->smem > kMaxSmemOptin) return false;
-  const long long mtiles = (g.P + kBM - 1) / kBM;
+  // Tile shape: TH x TW pixels of one sample, TH*TW = 128.  Fewest tiles wins; among
+  // shapes within 3 % of the fewest, the one closest to square (smallest sampled footprint).
+  int best = -1;
+  {
+    const int forced = env_int("DCN_B200_TILE_W", 0, 0, 128);
+    long long tiles[8] = {0}, fewest = -1;
+    for (int lg = 3; lg <= 7; ++lg) {
+      const int tw = 1 << lg, th = kBM >> lg;
+      tiles[lg] = (long long)((g.Wo + tw - 1) / tw) * ((g.Ho + th - 1) / th);
+      if (fewest < 0 || tiles[lg] < fewest) fewest = tiles[lg];
+    }
+    const int preference[5] = {4, 3, 5, 6, 7};  // 8x16, 16x8, 4x32, 2x64, 1x128
+    for (int k = 0; k < 5 && best < 0; ++k)
+      if (tiles[preference[k]] * 100 <= fewest * 103) best = preference[k];
+    for (int lg = 3; lg <= 7; ++lg)
+      if (forced == (1 << lg)) best = lg;
+  }
+  if (best < 0) best = 4;
+  tp->tw_log2 = best;
+  tp->tiles_x = (g.Wo + (1 << best) - 1) >> best;
+  tp->tiles_y = (g.Ho + (kBM >> best) - 1) / (kBM >> best);
+  const long long mtiles = (long long)g.N * tp->tiles_x * tp->tiles_y;
   tp->items = mtiles * g.groups * tp->NT;
   tp->grid = (int)(tp->items < sms ? tp->items : sms);
   return true;
@@ -244,7 +293,7 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   info->tile_n = pl.tc ? pl.tp.BN : 1;
   info->tile_k = pl.tc ? kBK : 1;
   info->grid = pl.tc ? pl.tp.grid : 0;
-  info->block = pl.tc ? kTcThreads : 256;
+  info->block = pl.tc ? (6 + pl.tp.producer_warps) * 32 : 256;
   info->smem_bytes = pl.tc ? (int64_t)pl.tp.smem : 0;
   info->Ho = pl.g.Ho;
   info->Wo = pl.g.Wo;
@@ -297,15 +346,6 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
     if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;
   }
-  {
-    std::lock_guard<std::mutex> lk(g_mu);
-    if (dev->tc_smem_set < pl.tp.smem) {
-      e = tc_set_attributes(kMaxSmemOptin);
-      if (e != cudaSuccess)
-        return fail(DCN_ERR_CUDA, "cudaFuncSetAttribute(shared memory): %s", cudaGetErrorString(e));
-      dev->tc_smem_set = kMaxSmemOptin;
-    }
-  }
   const __nv_bfloat16 *xcl = (const __nv_bfloat16 *)p->input;
   if (pl.stage) {
     __nv_bfloat16 *dst = (__nv_bfloat16 *)(ws + pl.ws.xcl_off);
@@ -317,7 +357,10 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, ws + pl.ws.wtile_off, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
   if (ev) cudaEventRecord(ev[2], s);
-  e = launch_tc_bf16(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, s);
+  // phase counters live in the workspace header, bytes [64, 256); off unless asked for
+  unsigned long long *counters =
+      env_int("DCN_B200_COUNTERS", 0, 0, 1) ? (unsigned long long *)(ws + 64) : nullptr;
+  e = launch_tc_bf16(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, counters, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
   if (ev) cudaEventRecord(ev[3], s);
   return DCN_OK;
@@ -349,6 +392,15 @@ int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_by
   }
   for (int i = 0; i < 4; ++i) cudaEventDestroy(ev[i]);
   return rc;
+}
+
+int dcn_read_counters(const void *workspace, void *stream, uint64_t counters[24]) {
+  if (!workspace || !counters) return fail(DCN_ERR_ARG, "workspace and counters must be non-NULL");
+  cudaError_t e = cudaMemcpyAsync(counters, (const uint8_t *)workspace + 64, 24 * sizeof(uint64_t),
+                                  cudaMemcpyDeviceToHost, (cudaStream_t)stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "counter read: %s", cudaGetErrorString(e));
+  return DCN_OK;
 }
 
 int dcn_read_status(const void *workspace, void *stream, int32_t *status) {

@@ -49,9 +49,13 @@ struct TcPlan {
   long long items;  // tiles*groups*NT
   int grid;
   size_t smem;
+  int tw_log2;             // tile = (128 >> tw_log2) x (1 << tw_log2) output pixels of one sample
+  int tiles_x, tiles_y;    // tiles per sample
+  int blend_packed;        // 1: bilinear blend on packed bf16 FMAs, 0: in fp32
+  int producer_warps;      // 8 or 16
 };
 
-enum { kTcThreads = 448, kTcProducerWarps = 8, kBM = 128, kBK = 64 };
+enum { kBM = 128, kBK = 64 };
 
 // One sampling tap: bilinear corner weights (already multiplied by the modulation
 // mask, and zero for corners outside the plane) and the integer position of the
@@ -109,8 +113,7 @@ cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *wei
                                 int dtype, void *wtiles, cudaStream_t s);
 cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
                            const __nv_bfloat16 *xcl, const void *wtiles, int *status,
-                           cudaStream_t s);
-cudaError_t tc_set_attributes(size_t smem);
+                           unsigned long long *counters, cudaStream_t s);
 cudaError_t launch_clear_status(int *status, cudaStream_t s);
 
 // Records `msg` as the calling thread's dcn_last_error() text and returns `code`.

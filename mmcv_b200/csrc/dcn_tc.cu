@@ -20,6 +20,9 @@
 // Every wait on an mbarrier is bounded: after kWaitLimitNs the waiting thread raises a
 // block-wide abort flag, records a code in the status word and every role leaves its
 // loop; tensor memory is released on every exit path.
+#include <atomic>
+#include <climits>
+
 #include "dcn_internal.cuh"
 
 namespace dcn {
@@ -31,7 +34,6 @@ constexpr int kEpilogueWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
 constexpr int kFirstProducerWarp = 6;
-constexpr int kProducerThreads = kTcProducerWarps * 32;
 constexpr int kAStageBytes = kBM * kBK * 2;  // 16 KiB
 
 struct TcArgs {
@@ -42,6 +44,7 @@ struct TcArgs {
   const void *offset, *mask, *bias;
   void *output;
   int *status;
+  unsigned long long *counters;  // optional phase timers (block 0 only), or nullptr
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -97,6 +100,49 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uin
       ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
       : "memory");
 }
+// Phase timer for the optional counters: adds the clock cycles since `t0` to slot `i` and
+// restarts `t0`.
+struct PhaseTimer {
+  unsigned long long *c;
+  long long t0;
+  __device__ __forceinline__ PhaseTimer(unsigned long long *counters, bool elected)
+      : c(elected ? counters : nullptr), t0(0) {
+    if (c) t0 = clock64();
+  }
+  __device__ __forceinline__ void lap(int i) {
+    if (c) {
+      const long long t1 = clock64();
+      c[i] += (unsigned long long)(t1 - t0);
+      t0 = t1;
+    }
+  }
+  __device__ __forceinline__ void count(int i) {
+    if (c) c[i] += 1;
+  }
+};
+
+__device__ __forceinline__ void prefetch_l2(const void *p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+// Loads whose issue order the compiler must keep (volatile): a batch of them is issued
+// back to back so that their latencies overlap, and only then is the first one consumed.
+// The value is returned raw; converting it (raw_to_float) is a use and waits for the load.
+__device__ __forceinline__ uint32_t ldg_raw_ordered(const float *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ unsigned short ldg_raw_ordered(const __nv_bfloat16 *p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ float raw_to_float(uint32_t v) { return __uint_as_float(v); }
+__device__ __forceinline__ float raw_to_float(unsigned short v) {
+  return __uint_as_float((uint32_t)v << 16);
+}
+template <typename T> struct RawOf { using type = uint32_t; };
+template <> struct RawOf<__nv_bfloat16> { using type = unsigned short; };
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -169,11 +215,59 @@ __device__ __forceinline__ void unpack_fma(float (&acc)[8], float w, const uint4
   }
 }
 
+__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) {
+  return *reinterpret_cast<const __nv_bfloat162 *>(&u);
+}
+__device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 h) {
+  return *reinterpret_cast<const uint32_t *>(&h);
+}
+
+// Bilinear blend of four 8-channel corner vectors.  kPacked: weights are bf16 pairs and the
+// blend runs on packed bf16 FMAs (one multiply and three fused multiply-adds per channel
+// pair, each rounding to bf16); otherwise weights are fp32 and the blend is done in fp32
+// and rounded once.
+template <bool kPacked>
+__device__ __forceinline__ uint4 blend8(const uint4 &w, const uint4 &q0, const uint4 &q1,
+                                        const uint4 &q2, const uint4 &q3) {
+  uint4 o;
+  if constexpr (kPacked) {
+    const __nv_bfloat162 w0 = as_bf162(w.x), w1 = as_bf162(w.y), w2 = as_bf162(w.z),
+                         w3 = as_bf162(w.w);
+    const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
+    const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
+    const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
+    const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
+    uint32_t *r = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __nv_bfloat162 t = __hmul2(w0, as_bf162(a0[i]));
+      t = __hfma2(w1, as_bf162(a1[i]), t);
+      t = __hfma2(w2, as_bf162(a2[i]), t);
+      t = __hfma2(w3, as_bf162(a3[i]), t);
+      r[i] = bf162_bits(t);
+    }
+  } else {
+    float acc[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+    unpack_fma(acc, __uint_as_float(w.x), q0);
+    unpack_fma(acc, __uint_as_float(w.y), q1);
+    unpack_fma(acc, __uint_as_float(w.z), q2);
+    unpack_fma(acc, __uint_as_float(w.w), q3);
+    __nv_bfloat162 *oh2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  }
+  return o;
+}
+
+constexpr int kRowInvalid = INT_MIN;
+
 struct SmemLayout {
   uint8_t *a, *b;
-  float4 *tab_w;
-  int *tab_base;
-  int *row_n, *row_h, *row_w, *row_pix;
+  uint4 *tab_w;        // four corner weights per (tap, deform group, row)
+  uint32_t *tab_off;   // byte offset of the top-left corner from the sample's base
+  int *row_h, *row_w, *row_pix;
   uint64_t *bars;
   uint32_t *tmem_slot;
   int *abort_flag;
@@ -184,9 +278,8 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
   uint8_t *p = base;
   L.a = p; p += (size_t)tp.a_stages * kAStageBytes;
   L.b = p; p += (size_t)tp.b_stages * tp.BN * 128;
-  L.tab_w = (float4 *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(float4);
-  L.tab_base = (int *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(int);
-  L.row_n = (int *)p; p += kBM * sizeof(int);
+  L.tab_w = (uint4 *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint4);
+  L.tab_off = (uint32_t *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint32_t);
   L.row_h = (int *)p; p += kBM * sizeof(int);
   L.row_w = (int *)p; p += kBM * sizeof(int);
   L.row_pix = (int *)p; p += kBM * sizeof(int);
@@ -201,15 +294,38 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
 size_t tc_smem_bytes(const TcPlan &tp, int T) {
   size_t s = 1024;  // slack for manual 1024-byte alignment
   s += (size_t)tp.a_stages * kAStageBytes + (size_t)tp.b_stages * tp.BN * 128;
-  s += (size_t)T * tp.ndgc * kBM * (sizeof(float4) + sizeof(int));
-  s += 4 * kBM * sizeof(int);
+  s += (size_t)T * tp.ndgc * kBM * (sizeof(uint4) + sizeof(uint32_t));
+  s += 3 * kBM * sizeof(int);
   s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t) + 16;
   return s;
 }
 
-template <typename TIO>
-__global__ void __launch_bounds__(kTcThreads, 1)
+// Tile geometry: a tile is TH x TW output pixels of ONE sample (TH*TW = 128, TW a power of
+// two); tile row r is pixel (r / TW, r % TW) of the tile.
+struct TileId {
+  int n, ho0, wo0, grp, nt;
+};
+__device__ __forceinline__ TileId decode_item(long long item, const Geom &g, const TcPlan &tp) {
+  const int per_mt = g.groups * tp.NT;
+  const long long mt = item / per_mt;
+  const int rem = (int)(item - mt * per_mt);
+  const int tiles_img = tp.tiles_x * tp.tiles_y;
+  TileId t;
+  t.n = (int)(mt / tiles_img);
+  const int ti = (int)(mt - (long long)t.n * tiles_img);
+  const int ty = ti / tp.tiles_x;
+  t.ho0 = ty * (kBM >> tp.tw_log2);
+  t.wo0 = (ti - ty * tp.tiles_x) << tp.tw_log2;
+  t.grp = rem / tp.NT;
+  t.nt = rem - t.grp * tp.NT;
+  return t;
+}
+
+template <typename TIO, bool kPacked, int NPW>
+__global__ void __launch_bounds__((kFirstProducerWarp + NPW) * 32, 1)
 dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
+  constexpr int kProdThreads = NPW * 32;
+  constexpr int kGroups = NPW / 8;  // producer groups; group i fills k-stages i, i+G, ...
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const Geom &g = a.g;
@@ -227,7 +343,7 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < A; ++i) {
-      mbar_init(full_a + 8 * i, kTcProducerWarps);
+      mbar_init(full_a + 8 * i, 8);  // the eight warps of one producer group
       mbar_init(empty_a + 8 * i, 1);
     }
     for (int i = 0; i < B; ++i) {
@@ -238,7 +354,7 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
       mbar_init(tmem_full + 8 * i, 1);
       mbar_init(tmem_empty + 8 * i, kEpilogueWarps);
     }
-    mbar_init(prod_bar, kProducerThreads);
+    mbar_init(prod_bar, kProdThreads);
     *L.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -252,31 +368,29 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
   const uint32_t tmem_base = *L.tmem_slot;
 
   const long long items = tp.items;
-  const int per_mt = g.groups * tp.NT;
   const long long plane = (long long)g.Ho * g.Wo;
+  const int tw_mask = (1 << tp.tw_log2) - 1;
 
   if (warp < kEpilogueWarps) {
     // ------------------------------ epilogue ------------------------------
     TIO *out = (TIO *)a.output;
     const TIO *bias = (const TIO *)a.bias;
     const int row = warp * 32 + lane;
+    const int ty = row >> tp.tw_log2, tx = row & tw_mask;
+    PhaseTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     long long li = 0;
     for (long long item = blockIdx.x; item < items; item += gridDim.x, ++li) {
-      const long long mt = item / per_mt;
-      const int rem = (int)(item % per_mt);
-      const int grp = rem / tp.NT, nt = rem % tp.NT;
+      const TileId t = decode_item(item, g, tp);
       const int buf = (int)(li & 1);
       const uint32_t par = (uint32_t)((li >> 1) & 1);
-      const long long p = mt * kBM + row;
-      const bool valid = p < g.P;
-      long long obase = 0;
-      if (valid) {
-        const long long n = p / plane;
-        obase = n * g.out_sn + (p - n * plane);
-      }
-      const int ncols = min(tp.BN, g.Cog - nt * tp.BN);
-      const int co0 = grp * g.Cog + nt * tp.BN;
+      const int ho = t.ho0 + ty, wo = t.wo0 + tx;
+      const bool valid = ho < g.Ho && wo < g.Wo;
+      const long long obase = (long long)t.n * g.out_sn + (long long)ho * g.Wo + wo;
+      const int ncols = min(tp.BN, g.Cog - t.nt * tp.BN);
+      const int co0 = t.grp * g.Cog + t.nt * tp.BN;
+      pt.lap(13);
       if (!mbar_wait(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
+      pt.lap(12);
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t)(buf * tp.BN) + ((uint32_t)(warp * 32) << 16);
       for (int c0 = 0; c0 < ncols; c0 += 32) {
@@ -306,18 +420,24 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
       uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
       long long li = 0;
       bool ok = true;
+      PhaseTimer pt(a.counters, blockIdx.x == 0);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++li) {
         const int buf = (int)(li & 1);
         const uint32_t par = (uint32_t)((li >> 1) & 1);
+        pt.lap(11);
         ok = mbar_wait(tmem_empty + 8 * buf, par ^ 1u, abort_s, a.status, 4);
         if (!ok) break;
+        pt.lap(10);
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * tp.BN);
         for (int ks = 0; ks < tp.S; ++ks) {
+          pt.lap(11);
           ok = mbar_wait(full_b + 8 * sb, pb, abort_s, a.status, 5);
           if (!ok) break;
+          pt.lap(8);
           ok = mbar_wait(full_a + 8 * sa, pa, abort_s, a.status, 6);
           if (!ok) break;
+          pt.lap(9);
           tc_fence_after();
           const uint64_t adesc = smem_desc_sw128(smem_u32(L.a + (size_t)sa * kAStageBytes));
           const uint64_t bdesc = smem_desc_sw128(smem_u32(L.b + (size_t)sb * b_stage_bytes));
@@ -338,14 +458,18 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
   } else if (warp == kLoadWarp) {
     // ------------------------------ weight loader ------------------------------
     if (lane == 0) {
+      const int per_mt = g.groups * tp.NT;
       uint32_t sb = 0, pb = 0;
       bool ok = true;
+      PhaseTimer pt(a.counters, blockIdx.x == 0);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int rem = (int)(item % per_mt);
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
         for (int ks = 0; ks < tp.S; ++ks) {
+          pt.lap(15);
           ok = mbar_wait(empty_b + 8 * sb, pb ^ 1u, abort_s, a.status, 7);
           if (!ok) break;
+          pt.lap(14);
           mbar_arrive_expect_tx(full_b + 8 * sb, b_stage_bytes);
           bulk_copy_g2s(smem_u32(L.b + (size_t)sb * b_stage_bytes),
                         src + (size_t)ks * b_stage_bytes, b_stage_bytes, full_b + 8 * sb);
@@ -358,13 +482,20 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
     // ------------------------------ producers ------------------------------
     const int ptid = threadIdx.x - kFirstProducerWarp * 32;
     const int pw = ptid >> 5;
-    const int sub = lane >> 3;  // row within the warp's group of four
-    const int v = lane & 7;     // 16-byte vector (8 channels) within the 128-byte row
+    const int gi = pw >> 3;      // producer group
+    const int pwl = pw & 7;      // warp within the group
+    const int sub = lane >> 3;   // row within the warp's group of four
+    const int v = lane & 7;      // 16-byte vector (8 channels) within the 128-byte row
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
-    const long long img = (long long)g.H * g.W;
-    const long long cW = (long long)g.C, cH = (long long)g.W * g.C;
-    uint32_t sa = 0, pa = 0, pp = 0;
+    const uint32_t cW2 = (uint32_t)g.C * 2u, cH2 = (uint32_t)g.W * (uint32_t)g.C * 2u;
+    // this thread's four rows of a stage and where their 16 bytes go (128-byte swizzle)
+    const int row0 = pwl * 4 + sub;
+    const uint32_t soff0 = (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
+    // rows whose tap entries this thread computes when a table is rebuilt
+    const int trow = ptid & (kBM - 1);
+    const int tpart = ptid >> 7, tparts = kProdThreads >> 7;
+    uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = 0, pp = 0;
     bool ok = true;
     // Producer-only rendezvous on an mbarrier, so that it is bounded like every other wait.
     auto psync = [&]() -> bool {
@@ -373,111 +504,186 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
       pp ^= 1u;
       return r;
     };
+    uint32_t tcount = 0;  // global k-stage counter of this CTA (same in every producer)
+    PhaseTimer pt(a.counters, blockIdx.x == 0 && ptid == 0);
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
-      const long long mt = item / per_mt;
-      const int grp = (int)(item % per_mt) / tp.NT;
+      const TileId t = decode_item(item, g, tp);
       // all producers are done with the previous tile's tables before they are rebuilt
+      pt.lap(0);
       if (!(ok = psync())) break;
+      pt.lap(2);
       if (ptid < kBM) {
-        const long long p = mt * kBM + ptid;
-        int n = -1, hb = 0, wb = 0, pix = 0;
-        if (p < g.P) {
-          n = (int)(p / plane);
-          pix = (int)(p - (long long)n * plane);
-          const int ho = pix / g.Wo, wo = pix - ho * g.Wo;
-          hb = ho * g.stride_h - g.pad_h;
-          wb = wo * g.stride_w - g.pad_w;
-        }
-        L.row_n[ptid] = n;
-        L.row_h[ptid] = hb;
-        L.row_w[ptid] = wb;
-        L.row_pix[ptid] = pix;
+        const int ho = t.ho0 + (ptid >> tp.tw_log2), wo = t.wo0 + (ptid & tw_mask);
+        const bool valid = ho < g.Ho && wo < g.Wo;
+        L.row_h[ptid] = valid ? ho * g.stride_h - g.pad_h : kRowInvalid;
+        L.row_w[ptid] = wo * g.stride_w - g.pad_w;
+        L.row_pix[ptid] = valid ? ho * g.Wo + wo : 0;
       }
+      pt.lap(0);
       if (!(ok = psync())) break;
+      pt.lap(2);
+      // Ask L2 for the offsets and masks of the tile after this one (of this one too, the
+      // first time): the tap tables are built from them and would otherwise wait on DRAM.
+      for (long long nitem = (item == (long long)blockIdx.x ? item : item + gridDim.x);
+           nitem <= item + gridDim.x && nitem < items; nitem += gridDim.x) {
+        const TileId nt_ = decode_item(nitem, g, tp);
+        const int th = kBM >> tp.tw_log2;
+        const int lines_row = ((int)sizeof(TIO) << tp.tw_log2) + 127 >> 7;  // 128-byte lines per tile row
+        const int planes_off = off ? g.dg * 2 * g.T : 0;
+        const int planes = planes_off + (msk ? g.dg * g.T : 0);
+        const int per_plane = th * lines_row;
+        for (int idx = ptid; idx < planes * per_plane; idx += kProdThreads) {
+          const int pl = idx / per_plane, r = idx - pl * per_plane;
+          const int ry = r / lines_row, rl = r - ry * lines_row;
+          const int ho = nt_.ho0 + ry;
+          if (ho >= g.Ho) continue;
+          const long long pixel = (long long)ho * g.Wo + nt_.wo0;
+          const TIO *ptr = pl < planes_off
+                               ? off + (long long)nt_.n * g.off_sn + (long long)pl * plane + pixel
+                               : msk + (long long)nt_.n * g.msk_sn + (long long)(pl - planes_off) * plane + pixel;
+          if (nt_.wo0 + rl * (int)(128 / sizeof(TIO)) < g.Wo)
+            prefetch_l2(reinterpret_cast<const char *>(ptr) + rl * 128);
+        }
+      }
+      pt.lap(17);
+      const char *xb = reinterpret_cast<const char *>(a.xcl + (long long)t.n * g.H * g.W * g.C);
       int cur_lo = -1, cur_nd = 0;
       for (int cc = 0; cc < tp.KC && ok; ++cc) {
-        const int c0 = grp * g.Cg + cc * kBK;
+        const int c0 = t.grp * g.Cg + cc * kBK;
         const int dg_lo = c0 / g.cpdg;
         const int dg_hi = min(g.dg - 1, (c0 + kBK - 1) / g.cpdg);
         const int nd = dg_hi - dg_lo + 1;
         if (dg_lo != cur_lo || nd != cur_nd) {
+          pt.lap(0);
           if (cur_lo >= 0 && !(ok = psync())) break;
-          const int entries = g.T * nd * kBM;
-          for (int e = ptid; e < entries; e += kProducerThreads) {
-            const int row = e & (kBM - 1);
-            const int q = e >> 7;
-            const int dgl = q % nd, tap = q / nd;
-            const int n = L.row_n[row];
-            float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
-            int base = 0;
-            if (n >= 0) {
-              const int pix = L.row_pix[row];
-              const int i = tap / g.kw, j = tap - i * g.kw;
-              float oh = 0.f, ow = 0.f, m = 1.f;
-              if (off) {
-                const TIO *o = off + (long long)n * g.off_sn +
-                               ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap) * plane + pix;
-                oh = ld_as_float(o, 0);
-                ow = ld_as_float(o, plane);
+          pt.lap(2);
+          pt.count(6);
+          {
+            // Each thread fills the entries e = tpart, tpart + tparts, ... of its row.  The
+            // offset/mask loads of a batch of entries are all issued before any is used, so
+            // their DRAM latency overlaps.
+            const int hb = L.row_h[trow], wb = L.row_w[trow], pix = L.row_pix[trow];
+            const bool rvalid = hb != kRowInvalid;
+            const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
+            const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
+            const int total = g.T * nd;
+            constexpr int kEnt = NPW == 8 ? 9 : 5;  // entries in flight per thread
+            int tap = 0, dgl = tpart, ti = 0, tj = 0;  // entry e <-> (tap, dgl), tap <-> (ti, tj)
+            auto normalise = [&]() {
+              while (dgl >= nd) {
+                dgl -= nd;
+                ++tap;
+                if (++tj == g.kw) { tj = 0; ++ti; }
               }
-              if (msk)
-                m = ld_as_float(msk, (long long)n * g.msk_sn +
-                                         ((long long)(dg_lo + dgl) * g.T + tap) * plane + pix);
-              int h_low, w_low;
-              tap_weights(oh, ow, m, L.row_h[row] + i * g.dil_h, L.row_w[row] + j * g.dil_w,
-                          g.H, g.W, wt, h_low, w_low);
-              base = (int)((long long)n * img) + h_low * g.W + w_low;
+            };
+            normalise();
+            for (int e0 = tpart; e0 < total; e0 += tparts * kEnt) {
+              typename RawOf<TIO>::type oh[kEnt], ow[kEnt], mm[kEnt];  // raw element bits
+              int where[kEnt];
+#pragma unroll
+              for (int k = 0; k < kEnt; ++k) {
+                oh[k] = 0; ow[k] = 0; mm[k] = 0;
+                where[k] = -1;
+                if (e0 + k * tparts < total) {
+                  where[k] = tap | (dgl << 12) | (ti << 16) | (tj << 24);
+                  if (rvalid) {
+                    if (offp) {
+                      const long long ch = ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap) * plane;
+                      oh[k] = ldg_raw_ordered(offp + ch);
+                      ow[k] = ldg_raw_ordered(offp + ch + plane);
+                    }
+                    if (mskp)
+                      mm[k] = ldg_raw_ordered(mskp + ((long long)(dg_lo + dgl) * g.T + tap) * plane);
+                  }
+                  dgl += tparts;
+                  normalise();
+                }
+              }
+              asm volatile("" ::: "memory");  // every load of the batch is issued before this
+              pt.lap(16);
+#pragma unroll
+              for (int k = 0; k < kEnt; ++k) {
+                if (where[k] < 0) continue;
+                const int etap = where[k] & 0xfff, edgl = (where[k] >> 12) & 0xf;
+                const int ei = (where[k] >> 16) & 0xff, ej = (where[k] >> 24) & 0xff;
+                float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
+                int h_low = 0, w_low = 0;
+                if (rvalid)
+                  tap_weights(raw_to_float(oh[k]), raw_to_float(ow[k]),
+                              mskp ? raw_to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
+                              wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
+                uint4 wq;
+                if constexpr (kPacked) {
+                  wq.x = bf162_bits(__float2bfloat162_rn(wt.x));
+                  wq.y = bf162_bits(__float2bfloat162_rn(wt.y));
+                  wq.z = bf162_bits(__float2bfloat162_rn(wt.z));
+                  wq.w = bf162_bits(__float2bfloat162_rn(wt.w));
+                  // a weight that rounds to (signed) zero is dropped: the corner is not read
+                  wq.x = (wq.x & 0x7fff7fffu) ? wq.x : 0u;
+                  wq.y = (wq.y & 0x7fff7fffu) ? wq.y : 0u;
+                  wq.z = (wq.z & 0x7fff7fffu) ? wq.z : 0u;
+                  wq.w = (wq.w & 0x7fff7fffu) ? wq.w : 0u;
+                } else {
+                  wq.x = wt.x == 0.f ? 0u : __float_as_uint(wt.x);
+                  wq.y = wt.y == 0.f ? 0u : __float_as_uint(wt.y);
+                  wq.z = wt.z == 0.f ? 0u : __float_as_uint(wt.z);
+                  wq.w = wt.w == 0.f ? 0u : __float_as_uint(wt.w);
+                }
+                const int slot = (etap * tp.ndgc + edgl) * kBM + trow;
+                L.tab_w[slot] = wq;
+                L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * 2);
+              }
             }
-            const int slot = (tap * tp.ndgc + dgl) * kBM + row;
-            L.tab_w[slot] = wt;
-            L.tab_base[slot] = base;
           }
+          pt.lap(1);
           if (!(ok = psync())) break;
+          pt.lap(2);
           cur_lo = dg_lo;
           cur_nd = nd;
         }
         const int c = c0 + v * 8;
         const int dgl = c / g.cpdg - dg_lo;
-        const __nv_bfloat16 *xc = a.xcl + c;
-        for (int tap = 0; tap < g.T; ++tap) {
-          ok = mbar_wait(empty_a + 8 * sa, pa ^ 1u, abort_s, a.status, 8);
+        const uint32_t c2 = (uint32_t)c * 2u;
+        for (int tap = 0; tap < g.T; ++tap, ++tcount) {
+          if (kGroups > 1 && (int)(tcount % kGroups) != gi) continue;
+          pt.lap(0);
+          pt.count(5);
+          uint8_t *stage = L.a + (size_t)sa * kAStageBytes + soff0;
+          const int slot0 = (tap * tp.ndgc + dgl) * kBM + row0;
+          const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+          // kBatch rows of this thread are in flight at a time (four 16-byte loads each)
+          constexpr int kBatch = NPW == 8 ? 4 : 2;
+#pragma unroll
+          for (int p0 = 0; p0 < 4; p0 += kBatch) {
+            uint4 q[kBatch][4], wq[kBatch];
+#pragma unroll
+            for (int ps = 0; ps < kBatch; ++ps) {
+              wq[ps] = L.tab_w[slot0 + (p0 + ps) * 32];
+              const uint32_t o = L.tab_off[slot0 + (p0 + ps) * 32] + c2;
+              q[ps][0] = wq[ps].x ? __ldg((const uint4 *)(xb + o)) : z;
+              q[ps][1] = wq[ps].y ? __ldg((const uint4 *)(xb + (uint32_t)(o + cW2))) : z;
+              q[ps][2] = wq[ps].z ? __ldg((const uint4 *)(xb + (uint32_t)(o + cH2))) : z;
+              q[ps][3] = wq[ps].w ? __ldg((const uint4 *)(xb + (uint32_t)(o + cH2 + cW2))) : z;
+            }
+            if (p0 == 0) {
+              // the stage must be free only now, with this batch's loads already in flight
+              pt.lap(4);
+              ok = mbar_wait(empty_a + 8 * sa, pa ^ 1u, abort_s, a.status, 8);
+              pt.lap(3);
+            }
+#pragma unroll
+            for (int ps = 0; ps < kBatch; ++ps)
+              *reinterpret_cast<uint4 *>(stage + (p0 + ps) * 32 * 128) =
+                  blend8<kPacked>(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
+          }
           if (!ok) break;
-          uint8_t *stage = L.a + (size_t)sa * kAStageBytes;
-          const int slot0 = (tap * tp.ndgc + dgl) * kBM;
-          uint4 q[4][4];
-          float4 wts[4];
-#pragma unroll
-          for (int ps = 0; ps < 4; ++ps) {
-            const int row = ps * 32 + pw * 4 + sub;
-            const float4 wt = L.tab_w[slot0 + row];
-            const long long e0 = (long long)L.tab_base[slot0 + row] * cW;
-            const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-            q[ps][0] = wt.x != 0.f ? __ldg((const uint4 *)(xc + e0)) : z;
-            q[ps][1] = wt.y != 0.f ? __ldg((const uint4 *)(xc + e0 + cW)) : z;
-            q[ps][2] = wt.z != 0.f ? __ldg((const uint4 *)(xc + e0 + cH)) : z;
-            q[ps][3] = wt.w != 0.f ? __ldg((const uint4 *)(xc + e0 + cH + cW)) : z;
-            wts[ps] = wt;
-          }
-#pragma unroll
-          for (int ps = 0; ps < 4; ++ps) {
-            const int row = ps * 32 + pw * 4 + sub;
-            float acc[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-            unpack_fma(acc, wts[ps].x, q[ps][0]);
-            unpack_fma(acc, wts[ps].y, q[ps][1]);
-            unpack_fma(acc, wts[ps].z, q[ps][2]);
-            unpack_fma(acc, wts[ps].w, q[ps][3]);
-            uint4 o;
-            __nv_bfloat162 *oh2 = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) oh2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-            *reinterpret_cast<uint4 *>(stage + row * 128 + ((v ^ (row & 7)) << 4)) = o;
-          }
+          pt.lap(4);
           fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive(full_a + 8 * sa);
-          if (++sa == (uint32_t)A) { sa = 0; pa ^= 1u; }
+          pt.lap(7);
+          sa += (uint32_t)kGroups;
+          if (sa >= (uint32_t)A) { sa -= (uint32_t)A; pa ^= 1u; }
         }
       }
     }
@@ -584,24 +790,54 @@ cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *wei
   return cudaGetLastError();
 }
 
-__global__ void dcn_clear_status(int *status) { *status = 0; }
+__global__ void dcn_clear_status(int *status) {
+  // the whole 256-byte workspace header: status word and the optional phase counters
+  status[threadIdx.x] = 0;
+}
 
 cudaError_t launch_clear_status(int *status, cudaStream_t s) {
-  dcn_clear_status<<<1, 1, 0, s>>>(status);
+  dcn_clear_status<<<1, 64, 0, s>>>(status);
   return cudaGetLastError();
 }
 
-cudaError_t tc_set_attributes(size_t smem) {
-  cudaError_t e = cudaFuncSetAttribute(dcn_fwd_tc_bf16<float>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+namespace {
+template <typename TIO, bool kPacked, int NPW>
+cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
+  auto kern = dcn_fwd_tc_bf16<TIO, kPacked, NPW>;
+  // opt in to large dynamic shared memory once per device and instantiation
+  static std::atomic<unsigned long long> done_mask{0};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(dcn_fwd_tc_bf16<__nv_bfloat16>,
-                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const unsigned long long bit = 1ull << (dev & 63);
+  if (!(done_mask.load(std::memory_order_acquire) & bit)) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448);
+    if (e != cudaSuccess) return e;
+    done_mask.fetch_or(bit, std::memory_order_release);
+  }
+  // leave what the kernel does not need of the SM's 256 KB to L1: the gather lives on it
+  static std::atomic<int> carve_pct[64];
+  const int pct = (int)((tp.smem + 1024) * 100 / 233472) + 1;
+  if (carve_pct[dev & 63].load(std::memory_order_acquire) != pct) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             pct > 100 ? 100 : pct);
+    if (e != cudaSuccess) return e;
+    carve_pct[dev & 63].store(pct, std::memory_order_release);
+  }
+  kern<<<tp.grid, (kFirstProducerWarp + NPW) * 32, tp.smem, s>>>(a);
+  return cudaGetLastError();
 }
+template <typename TIO>
+cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
+  if (tp.producer_warps == 16)
+    return tp.blend_packed ? launch_one<TIO, true, 16>(a, tp, s) : launch_one<TIO, false, 16>(a, tp, s);
+  return tp.blend_packed ? launch_one<TIO, true, 8>(a, tp, s) : launch_one<TIO, false, 8>(a, tp, s);
+}
+}  // namespace
 
 cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
                            const __nv_bfloat16 *xcl, const void *wtiles, int *status,
-                           cudaStream_t s) {
+                           unsigned long long *counters, cudaStream_t s) {
   if (tp.items == 0) return cudaSuccess;
   TcArgs a;
   a.g = g;
@@ -613,11 +849,8 @@ cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int d
   a.bias = p.bias;
   a.output = p.output;
   a.status = status;
-  if (dtype == DCN_DTYPE_F32)
-    dcn_fwd_tc_bf16<float><<<tp.grid, kTcThreads, tp.smem, s>>>(a);
-  else
-    dcn_fwd_tc_bf16<__nv_bfloat16><<<tp.grid, kTcThreads, tp.smem, s>>>(a);
-  return cudaGetLastError();
+  a.counters = counters;
+  return dtype == DCN_DTYPE_F32 ? launch_io<float>(a, tp, s) : launch_io<__nv_bfloat16>(a, tp, s);
 }
 
 }  // namespace dcn
