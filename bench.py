@@ -167,6 +167,147 @@ def cpu_reference_sample(wl, seconds_budget=20.0, max_reps=3):
                 seconds_per_call=best, pixels_per_s=n * Ho * Wo / best)
 
 
+C4_LAYERS = [  # (count, C, H, W): the 13 deformable 3x3 convs of ResNet-50-DCNv2 stages 3-5
+    (4, 128, 168, 100), (6, 256, 84, 50), (3, 512, 42, 25)]
+C4_BATCH = 16
+
+
+def c4_work(n):
+    fl = by = 0.0
+    for cnt, C, H, W in C4_LAYERS:
+        dcn = 2.0 * n * C * H * W * C * 9
+        off = 2.0 * n * 27 * H * W * C * 9
+        b_dcn = 2 * (n * C * H * W * 2 + n * 27 * H * W + C * C * 9 + C)
+        b_off = 2 * (n * C * H * W + 27 * C * 9 + 27 + n * 27 * H * W)
+        fl += cnt * (dcn + off)
+        by += cnt * (b_dcn + b_off)
+    return fl, by
+
+
+def run_c4(args, rank, world, local):
+    """13-layer stack through ModulatedDeformConv2dPack, bf16, N=16 (batch-sharded)."""
+    import torch.distributed as dist
+    from mmcv_b200.ops import ModulatedDeformConv2dPack
+    from mmcv_b200.shard import batch_shard
+    torch.cuda.set_device(local)
+    dev = torch.device('cuda', local)
+    if world > 1:
+        os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
+        dist.init_process_group('nccl', device_id=dev)
+    n_total = args.batch or C4_BATCH
+    n0, n1 = batch_shard(n_total, rank, world)
+    n = n1 - n0
+    torch.manual_seed(0)
+    layers, inputs = [], []
+    for cnt, C, H, W in C4_LAYERS:
+        for _ in range(cnt):
+            m = ModulatedDeformConv2dPack(C, C, 3, padding=1, deform_groups=1, bias=True)
+            m.conv_offset.weight.data.normal_(0, 0.01)
+            layers.append(m.to(dev, torch.bfloat16).eval())
+            gen = torch.Generator(device=dev).manual_seed(len(layers) * 1000 + n0)
+            inputs.append(torch.relu(torch.randn(n, C, H, W, device=dev, generator=gen)).to(torch.bfloat16))
+    stream = torch.cuda.current_stream(dev)
+
+    def step():
+        with torch.no_grad():
+            for m, x in zip(layers, inputs):
+                m(x)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    barrier()
+    ms = e0.elapsed_time(e1) / args.steps
+    clocks = sampler.stop() if sampler else None
+    # per stage kind, one layer timed alone (events around a single layer call)
+    per_kind, idx = {}, 0
+    for cnt, C, H, W in C4_LAYERS:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.no_grad():
+            layers[idx](inputs[idx])
+            a.record(stream)
+            for _ in range(5):
+                layers[idx](inputs[idx])
+            b.record(stream)
+        torch.cuda.synchronize(dev)
+        per_kind[f'C{C}_{H}x{W}'] = a.elapsed_time(b) / 5
+        idx += cnt
+    # end to end: host inputs in, last layer's output out, every step
+    hin = [x.cpu().pin_memory() for x in inputs]
+    hout = torch.empty(inputs[-1].shape, dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+        with torch.no_grad():
+            y = None
+            for m, hx in zip(layers, hin):
+                y = m(hx.to(dev, non_blocking=True))
+            hout.copy_(y, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for _ in range(max(1, min(args.e2e_steps, args.steps))):
+        e2e_step()
+    f1.record(stream)
+    barrier()
+    e2e_ms = f0.elapsed_time(f1) / max(1, min(args.e2e_steps, args.steps))
+    t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+    if rank == 0:
+        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))) if os.path.exists(
+            os.path.join(ROOT, 'MEASURED_PEAKS.json')) else {}
+        peak_tf, hbm = peaks.get('bf16_tflops', 1590.0), peaks.get('hbm_gbs', 6650.0)
+        fl, by = c4_work(n_total)
+        fl_r, _ = c4_work(n)
+        roof = 0.0
+        for cnt, C, H, W in C4_LAYERS:
+            dcn = 2.0 * n * C * H * W * C * 9
+            off = 2.0 * n * 27 * H * W * C * 9
+            b_dcn = 2 * (n * C * H * W * 2 + n * 27 * H * W + C * C * 9 + C)
+            b_off = 2 * (n * C * H * W + 27 * C * 9 + 27 + n * 27 * H * W)
+            roof += cnt * (max(dcn / (peak_tf * 1e12), b_dcn / (hbm * 1e9)) +
+                           max(off / (peak_tf * 1e12), b_off / (hbm * 1e9)))
+        line = dict(
+            metric='dcnv2_fwd_tflops', value=fl / (ms * 1e-3) / 1e12, unit='TFLOP/s', n_gpus=world,
+            steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True,
+            scaling='strong', vs_baseline=None, dtype='bf16', data='synthetic',
+            config=dict(workload='c4: 13 ModulatedDeformConv2dPack layers (ResNet-50-DCNv2 stages '
+                                 '3-5), N=16, bf16, offset branch on the same kernel',
+                        global_batch=n_total, parallelism=f'batch-shard x{world}, no collective',
+                        l2='layer inputs 53-107 MB each, 13 distinct tensors per step (> L2)'),
+            layer_roofline=dict(ms=roof * 1e3, frac=roof * 1e3 / ms if world == 1 else None,
+                                flops=fl_r, note='sum over the 26 launches of max(FLOPs at bf16 '
+                                                 'peak, compulsory bytes at HBM bandwidth)'),
+            per_layer_ms=per_kind,
+            roofline=dict(bound='tensor', achieved=fl_r / (ms * 1e-3) / 1e12, peak=peak_tf,
+                          unit='TFLOP/s', frac=fl_r / (ms * 1e-3) / 1e12 / peak_tf, traffic=None,
+                          kernel='dcn_fwd_tc_bf16 (whole stack incl. restaging and weight tiling)'),
+            e2e=dict(value=fl / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
+                     h2d_bytes_per_step=sum(h.numel() * 2 for h in hin),
+                     d2h_bytes_per_step=hout.numel() * 2, ms_per_step=e2e_ms,
+                     api='mmcv_b200.ops.ModulatedDeformConv2dPack'),
+            gpu_launches=args.steps * 13 * 8, clocks=clocks)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def run_reference(args, wl, rank, world):
     if rank != 0:
         return
@@ -206,12 +347,20 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c5', choices=sorted(WORKLOADS))
+    ap.add_argument('--workload', default='c5', choices=sorted(WORKLOADS) + ['c4'])
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+    if args.workload == 'c4':
+        if args.impl == 'reference':
+            raise SystemExit('the reference arm is quoted on the single-layer workloads')
+        if not torch.cuda.is_available():
+            raise SystemExit('bench.py needs a CUDA device: there is no CPU path')
+        run_c4(args, int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1')),
+               int(os.environ.get('LOCAL_RANK', '0')))
+        return
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
         wl['N'] = args.batch

@@ -108,6 +108,17 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     return ws
 
 
+def _per_sample(t):
+    """(tensor, batch stride in elements) for a tensor whose samples are each contiguous;
+    a channel slice of a larger NCHW tensor qualifies and is passed without a copy."""
+    if t.dim() == 4 and t.size(0) > 0:
+        st, sh = t.stride(), t.shape
+        if st[3] == 1 and st[2] == sh[3] and st[1] == sh[2] * sh[3] and st[0] >= sh[1] * st[1]:
+            return t, st[0]
+    t = t.contiguous()
+    return t, 0
+
+
 def _input_layout(x):
     if x.is_contiguous() or x.is_contiguous(memory_format=torch.channels_last):
         return x
@@ -131,9 +142,11 @@ def modulated_deform_conv_forward(input, weight, bias, ones, offset, mask, outpu
     b = bias.contiguous() if (with_bias and bias is not None and bias.numel() > 0) else None
     if with_bias and b is None:
         raise RuntimeError('dcn_b200: with_bias is set but bias is empty')
-    forward(_input_layout(input), offset.contiguous(), mask.contiguous(), weight.contiguous(), b,
-            output, (stride_h, stride_w), (pad_h, pad_w), (dilation_h, dilation_w), group,
-            deformable_group)
+    offset, off_bs = _per_sample(offset)
+    mask, msk_bs = _per_sample(mask)
+    forward(_input_layout(input), offset, mask, weight.contiguous(), b, output,
+            (stride_h, stride_w), (pad_h, pad_w), (dilation_h, dilation_w), group,
+            deformable_group, offset_batch_stride=off_bs, mask_batch_stride=msk_bs)
 
 
 def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW, dH, padW,
@@ -177,6 +190,22 @@ def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW
         raise RuntimeError('batch size must be divisible by im2col_step')
     forward(input, offset, None, weight, None, output, (dH, dW), (padH, padW),
             (dilationH, dilationW), group, deformable_group)
+
+
+def conv_offset_forward(x, weight, bias, stride, padding, dilation, sigmoid_from=None):
+    """The offset(/mask) branch of the Pack layers as an ordinary convolution on the same
+    implicit-GEMM kernel (zero offsets, unit mask), with the sigmoid of the mask channels
+    [sigmoid_from, Cout) fused into the epilogue.  Returns [N, Cout, Ho, Wo]."""
+    kh, kw = weight.shape[2], weight.shape[3]
+    ho = (x.size(2) + 2 * padding[0] - (dilation[0] * (kh - 1) + 1)) // stride[0] + 1
+    wo = (x.size(3) + 2 * padding[1] - (dilation[1] * (kw - 1) + 1)) // stride[1] + 1
+    out = x.new_empty((x.size(0), weight.size(0), ho, wo))
+    act = _lib.ACT_SIGMOID if sigmoid_from is not None else _lib.ACT_NONE
+    rng = (sigmoid_from, weight.size(0)) if sigmoid_from is not None else (0, 0)
+    forward(_input_layout(x), None, None, weight.contiguous(),
+            None if bias is None else bias.contiguous(), out, stride, padding, dilation, 1, 1,
+            act=act, act_range=rng)
+    return out
 
 
 def _no_backward(name):

@@ -11,7 +11,8 @@ from torch.autograd import Function
 from torch.nn.modules.utils import _pair, _single
 
 from .. import _ext as ext_module
-from .modulated_deform_conv import _rename_kw, _upgrade_offset_keys, conv_output_size
+from .modulated_deform_conv import (_rename_kw, _upgrade_offset_keys, branch_dtype,
+                                    conv_output_size, fused_branch_applies, shared_layout)
 
 
 class DeformConv2dFunction(Function):
@@ -142,7 +143,14 @@ class DeformConv2dPack(DeformConv2d):
         self.conv_offset.bias.data.zero_()
 
     def forward(self, x: Tensor) -> Tensor:  # type: ignore[override]
-        offset = self.conv_offset(x)
+        if fused_branch_applies(x, self.conv_offset):
+            dtype = branch_dtype(x)
+            x = shared_layout(x.to(dtype))
+            offset = ext_module.conv_offset_forward(
+                x, self.conv_offset.weight.to(dtype), self.conv_offset.bias.to(dtype),
+                _pair(self.stride), _pair(self.padding), _pair(self.dilation))
+        else:
+            offset = self.conv_offset(x)
         return deform_conv2d(x, offset, self.weight, self.stride, self.padding, self.dilation,
                              self.groups, self.deform_groups, False, self.im2col_step)
 

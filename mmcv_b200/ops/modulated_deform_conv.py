@@ -76,6 +76,30 @@ class ModulatedDeformConv2dFunction(Function):
 modulated_deform_conv2d = ModulatedDeformConv2dFunction.apply
 
 
+def fused_branch_applies(x, conv):
+    """The offset branch runs on this library's kernel when nothing needs its gradient
+    (inference); otherwise it stays an nn.Conv2d so that autograd sees it."""
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+        return False
+    if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') != torch.bfloat16:
+        return False
+    needs_grad = torch.is_grad_enabled() and (
+        x.requires_grad or any(p.requires_grad for p in conv.parameters()))
+    return not needs_grad
+
+
+def shared_layout(x):
+    """bf16 inputs are put in channels-last order once, so that the offset branch and the
+    deformable convolution both read them without a restaging pass of their own."""
+    if x.dtype == torch.bfloat16 and x.size(1) % 64 == 0:
+        return x.contiguous(memory_format=torch.channels_last)
+    return x
+
+
+def branch_dtype(x):
+    return torch.bfloat16 if torch.is_autocast_enabled('cuda') else x.dtype
+
+
 def _rename_kw(kwargs, old, new):
     if old in kwargs:
         kwargs[new] = kwargs.pop(old)
@@ -151,11 +175,21 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
             self.conv_offset.bias.data.zero_()
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:  # type: ignore[override]
-        out = self.conv_offset(x)
-        two_thirds = out.size(1) // 3 * 2
+        two_thirds = self.conv_offset.out_channels // 3 * 2
         # chunk(3) + cat of the first two chunks == the first two thirds of the channels
-        offset = out[:, :two_thirds].contiguous()
-        mask = torch.sigmoid(out[:, two_thirds:])
+        if fused_branch_applies(x, self.conv_offset):
+            # one launch of the implicit-GEMM kernel: convolution + sigmoid of the mask third;
+            # offset and mask are then channel slices of its output, passed without copies
+            dtype = branch_dtype(x)
+            x = shared_layout(x.to(dtype))
+            out = ext_module.conv_offset_forward(
+                x, self.conv_offset.weight.to(dtype), self.conv_offset.bias.to(dtype),
+                self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
+            offset, mask = out[:, :two_thirds], out[:, two_thirds:]
+        else:
+            out = self.conv_offset(x)
+            offset = out[:, :two_thirds].contiguous()
+            mask = torch.sigmoid(out[:, two_thirds:])
         return modulated_deform_conv2d(x, offset, mask, self.weight, self.bias, self.stride,
                                        self.padding, self.dilation, self.groups,
                                        self.deform_groups)

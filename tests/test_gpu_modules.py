@@ -80,3 +80,58 @@ def test_autocast_dtype_follows_offset():
     y32 = dcn(x)
     assert y32.dtype == torch.float32
     assert rel_l2(y.float().cpu(), y32.detach().cpu()) < 5e-2
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_offset_branch_on_the_same_kernel(dtype):
+    # ordinary convolution through the implicit-GEMM kernel (zero offsets, unit mask),
+    # sigmoid fused on the mask third; checked against F.conv2d in fp32 on the same inputs
+    import torch.nn.functional as F
+    from mmcv_b200 import _ext
+    torch.manual_seed(0)
+    x = torch.relu(torch.randn(2, 128, 21, 19)).to(dtype)
+    w = (torch.randn(27, 128, 3, 3) * 0.01).to(dtype)
+    b = (torch.randn(27) * 0.1).to(dtype)
+    out = _ext.conv_offset_forward(x.cuda(), w.cuda(), b.cuda(), (1, 1), (1, 1), (1, 1),
+                                   sigmoid_from=18).float().cpu()
+    ref = F.conv2d(x.float(), w.float(), b.float(), 1, 1)
+    ref = torch.cat([ref[:, :18], torch.sigmoid(ref[:, 18:])], 1)
+    if dtype == torch.float32:
+        ok, frac = fp32_close(out, ref)
+        assert ok, frac
+    else:
+        assert rel_l2(out, ref) <= 2e-2
+
+
+def test_pack_layers_with_fused_branch():
+    # inference path of the Pack layers: the offset branch runs on this library's kernel and
+    # feeds the deformable convolution through channel slices (no copies).  The branch is
+    # checked against F.conv2d; the layer output against the CPU checker fed the branch's
+    # own (bf16) offsets and mask, which isolates the sampling kernel from branch rounding.
+    import torch.nn.functional as F
+    from mmcv_b200 import _ext
+    from mmcv_b200.ops import DeformConv2dPack, ModulatedDeformConv2dPack
+    torch.manual_seed(0)
+    for cls, dg in ((ModulatedDeformConv2dPack, 2), (DeformConv2dPack, 1)):
+        layer = cls(64, 96, 3, padding=1, deform_groups=dg).cuda().to(torch.bfloat16)
+        layer.conv_offset.weight.data.normal_(0, 0.02)
+        layer.conv_offset.bias.data.normal_(0, 0.1)
+        x = torch.relu(torch.randn(2, 64, 30, 26, device='cuda')).to(torch.bfloat16)
+        modulated = cls is ModulatedDeformConv2dPack
+        k = layer.conv_offset.out_channels // 3 * 2 if modulated else None
+        with torch.no_grad():
+            fused = layer(x).float().cpu()
+            branch = _ext.conv_offset_forward(x, layer.conv_offset.weight, layer.conv_offset.bias,
+                                              (1, 1), (1, 1), (1, 1), sigmoid_from=k).float().cpu()
+        o = F.conv2d(x.float().cpu(), layer.conv_offset.weight.float().cpu(),
+                     layer.conv_offset.bias.float().cpu(), 1, 1)
+        if modulated:
+            o = torch.cat([o[:, :k], torch.sigmoid(o[:, k:])], 1)
+        assert rel_l2(branch, o) <= 2e-2
+        off = branch[:, :k] if modulated else branch
+        msk = branch[:, k:] if modulated else None
+        bias = layer.bias.float().cpu() if modulated else None
+        ref = oracle.best_forward(x.float().cpu(), off.contiguous(),
+                                  None if msk is None else msk.contiguous(),
+                                  layer.weight.float().cpu(), bias, 1, 1, 1, 1, dg)
+        assert rel_l2(fused, ref) <= 2e-2
