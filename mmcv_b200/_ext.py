@@ -159,7 +159,8 @@ def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW
         if not t.is_cuda:
             raise RuntimeError(f'{name} must be a CUDA tensor (this build has no CPU '
                                'implementation)')
-        if not t.is_contiguous():
+        if not t.is_contiguous() and not (
+                name == 'input' and t.is_contiguous(memory_format=torch.channels_last)):
             raise RuntimeError(f'{name} must be contiguous')
     if weight.dim() != 4:
         raise RuntimeError('4D weight tensor (nOutputPlane,nInputPlane,kH,kW) expected, but got: '
