@@ -116,47 +116,61 @@ int build_geom(const DcnFwdParams *p, Geom *g) {
   return DCN_OK;
 }
 
-bool input_is_cl_bf16(const DcnFwdParams *p, const Geom &g) {
-  return p->dtype == DCN_DTYPE_BF16 && g.in_sc == 1 && g.in_sw == g.C &&
+// The input can be gathered from where it lies: channels-last, dense, and already in the
+// element type the mode samples (bf16 for the bf16 contraction, fp32 for TF32x3).
+bool input_is_ready(const DcnFwdParams *p, const Geom &g, bool tf32) {
+  return p->dtype == (tf32 ? DCN_DTYPE_F32 : DCN_DTYPE_BF16) && g.in_sc == 1 && g.in_sw == g.C &&
          g.in_sh == (long long)g.W * g.C && g.in_sn == (long long)g.H * g.W * g.C;
+}
+
+int resolved_math(const DcnFwdParams *p) {
+  return p->math_mode == DCN_MATH_AUTO
+             ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_FFMA)
+             : p->math_mode;
 }
 
 // Decide whether the tensor-core kernel can take the problem and with what tiling.
 bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
-  const int math = p->math_mode == DCN_MATH_AUTO
-                       ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_FFMA)
-                       : p->math_mode;
-  if (math != DCN_MATH_BF16) return false;
-  if (g.Cg % kBK != 0 || g.cpdg % 8 != 0) return false;
+  const int math = resolved_math(p);
+  if (math != DCN_MATH_BF16 && math != DCN_MATH_TF32X3) return false;
+  const bool tf32 = math == DCN_MATH_TF32X3;
+  const int ch = tf32 ? 32 : 64, cpv = tf32 ? 4 : 8;
+  if (g.Cg % ch != 0 || g.cpdg % cpv != 0) return false;
   if ((long long)g.N * g.H * g.W >= 2147483647LL) return false;
-  memset(tp, 0, sizeof(*tp));
-  tp->NT = (g.Cog + 255) / 256;
-  const int per = (g.Cog + tp->NT - 1) / tp->NT;
-  tp->BN = (per + 31) / 32 * 32;
-  tp->KC = g.Cg / kBK;
-  tp->S = tp->KC * g.T;
-  int ndgc = 1;
-  for (int grp = 0; grp < g.groups; ++grp)
-    for (int cc = 0; cc < tp->KC; ++cc) {
-      const int c0 = grp * g.Cg + cc * kBK;
-      const int lo = c0 / g.cpdg, hi = (c0 + kBK - 1) / g.cpdg;
-      const int nd = (hi < g.dg ? hi : g.dg - 1) - lo + 1;
-      if (nd > ndgc) ndgc = nd;
-    }
-  tp->ndgc = ndgc;
-  tp->blend_packed = env_int("DCN_B200_PACKED_BLEND", 1, 0, 1);
-  tp->producer_warps = env_int("DCN_B200_PRODUCER_WARPS", 16, 8, 16) >= 16 ? 16 : 8;
-  int cols = 32;
-  while (cols < 2 * tp->BN) cols *= 2;
-  tp->tmem_cols = cols;
-  // Pipeline depth.  Shared memory the kernel does not take stays L1, and the gather's hit
-  // rate depends on it, so first try to fit the 164 KB shared-memory configuration (92 KB of
-  // L1), deepest A ring first; only then fall back to the largest configuration.
-  {
-    const int a_forced = env_int("DCN_B200_A_STAGES", 0, 0, 8);
-    const int b_forced = env_int("DCN_B200_B_STAGES", 0, 0, 8);
+  if ((long long)g.H * g.W * g.C * (tf32 ? 4 : 2) >= 4294967295LL) return false;
+  if (g.kh > 255 || g.kw > 255 || g.T > 4095) return false;
+  const int a_forced = env_int("DCN_B200_A_STAGES", 0, 0, 8);
+  const int b_forced = env_int("DCN_B200_B_STAGES", 0, 0, 8);
+  // Output channels per tile: as many as fit (fewest passes over the gather); TF32x3 needs
+  // twice the operand memory per stage and may have to halve it.
+  bool found = false;
+  for (int cap = 256; cap >= 32 && !found; cap /= 2) {
+    memset(tp, 0, sizeof(*tp));
+    tp->tiles_per_stage = tf32 ? 2 : 1;
+    tp->ch_per_stage = ch;
+    tp->NT = (g.Cog + cap - 1) / cap;
+    const int per = (g.Cog + tp->NT - 1) / tp->NT;
+    tp->BN = (per + 31) / 32 * 32;
+    tp->KC = g.Cg / ch;
+    tp->S = tp->KC * g.T;
+    int ndgc = 1;
+    for (int grp = 0; grp < g.groups; ++grp)
+      for (int cc = 0; cc < tp->KC; ++cc) {
+        const int c0 = grp * g.Cg + cc * ch;
+        const int lo = c0 / g.cpdg, hi = (c0 + ch - 1) / g.cpdg;
+        const int nd = (hi < g.dg ? hi : g.dg - 1) - lo + 1;
+        if (nd > ndgc) ndgc = nd;
+      }
+    if (ndgc > 15) return false;
+    tp->ndgc = ndgc;
+    tp->producer_warps = env_int("DCN_B200_PRODUCER_WARPS", 16, 8, 16) >= 16 ? 16 : 8;
+    int cols = 32;
+    while (cols < 2 * tp->BN) cols *= 2;
+    tp->tmem_cols = cols;
+    // Pipeline depth.  Shared memory the kernel does not take stays L1, and the gather's hit
+    // rate depends on it, so first try to fit the 164 KB shared-memory configuration (92 KB
+    // of L1), deepest A ring first; only then fall back to the largest configuration.
     const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
-    bool found = false;
     for (int bi = 0; bi < 2 && !found; ++bi)
       for (int as = 4; as >= 2 && !found; --as)
         for (int bs = (bi == 0 ? 2 : 4); bs >= 2 && !found; --bs) {
@@ -166,14 +180,8 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
           tp->smem = tc_smem_bytes(*tp, g.T);
           found = tp->smem <= budgets[bi];
         }
-    if (!found) {
-      if (!a_forced && !b_forced) return false;
-      tp->a_stages = a_forced ? a_forced : 2;
-      tp->b_stages = b_forced ? b_forced : 2;
-      tp->smem = tc_smem_bytes(*tp, g.T);
-      if (tp->smem > kMaxSmemOptin) return false;
-    }
   }
+  if (!found) return false;
   // Tile shape: TH x TW pixels of one sample, TH*TW = 128.  Fewest tiles wins; among
   // shapes within 3 % of the fewest, the one closest to square (smallest sampled footprint).
   int best = -1;
@@ -207,11 +215,11 @@ void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPla
   size_t off = 256;
   if (tc) {
     ws->wtile_off = off;
-    ws->wtile_bytes = (size_t)g.groups * tp.NT * tp.S * tp.BN * 128;
+    ws->wtile_bytes = (size_t)g.groups * tp.NT * tp.S * tp.BN * 128 * tp.tiles_per_stage;
     off = align_up(off + ws->wtile_bytes, 256);
-    if (!input_is_cl_bf16(p, g)) {
+    if (!input_is_ready(p, g, tp.tiles_per_stage == 2)) {
       ws->xcl_off = off;
-      ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * 2;
+      ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * (tp.tiles_per_stage == 2 ? 4 : 2);
       off = align_up(off + ws->xcl_bytes, 256);
     }
   }
@@ -253,13 +261,15 @@ struct Plan {
 int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
   int rc = build_geom(p, &pl->g);
   if (rc) return rc;
-  if (p->math_mode == DCN_MATH_TF32X3)
-    return fail(DCN_ERR_UNSUPPORTED, "the 3xTF32 contraction is not built yet; use FFMA");
+  if (p->math_mode == DCN_MATH_TF32X3 && p->dtype != DCN_DTYPE_F32)
+    return fail(DCN_ERR_ARG, "the 3xTF32 contraction is for fp32 tensors");
   pl->tc = plan_tc(p, pl->g, sms, &pl->tp);
   if (!pl->tc && p->math_mode == DCN_MATH_BF16)
     return fail(DCN_ERR_UNSUPPORTED,
                 "bf16 tensor-core contraction needs C/groups %% 64 == 0 and C/deformable_group %% 8 "
                 "== 0 (got C/groups=%d, C/deformable_group=%d)", pl->g.Cg, pl->g.cpdg);
+  // 3xTF32 on a shape the tensor-core kernel does not take runs on the FFMA kernel: both
+  // meet the fp32 tolerance, so the request degrades instead of failing.
   layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);
   pl->stage = pl->tc && pl->ws.xcl_bytes != 0;
   pl->launches = pl->tc ? (3 + (pl->stage ? 1 : 0)) : 2;  // status clear + prep + main
@@ -291,7 +301,7 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   info->stages_input = pl.stage ? 1 : 0;
   info->tile_m = pl.tc ? kBM : 1;
   info->tile_n = pl.tc ? pl.tp.BN : 1;
-  info->tile_k = pl.tc ? kBK : 1;
+  info->tile_k = pl.tc ? pl.tp.ch_per_stage : 1;
   info->grid = pl.tc ? pl.tp.grid : 0;
   info->block = pl.tc ? (6 + pl.tp.producer_warps) * 32 : 256;
   info->smem_bytes = pl.tc ? (int64_t)pl.tp.smem : 0;
@@ -346,10 +356,10 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
     if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;
   }
-  const __nv_bfloat16 *xcl = (const __nv_bfloat16 *)p->input;
+  const void *xcl = p->input;
   if (pl.stage) {
-    __nv_bfloat16 *dst = (__nv_bfloat16 *)(ws + pl.ws.xcl_off);
-    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, s);
+    void *dst = ws + pl.ws.xcl_off;
+    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.tiles_per_stage == 2, s);
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
     xcl = dst;
   }
@@ -360,7 +370,7 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   // phase counters live in the workspace header, bytes [64, 256); off unless asked for
   unsigned long long *counters =
       env_int("DCN_B200_COUNTERS", 0, 0, 1) ? (unsigned long long *)(ws + 64) : nullptr;
-  e = launch_tc_bf16(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, counters, s);
+  e = launch_tc(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, counters, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
   if (ev) cudaEventRecord(ev[3], s);
   return DCN_OK;

@@ -51,11 +51,12 @@ struct TcPlan {
   size_t smem;
   int tw_log2;             // tile = (128 >> tw_log2) x (1 << tw_log2) output pixels of one sample
   int tiles_x, tiles_y;    // tiles per sample
-  int blend_packed;        // 1: bilinear blend on packed bf16 FMAs, 0: in fp32
+  int tiles_per_stage;     // 1: bf16 operands; 2: TF32x3 (high part and remainder)
+  int ch_per_stage;        // input channels per k-stage: 64 (bf16) or 32 (TF32x3)
   int producer_warps;      // 8 or 16
 };
 
-enum { kBM = 128, kBK = 64 };
+enum { kBM = 128 };
 
 // One sampling tap: bilinear corner weights (already multiplied by the modulation
 // mask, and zero for corners outside the plane) and the integer position of the
@@ -107,13 +108,13 @@ cudaError_t launch_simt_tiled(const Geom &g, const Ptrs &p, int dtype, cudaStrea
 size_t simt_tiled_smem(const Geom &g);
 bool simt_tiled_supported(const Geom &g);
 
-cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype,
-                                  __nv_bfloat16 *xcl, cudaStream_t s);
+cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
+                                  bool to_fp32, cudaStream_t s);
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight,
                                 int dtype, void *wtiles, cudaStream_t s);
-cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
-                           const __nv_bfloat16 *xcl, const void *wtiles, int *status,
-                           unsigned long long *counters, cudaStream_t s);
+cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,
+                      const void *wtiles, int *status, unsigned long long *counters,
+                      cudaStream_t s);
 cudaError_t launch_clear_status(int *status, cudaStream_t s);
 
 // Records `msg` as the calling thread's dcn_last_error() text and returns `code`.

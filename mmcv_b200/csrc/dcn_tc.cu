@@ -34,12 +34,27 @@ constexpr int kEpilogueWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
 constexpr int kFirstProducerWarp = 6;
-constexpr int kAStageBytes = kBM * kBK * 2;  // 16 KiB
+constexpr int kTileBytes = kBM * 128;  // one operand tile: 128 rows of 128 bytes (16 KiB)
+
+// Arithmetic modes of the contraction.
+//  kModeBf16:   bf16 operands, one operand tile per stage, 64 channels per stage;
+//  kModeTf32x3: fp32 data split into a TF32 high part and a remainder (a = hi + lo, both
+//               held as fp32 bit patterns; the tensor core reads their top 19 bits), two
+//               operand tiles per stage, 32 channels per stage, three MMAs per k-step:
+//               hi*hi + lo*hi + hi*lo with fp32 accumulation.
+enum { kModeBf16 = 0, kModeTf32x3 = 1 };
+template <int MODE> struct ModeTraits;
+template <> struct ModeTraits<kModeBf16> {
+  static constexpr int kCh = 64, kCpv = 8, kEsz = 2, kTiles = 1;
+};
+template <> struct ModeTraits<kModeTf32x3> {
+  static constexpr int kCh = 32, kCpv = 4, kEsz = 4, kTiles = 2;
+};
 
 struct TcArgs {
   Geom g;
   TcPlan tp;
-  const __nv_bfloat16 *xcl;  // channels-last bf16 input [N, H, W, C]
+  const void *xcl;           // channels-last input [N, H, W, C], bf16 or fp32 by mode
   const uint8_t *wtiles;     // pre-swizzled weight stages
   const void *offset, *mask, *bias;
   void *output;
@@ -173,6 +188,15 @@ __device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -205,16 +229,6 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
   return d;
 }
 
-__device__ __forceinline__ void unpack_fma(float (&acc)[8], float w, const uint4 &q) {
-  const __nv_bfloat162 *h = reinterpret_cast<const __nv_bfloat162 *>(&q);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const float2 f = __bfloat1622float2(h[i]);
-    acc[2 * i] = fmaf(w, f.x, acc[2 * i]);
-    acc[2 * i + 1] = fmaf(w, f.y, acc[2 * i + 1]);
-  }
-}
-
 __device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) {
   return *reinterpret_cast<const __nv_bfloat162 *>(&u);
 }
@@ -222,43 +236,53 @@ __device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 h) {
   return *reinterpret_cast<const uint32_t *>(&h);
 }
 
-// Bilinear blend of four 8-channel corner vectors.  kPacked: weights are bf16 pairs and the
-// blend runs on packed bf16 FMAs (one multiply and three fused multiply-adds per channel
-// pair, each rounding to bf16); otherwise weights are fp32 and the blend is done in fp32
-// and rounded once.
-template <bool kPacked>
-__device__ __forceinline__ uint4 blend8(const uint4 &w, const uint4 &q0, const uint4 &q1,
-                                        const uint4 &q2, const uint4 &q3) {
+// Bilinear blend of four 8-channel bf16 corner vectors on packed bf16 FMAs: one multiply
+// and three fused multiply-adds per channel pair, each rounding to bf16.  `w` holds each
+// corner weight twice (a bf16 pair).
+__device__ __forceinline__ uint4 blend8_bf16(const uint4 &w, const uint4 &q0, const uint4 &q1,
+                                             const uint4 &q2, const uint4 &q3) {
   uint4 o;
-  if constexpr (kPacked) {
-    const __nv_bfloat162 w0 = as_bf162(w.x), w1 = as_bf162(w.y), w2 = as_bf162(w.z),
-                         w3 = as_bf162(w.w);
-    const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
-    const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
-    const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
-    const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
-    uint32_t *r = reinterpret_cast<uint32_t *>(&o);
+  const __nv_bfloat162 w0 = as_bf162(w.x), w1 = as_bf162(w.y), w2 = as_bf162(w.z),
+                       w3 = as_bf162(w.w);
+  const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
+  const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
+  const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
+  const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
+  uint32_t *r = reinterpret_cast<uint32_t *>(&o);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      __nv_bfloat162 t = __hmul2(w0, as_bf162(a0[i]));
-      t = __hfma2(w1, as_bf162(a1[i]), t);
-      t = __hfma2(w2, as_bf162(a2[i]), t);
-      t = __hfma2(w3, as_bf162(a3[i]), t);
-      r[i] = bf162_bits(t);
-    }
-  } else {
-    float acc[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-    unpack_fma(acc, __uint_as_float(w.x), q0);
-    unpack_fma(acc, __uint_as_float(w.y), q1);
-    unpack_fma(acc, __uint_as_float(w.z), q2);
-    unpack_fma(acc, __uint_as_float(w.w), q3);
-    __nv_bfloat162 *oh2 = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) oh2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 t = __hmul2(w0, as_bf162(a0[i]));
+    t = __hfma2(w1, as_bf162(a1[i]), t);
+    t = __hfma2(w2, as_bf162(a2[i]), t);
+    t = __hfma2(w3, as_bf162(a3[i]), t);
+    r[i] = bf162_bits(t);
   }
   return o;
+}
+
+// Bilinear blend of four 4-channel fp32 corner vectors in fp32 (weights are fp32 bits),
+// split into the TF32 high part (low 13 mantissa bits cleared) and the exact remainder.
+__device__ __forceinline__ void blend4_tf32(const uint4 &w, const uint4 &q0, const uint4 &q1,
+                                            const uint4 &q2, const uint4 &q3, uint4 &hi,
+                                            uint4 &lo) {
+  const float w0 = __uint_as_float(w.x), w1 = __uint_as_float(w.y), w2 = __uint_as_float(w.z),
+              w3 = __uint_as_float(w.w);
+  const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
+  const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
+  const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
+  const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
+  uint32_t *h = reinterpret_cast<uint32_t *>(&hi);
+  uint32_t *l = reinterpret_cast<uint32_t *>(&lo);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float t = w0 * __uint_as_float(a0[i]);
+    t = fmaf(w1, __uint_as_float(a1[i]), t);
+    t = fmaf(w2, __uint_as_float(a2[i]), t);
+    t = fmaf(w3, __uint_as_float(a3[i]), t);
+    const uint32_t hb = __float_as_uint(t) & 0xffffe000u;
+    h[i] = hb;
+    l[i] = __float_as_uint(t - __uint_as_float(hb));
+  }
 }
 
 constexpr int kRowInvalid = INT_MIN;
@@ -276,8 +300,8 @@ struct SmemLayout {
 __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int T) {
   SmemLayout L;
   uint8_t *p = base;
-  L.a = p; p += (size_t)tp.a_stages * kAStageBytes;
-  L.b = p; p += (size_t)tp.b_stages * tp.BN * 128;
+  L.a = p; p += (size_t)tp.a_stages * tp.tiles_per_stage * kTileBytes;
+  L.b = p; p += (size_t)tp.b_stages * tp.tiles_per_stage * tp.BN * 128;
   L.tab_w = (uint4 *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint4);
   L.tab_off = (uint32_t *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint32_t);
   L.row_h = (int *)p; p += kBM * sizeof(int);
@@ -293,7 +317,7 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
 
 size_t tc_smem_bytes(const TcPlan &tp, int T) {
   size_t s = 1024;  // slack for manual 1024-byte alignment
-  s += (size_t)tp.a_stages * kAStageBytes + (size_t)tp.b_stages * tp.BN * 128;
+  s += (size_t)tp.tiles_per_stage * ((size_t)tp.a_stages * kTileBytes + (size_t)tp.b_stages * tp.BN * 128);
   s += (size_t)T * tp.ndgc * kBM * (sizeof(uint4) + sizeof(uint32_t));
   s += 3 * kBM * sizeof(int);
   s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t) + 16;
@@ -321,9 +345,11 @@ __device__ __forceinline__ TileId decode_item(long long item, const Geom &g, con
   return t;
 }
 
-template <typename TIO, bool kPacked, int NPW>
+template <typename TIO, int MODE, int NPW>
 __global__ void __launch_bounds__((kFirstProducerWarp + NPW) * 32, 1)
-dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
+dcn_fwd_tc(const __grid_constant__ TcArgs a) {
+  using MT = ModeTraits<MODE>;
+  constexpr int kAStageBytes = MT::kTiles * kTileBytes;
   constexpr int kProdThreads = NPW * 32;
   constexpr int kGroups = NPW / 8;  // producer groups; group i fills k-stages i, i+G, ...
   extern __shared__ uint8_t smem_raw[];
@@ -339,7 +365,8 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
                  empty_b = bar0 + 16 * A + 8 * B, tmem_full = bar0 + 16 * A + 16 * B,
                  tmem_empty = tmem_full + 16, prod_bar = tmem_full + 32;
   volatile int *abort_s = L.abort_flag;
-  const uint32_t b_stage_bytes = (uint32_t)tp.BN * 128u;
+  const uint32_t b_tile_bytes = (uint32_t)tp.BN * 128u;
+  const uint32_t b_stage_bytes = b_tile_bytes * MT::kTiles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < A; ++i) {
@@ -415,7 +442,10 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+      // fp32 accumulate, both operands K-major, M = 128 pixels, N = BN channels;
+      // operand format 1 = bf16, 2 = tf32
+      constexpr uint32_t kFmt = MODE == kModeBf16 ? 1u : 2u;
+      const uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) |
                              ((uint32_t)(tp.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
       long long li = 0;
@@ -441,10 +471,24 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
           tc_fence_after();
           const uint64_t adesc = smem_desc_sw128(smem_u32(L.a + (size_t)sa * kAStageBytes));
           const uint64_t bdesc = smem_desc_sw128(smem_u32(L.b + (size_t)sb * b_stage_bytes));
+          // four k-steps of 32 bytes per 128-byte row: 16 bf16 or 8 tf32 elements each
+          if constexpr (MODE == kModeBf16) {
 #pragma unroll
-          for (int k = 0; k < kBK / 16; ++k)
-            umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                      (ks | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                        (ks | k) != 0 ? 1u : 0u);
+          } else {
+            // operand tiles of a stage: [hi][lo]; products hi*hi + lo*hi + hi*lo
+            const uint64_t adesc_lo = adesc + (uint64_t)(kTileBytes >> 4);
+            const uint64_t bdesc_lo = bdesc + (uint64_t)(b_tile_bytes >> 4);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                        (ks | k) != 0 ? 1u : 0u);
+              umma_tf32(d_tmem, adesc_lo + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, 1u);
+              umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc_lo + (uint64_t)(2 * k), idesc, 1u);
+            }
+          }
           umma_commit(empty_a + 8 * sa);
           umma_commit(empty_b + 8 * sb);
           if (++sa == (uint32_t)A) { sa = 0; pa ^= 1u; }
@@ -485,10 +529,10 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
     const int gi = pw >> 3;      // producer group
     const int pwl = pw & 7;      // warp within the group
     const int sub = lane >> 3;   // row within the warp's group of four
-    const int v = lane & 7;      // 16-byte vector (8 channels) within the 128-byte row
+    const int v = lane & 7;      // 16-byte vector (8 bf16 / 4 fp32 channels) of the 128-byte row
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
-    const uint32_t cW2 = (uint32_t)g.C * 2u, cH2 = (uint32_t)g.W * (uint32_t)g.C * 2u;
+    const uint32_t cW2 = (uint32_t)g.C * MT::kEsz, cH2 = (uint32_t)g.W * (uint32_t)g.C * MT::kEsz;
     // this thread's four rows of a stage and where their 16 bytes go (128-byte swizzle)
     const int row0 = pwl * 4 + sub;
     const uint32_t soff0 = (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
@@ -546,12 +590,12 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
         }
       }
       pt.lap(17);
-      const char *xb = reinterpret_cast<const char *>(a.xcl + (long long)t.n * g.H * g.W * g.C);
+      const char *xb = reinterpret_cast<const char *>(a.xcl) + (long long)t.n * g.H * g.W * g.C * MT::kEsz;
       int cur_lo = -1, cur_nd = 0;
       for (int cc = 0; cc < tp.KC && ok; ++cc) {
-        const int c0 = t.grp * g.Cg + cc * kBK;
+        const int c0 = t.grp * g.Cg + cc * MT::kCh;
         const int dg_lo = c0 / g.cpdg;
-        const int dg_hi = min(g.dg - 1, (c0 + kBK - 1) / g.cpdg);
+        const int dg_hi = min(g.dg - 1, (c0 + MT::kCh - 1) / g.cpdg);
         const int nd = dg_hi - dg_lo + 1;
         if (dg_lo != cur_lo || nd != cur_nd) {
           pt.lap(0);
@@ -613,7 +657,7 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
                               mskp ? raw_to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
                               wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
                 uint4 wq;
-                if constexpr (kPacked) {
+                if constexpr (MODE == kModeBf16) {
                   wq.x = bf162_bits(__float2bfloat162_rn(wt.x));
                   wq.y = bf162_bits(__float2bfloat162_rn(wt.y));
                   wq.z = bf162_bits(__float2bfloat162_rn(wt.z));
@@ -631,7 +675,7 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
                 }
                 const int slot = (etap * tp.ndgc + edgl) * kBM + trow;
                 L.tab_w[slot] = wq;
-                L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * 2);
+                L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * MT::kEsz);
               }
             }
           }
@@ -641,9 +685,9 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
           cur_lo = dg_lo;
           cur_nd = nd;
         }
-        const int c = c0 + v * 8;
+        const int c = c0 + v * MT::kCpv;
         const int dgl = c / g.cpdg - dg_lo;
-        const uint32_t c2 = (uint32_t)c * 2u;
+        const uint32_t c2 = (uint32_t)c * MT::kEsz;
         for (int tap = 0; tap < g.T; ++tap, ++tcount) {
           if (kGroups > 1 && (int)(tcount % kGroups) != gi) continue;
           pt.lap(0);
@@ -672,9 +716,18 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
               pt.lap(3);
             }
 #pragma unroll
-            for (int ps = 0; ps < kBatch; ++ps)
-              *reinterpret_cast<uint4 *>(stage + (p0 + ps) * 32 * 128) =
-                  blend8<kPacked>(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
+            for (int ps = 0; ps < kBatch; ++ps) {
+              uint8_t *dst = stage + (p0 + ps) * 32 * 128;
+              if constexpr (MODE == kModeBf16) {
+                *reinterpret_cast<uint4 *>(dst) =
+                    blend8_bf16(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
+              } else {
+                uint4 hi, lo;
+                blend4_tf32(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3], hi, lo);
+                *reinterpret_cast<uint4 *>(dst) = hi;
+                *reinterpret_cast<uint4 *>(dst + kTileBytes) = lo;
+              }
+            }
           }
           if (!ok) break;
           pt.lap(4);
@@ -707,10 +760,10 @@ dcn_fwd_tc_bf16(const __grid_constant__ TcArgs a) {
 // Preparation kernels
 // ---------------------------------------------------------------------------------
 
-// Input [N,C,H,W] (any element strides) -> channels-last bf16 [N,H,W,C].
-template <typename T>
+// Input [N,C,H,W] (any element strides) -> channels-last [N,H,W,C] in bf16 or fp32.
+template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
-dcn_stage_input_cl(const T *__restrict__ x, __nv_bfloat16 *__restrict__ y, int C, int H, int W,
+dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, int W,
                    long long sn, long long sc, long long sh, long long sw) {
   __shared__ float tile[32][33];
   const int n = blockIdx.z;
@@ -734,59 +787,80 @@ dcn_stage_input_cl(const T *__restrict__ x, __nv_bfloat16 *__restrict__ y, int C
     for (int k = 0; k < 4; ++k) {
       const int q = q0 + ty + 8 * k;
       if (q < HW && c < C)
-        y[((long long)n * HW + q) * C + c] = __float2bfloat16_rn(tile[tx][ty + 8 * k]);
+        st_from_float(y, ((long long)n * HW + q) * C + c, tile[tx][ty + 8 * k]);
     }
   }
 }
 
-cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype,
-                                  __nv_bfloat16 *xcl, cudaStream_t s) {
+cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
+                                  bool to_fp32, cudaStream_t s) {
   if (g.N == 0) return cudaSuccess;
   dim3 grid((g.H * g.W + 31) / 32, (g.C + 31) / 32, g.N);
-  if (dtype == DCN_DTYPE_F32)
-    dcn_stage_input_cl<float><<<grid, 256, 0, s>>>((const float *)input, xcl, g.C, g.H, g.W,
-                                                    g.in_sn, g.in_sc, g.in_sh, g.in_sw);
+  if (dtype == DCN_DTYPE_F32 && to_fp32)
+    dcn_stage_input_cl<float, float><<<grid, 256, 0, s>>>(
+        (const float *)input, (float *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh, g.in_sw);
+  else if (dtype == DCN_DTYPE_F32)
+    dcn_stage_input_cl<float, __nv_bfloat16><<<grid, 256, 0, s>>>(
+        (const float *)input, (__nv_bfloat16 *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh,
+        g.in_sw);
+  else if (to_fp32)
+    dcn_stage_input_cl<__nv_bfloat16, float><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16 *)input, (float *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh,
+        g.in_sw);
   else
-    dcn_stage_input_cl<__nv_bfloat16><<<grid, 256, 0, s>>>(
-        (const __nv_bfloat16 *)input, xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh, g.in_sw);
+    dcn_stage_input_cl<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16 *)input, (__nv_bfloat16 *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc,
+        g.in_sh, g.in_sw);
   return cudaGetLastError();
 }
 
 // Weight [Co, Cg, kh, kw] -> one pre-swizzled shared-memory image per
-// (group, n-tile, k-stage): BN rows of 64 bf16 (128 bytes), 16-byte chunk index XORed
-// with (row & 7).  k-stage = chunk*T + tap; column = channel within the 64-chunk.
+// (group, n-tile, k-stage): BN rows of 128 bytes, 16-byte chunk index XORed with (row & 7).
+// k-stage = chunk*T + tap.  bf16 mode: 64 channels per row.  TF32x3 mode: 32 fp32 channels
+// per row and two images per stage, the TF32 high parts (low 13 mantissa bits cleared)
+// followed by the exact remainders.
 template <typename T>
 __global__ void __launch_bounds__(256)
 dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int Cog, int Tt,
-                 int BN, int NT, int S) {
+                 int BN, int NT, int S, int tf32) {
   const int blk = blockIdx.x;  // (grp*NT + nt)*S + ks
   const int ks = blk % S;
   const int gn = blk / S;
   const int nt = gn % NT, grp = gn / NT;
   const int cc = ks / Tt, tap = ks - cc * Tt;
-  uint8_t *out = dst + (size_t)blk * BN * 128;
-  for (int e = threadIdx.x; e < BN * 64; e += blockDim.x) {
-    const int r = e >> 6, j = e & 63;
+  const int ch = tf32 ? 32 : 64;  // channels per row
+  uint8_t *out = dst + (size_t)blk * BN * 128 * (tf32 ? 2 : 1);
+  for (int e = threadIdx.x; e < BN * ch; e += blockDim.x) {
+    const int r = e / ch, j = e - r * ch;
     const int col = nt * BN + r;
     float val = 0.f;
     if (col < Cog) {
       const long long co = (long long)grp * Cog + col;
-      val = ld_as_float(w, (co * Cg + (cc * 64 + j)) * Tt + tap);
+      val = ld_as_float(w, (co * Cg + (cc * ch + j)) * Tt + tap);
     }
-    const int byte = r * 128 + (((j >> 3) ^ (r & 7)) << 4) + (j & 7) * 2;
-    *reinterpret_cast<__nv_bfloat16 *>(out + byte) = __float2bfloat16_rn(val);
+    if (tf32) {
+      const int byte = r * 128 + (((j >> 2) ^ (r & 7)) << 4) + (j & 3) * 4;
+      const uint32_t hb = __float_as_uint(val) & 0xffffe000u;
+      *reinterpret_cast<uint32_t *>(out + byte) = hb;
+      *reinterpret_cast<float *>(out + (size_t)BN * 128 + byte) = val - __uint_as_float(hb);
+    } else {
+      const int byte = r * 128 + (((j >> 3) ^ (r & 7)) << 4) + (j & 7) * 2;
+      *reinterpret_cast<__nv_bfloat16 *>(out + byte) = __float2bfloat16_rn(val);
+    }
   }
 }
 
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight, int dtype,
                                 void *wtiles, cudaStream_t s) {
   const int blocks = g.groups * tp.NT * tp.S;
+  const int tf32 = tp.tiles_per_stage == 2 ? 1 : 0;
   if (dtype == DCN_DTYPE_F32)
     dcn_weight_tiles<float><<<blocks, 256, 0, s>>>((const float *)weight, (uint8_t *)wtiles, g.Cg,
-                                                   g.Cog, g.T, tp.BN, tp.NT, tp.S);
+                                                   g.Cog, g.T, tp.BN, tp.NT, tp.S, tf32);
   else
     dcn_weight_tiles<__nv_bfloat16><<<blocks, 256, 0, s>>>(
-        (const __nv_bfloat16 *)weight, (uint8_t *)wtiles, g.Cg, g.Cog, g.T, tp.BN, tp.NT, tp.S);
+        (const __nv_bfloat16 *)weight, (uint8_t *)wtiles, g.Cg, g.Cog, g.T, tp.BN, tp.NT, tp.S,
+        tf32);
   return cudaGetLastError();
 }
 
@@ -801,9 +875,9 @@ cudaError_t launch_clear_status(int *status, cudaStream_t s) {
 }
 
 namespace {
-template <typename TIO, bool kPacked, int NPW>
+template <typename TIO, int MODE, int NPW>
 cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
-  auto kern = dcn_fwd_tc_bf16<TIO, kPacked, NPW>;
+  auto kern = dcn_fwd_tc<TIO, MODE, NPW>;
   // opt in to large dynamic shared memory once per device and instantiation
   static std::atomic<unsigned long long> done_mask{0};
   int dev = 0;
@@ -829,15 +903,17 @@ cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 }
 template <typename TIO>
 cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
-  if (tp.producer_warps == 16)
-    return tp.blend_packed ? launch_one<TIO, true, 16>(a, tp, s) : launch_one<TIO, false, 16>(a, tp, s);
-  return tp.blend_packed ? launch_one<TIO, true, 8>(a, tp, s) : launch_one<TIO, false, 8>(a, tp, s);
+  if (tp.tiles_per_stage == 2)
+    return tp.producer_warps == 16 ? launch_one<TIO, kModeTf32x3, 16>(a, tp, s)
+                                   : launch_one<TIO, kModeTf32x3, 8>(a, tp, s);
+  return tp.producer_warps == 16 ? launch_one<TIO, kModeBf16, 16>(a, tp, s)
+                                 : launch_one<TIO, kModeBf16, 8>(a, tp, s);
 }
 }  // namespace
 
-cudaError_t launch_tc_bf16(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
-                           const __nv_bfloat16 *xcl, const void *wtiles, int *status,
-                           unsigned long long *counters, cudaStream_t s) {
+cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,
+                      const void *wtiles, int *status, unsigned long long *counters,
+                      cudaStream_t s) {
   if (tp.items == 0) return cudaSuccess;
   TcArgs a;
   a.g = g;

@@ -103,6 +103,29 @@ def test_fp32_tensors_with_bf16_contraction(name):
     assert rel_l2(out.cpu(), t['out']) <= BF16_TOL
 
 
+@pytest.mark.parametrize('name', ['v2_c64', 'v2_c128_co40_dg4', 'v2_c128_g2_dg2_s2', 'v1_c64'])
+def test_fp32_tf32x3_contraction_meets_fp32_bound(name):
+    # fp32 tensors, contraction on the tensor cores as three TF32 products (hi*hi + lo*hi +
+    # hi*lo): must meet the same fp32 bound as the FFMA kernel
+    m, t = golden_cases().get(name)
+    info = plan_path(t['x'], t['weight'], m, torch.float32, math=_lib.MATH_TF32X3)
+    assert info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
+    out = run_cuda(t, m, torch.float32, math=_lib.MATH_TF32X3)
+    ok, frac = fp32_close(out, t['out'])
+    assert ok, f'{name}: error is {frac:.3f}x the bound'
+    cl = run_cuda(t, m, torch.float32, math=_lib.MATH_TF32X3, channels_last=True)
+    assert torch.equal(cl, out)
+
+
+def test_tf32x3_falls_back_to_ffma_on_odd_shapes():
+    m, t = golden_cases().get('v2_basic')          # 8 channels: not a tensor-core shape
+    info = plan_path(t['x'], t['weight'], m, torch.float32, math=_lib.MATH_TF32X3)
+    assert info.path == _lib.PATH_SIMT_DIRECT
+    out = run_cuda(t, m, torch.float32, math=_lib.MATH_TF32X3)
+    ok, frac = fp32_close(out, t['out'])
+    assert ok, frac
+
+
 def synth(N, C, H, W, Co, k, s, p, d, g, dg, sigma, mask, bias, seed=0, int_frac=0.0,
           mask_sigma=1.0):
     gen = torch.Generator().manual_seed(seed)
@@ -122,8 +145,8 @@ def synth(N, C, H, W, Co, k, s, p, d, g, dg, sigma, mask, bias, seed=0, int_frac
     return m, t
 
 
-def check_against_oracle(m, t, dtype, samples=None):
-    out = run_cuda(t, m, dtype).float().cpu()
+def check_against_oracle(m, t, dtype, samples=None, math=None):
+    out = run_cuda(t, m, dtype, math=math).float().cpu()
     idx = list(range(t['x'].shape[0])) if samples is None else samples
     sub = {k: (v if (v is None or k in ('weight', 'bias')) else v[idx]) for k, v in t.items()}
     if dtype == torch.bfloat16:
@@ -150,6 +173,19 @@ def test_config3_full_edge_offsets(dtype):
     m, t = synth(4, 512, 64, 64, 512, 3, 2, 2, 2, 1, 4, 8.0, True, True, int_frac=0.05,
                  mask_sigma=2.0)
     check_against_oracle(m, t, dtype)
+
+
+def test_config1_and_config3_fp32_tf32x3():
+    m, t = synth(2, 64, 56, 56, 64, 3, 1, 1, 1, 1, 1, 2.0, True, True)
+    check_against_oracle(m, t, torch.float32, math=_lib.MATH_TF32X3)
+    m, t = synth(4, 512, 64, 64, 512, 3, 2, 2, 2, 1, 4, 8.0, True, True, int_frac=0.05,
+                 mask_sigma=2.0)
+    check_against_oracle(m, t, torch.float32, math=_lib.MATH_TF32X3)
+
+
+def test_config2_v1_fp32_tf32x3_two_samples():
+    m, t = synth(8, 256, 100, 168, 256, 3, 1, 1, 1, 1, 1, 1.5, False, False)
+    check_against_oracle(m, t, torch.float32, samples=[0, 7], math=_lib.MATH_TF32X3)
 
 
 def test_config2_v1_bf16_two_samples():

@@ -55,6 +55,11 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
+    assert info.smem_bytes <= 232448
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=8, Co=8))
+    assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT      # degrades to FFMA
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
     assert rc == 0 and (info.Ho, info.Wo) == (32, 32) and info.tile_n == 256
 
@@ -71,6 +76,8 @@ def test_plan_rejects_what_the_reference_rejects():
     assert rc == -2
     rc, _ = plan(params(C=48, Co=48, math=_lib.MATH_BF16))
     assert rc == -2
+    rc, _ = plan(params(math=_lib.MATH_TF32X3))          # bf16 tensors with the fp32-only mode
+    assert rc == -1
 
 
 def test_forward_on_cpu_tensors_fails_loudly():
