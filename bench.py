@@ -28,13 +28,13 @@ WORKLOADS = {
     # name: N, C, H, W, Co, k, stride, pad, dil, groups, dg, offset sigma, mask, bias, int_frac, mask sigma
     'c5': dict(N=256, C=256, H=128, W=128, Co=256, k=3, s=1, p=1, d=1, g=1, dg=8, sigma=2.0,
                mask=True, bias=True, int_frac=0.0, msigma=1.0,
-               desc='DCNv2 N=256 C=256 128x128 3x3 s1 p1 dg=8 bias bf16'),
+               desc='DCNv2 N=256 C=256 128x128 3x3 s1 p1 dg=8 bias'),
     'c2': dict(N=8, C=256, H=100, W=168, Co=256, k=3, s=1, p=1, d=1, g=1, dg=1, sigma=1.5,
                mask=False, bias=False, int_frac=0.0, msigma=1.0,
-               desc='DCNv1 N=8 C=256 100x168 3x3 s1 p1 dg=1 bf16'),
+               desc='DCNv1 N=8 C=256 100x168 3x3 s1 p1 dg=1'),
     'c3': dict(N=4, C=512, H=64, W=64, Co=512, k=3, s=2, p=2, d=2, g=1, dg=4, sigma=8.0,
                mask=True, bias=True, int_frac=0.05, msigma=2.0,
-               desc='DCNv2 N=4 C=512 64x64 3x3 s2 p2 d2 dg=4 bias bf16'),
+               desc='DCNv2 N=4 C=512 64x64 3x3 s2 p2 d2 dg=4 bias'),
 }
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
@@ -137,6 +137,25 @@ class ClockSampler:
             out.update(sm_mhz=load[len(load) // 2], sm_max_mhz=max(mx), samples=len(sm))
         out['reasons'] = sorted(reasons)
         return out
+
+
+def measure_tf32_peak(dev):
+    """Dense TF32 matmul rate of this GPU (library GEMM, best of 5): the denominator of the
+    3xTF32 roofline, measured the way the bf16 peak of MEASURED_PEAKS.json was."""
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    a = torch.randn(8192, 8192, device=dev)
+    b = torch.randn(8192, 8192, device=dev)
+    best = 1e9
+    for _ in range(6):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        a @ b
+        e1.record()
+        torch.cuda.synchronize(dev)
+        best = min(best, e0.elapsed_time(e1))
+    torch.backends.cuda.matmul.allow_tf32 = prev
+    return 2 * 8192 ** 3 / (best * 1e-3) / 1e12
 
 
 def cpu_reference_sample(wl, seconds_budget=20.0, max_reps=3):
@@ -255,6 +274,8 @@ def run_c4(args, rank, world, local):
                 y = m(hx.to(dev, non_blocking=True))
             hout.copy_(y, non_blocking=True)
 
+    if args.dtype == 'fp32':
+        _ext.set_fp32_math(args.fp32_math)
     e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -333,7 +354,7 @@ def run_reference(args, wl, rank, world):
                 n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
                 ms_per_step=total / args.steps * 1e3, higher_is_better=True, scaling='strong',
                 vs_baseline=None, dtype='f32', data='synthetic',
-                config=dict(workload=args.workload + ': ' + wl['desc'],
+                config=dict(workload=args.workload + ': ' + wl['desc'] + ' ' + args.dtype,
                             sample=f'each step = {n} of {wl["N"]} samples on the host CPU'),
                 cpu_baseline=cb,
                 e2e=dict(value=val, unit='TFLOP/s', h2d_bytes_per_step=0, d2h_bytes_per_step=0),
@@ -351,6 +372,9 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
+    ap.add_argument('--fp32-math', default='tf32x3', choices=['tf32x3', 'ffma'],
+                    help='contraction arithmetic for --dtype fp32')
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
     if args.workload == 'c4':
@@ -390,10 +414,11 @@ def main():
     n0, n1 = batch_shard(wl['N'], rank, world)
     per = (wl['N'] + world - 1) // world
     n = n1 - n0
-    dtype = torch.bfloat16
+    dtype = torch.bfloat16 if args.dtype == 'bf16' else torch.float32
+    esize = 2 if args.dtype == 'bf16' else 4
     x, off, msk, w, b = make_inputs(wl, n0, n1, dev, dtype)
-    fl_rank, by_rank, Ho, Wo = flops_and_bytes(wl, n, 2)
-    fl_total, by_total, _, _ = flops_and_bytes(wl, wl['N'], 2)
+    fl_rank, by_rank, Ho, Wo = flops_and_bytes(wl, n, esize)
+    fl_total, by_total, _, _ = flops_and_bytes(wl, wl['N'], esize)
     out = torch.empty(n, wl['Co'], Ho, Wo, device=dev, dtype=dtype)
     st, pd, dl = (wl['s'],) * 2, (wl['p'],) * 2, (wl['d'],) * 2
 
@@ -404,7 +429,11 @@ def main():
         p.mask = msk.data_ptr() if msk is not None else None
         p.weight, p.bias = w.data_ptr(), (b.data_ptr() if b is not None else None)
         p.output = out.data_ptr()
-        p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
+        if args.dtype == 'bf16':
+            p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
+        else:
+            p.dtype = _lib.DTYPE_F32
+            p.math_mode = _lib.MATH_TF32X3 if args.fp32_math == 'tf32x3' else _lib.MATH_FFMA
         p.N, p.C, p.H, p.W, p.Co = n, wl['C'], wl['H'], wl['W'], wl['Co']
         p.kh = p.kw = wl['k']
         p.stride_h = p.stride_w = wl['s']
@@ -464,8 +493,8 @@ def main():
     hx, hoff = x.cpu().pin_memory(), off.cpu().pin_memory()
     hmsk = msk.cpu().pin_memory() if msk is not None else None
     hout = torch.empty(out.shape, dtype=dtype).pin_memory()
-    h2d = hx.numel() * 2 + hoff.numel() * 2 + (hmsk.numel() * 2 if hmsk is not None else 0)
-    d2h = hout.numel() * 2
+    h2d = (hx.numel() + hoff.numel() + (hmsk.numel() if hmsk is not None else 0)) * esize
+    d2h = hout.numel() * esize
 
     def e2e_step():
         dx = hx.to(dev, non_blocking=True)
@@ -477,6 +506,8 @@ def main():
             y = deform_conv2d(dx, doff, w, st, pd, dl, wl['g'], wl['dg'], False, 32)
         hout.copy_(y, non_blocking=True)
 
+    if args.dtype == 'fp32':
+        _ext.set_fp32_math(args.fp32_math)
     e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -500,17 +531,25 @@ def main():
             peaks = json.load(open(ppath))
         peak_tf = peaks.get('bf16_tflops', 1590.0)
         peak_src = 'measured (MEASURED_PEAKS.json bf16_tflops, burst)' if peaks else 'fallback 1.59 PFLOP/s'
+        if args.dtype == 'fp32' and info.path == 1:
+            tf32 = measure_tf32_peak(dev)
+            peak_tf = tf32 / 3.0
+            peak_src = f'torch.matmul TF32 8192^3 measured in this run ({tf32:.0f} TFLOP/s) / 3 products'
+        elif args.dtype == 'fp32':
+            peak_tf = 148 * 128 * 2 * 1.965e9 / 1e12
+            peak_src = 'nominal FFMA rate: 148 SMs x 128 lanes x 2 flop x 1.965 GHz'
         hbm = peaks.get('hbm_gbs', 6650.0)
         achieved = fl_rank / (k_main * 1e-3) / 1e12 if k_main > 0 else 0.0
         roof_ms = max(fl_rank / (peak_tf * 1e12), by_rank / (hbm * 1e9)) * 1e3
-        traffic = NCU_TRAFFIC_BYTES.get(args.workload)
+        traffic = NCU_TRAFFIC_BYTES.get(args.workload) if args.dtype == 'bf16' else None
         traffic = traffic * n if traffic is not None else None
         line = dict(
             metric='dcnv2_fwd_tflops', value=fl_total / (ms_step * 1e-3) / 1e12, unit='TFLOP/s',
             n_gpus=world, steps=args.steps, warmup=args.warmup, ms_per_step=ms_step,
-            higher_is_better=True, scaling='strong', vs_baseline=None, dtype='bf16',
+            higher_is_better=True, scaling='strong', vs_baseline=None,
+            dtype='bf16' if args.dtype == 'bf16' else ('tf32x3' if info.path == 1 else 'f32'),
             data='synthetic',
-            config=dict(workload=args.workload + ': ' + wl['desc'], global_batch=wl['N'],
+            config=dict(workload=args.workload + ': ' + wl['desc'] + ' ' + args.dtype, global_batch=wl['N'],
                         per_gpu_batch=per, parallelism=f'batch-shard x{world}, no collective',
                         l2='inputs (GBs) larger than L2; no flush needed',
                         plan=dict(path={1: 'tcgen05', 2: 'simt_tiled', 3: 'simt_direct'}[info.path],
@@ -527,7 +566,7 @@ def main():
                           frac=achieved / peak_tf, traffic=traffic, peak_source=peak_src,
                           frac_of_sustained=(achieved / peaks['bf16_tflops_sustained']
                                              if 'bf16_tflops_sustained' in peaks else None),
-                          kernel='dcn_fwd_tc_bf16'),
+                          kernel='dcn_fwd_tc' if info.path == 1 else 'dcn_fwd_simt_direct'),
             e2e=dict(value=fl_total / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
                      h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms,
                      steps=e2e_steps, api='mmcv_b200.ops.modulated_deform_conv2d'),

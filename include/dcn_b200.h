@@ -23,9 +23,15 @@ extern "C" {
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1 };
 
-/* Arithmetic of the contraction.  AUTO picks BF16 for bf16 tensors and FFMA for
- * fp32 tensors.  BF16 = tcgen05 kind::f16 tensor-core MMA with fp32 accumulation
- * in tensor memory; FFMA = fp32 fused multiply-add on the SIMT cores. */
+/* Arithmetic of the contraction.
+ *   BF16   tcgen05 kind::f16 MMA on bf16 operands, fp32 accumulation in tensor memory.
+ *   TF32X3 fp32 tensors only: tcgen05 kind::tf32 MMA, every operand split into a TF32 high
+ *          part and a remainder, three products per step (hi*hi + lo*hi + hi*lo); meets the
+ *          same fp32 error bound as FFMA.  Shapes the tensor-core kernel does not take
+ *          (it needs C/groups % 4 == 0 and C/deformable_group % 4 == 0) run on the FFMA
+ *          kernel instead.
+ *   FFMA   fp32 fused multiply-add on the SIMT cores, any shape.
+ *   AUTO   BF16 for bf16 tensors, TF32X3 for fp32 tensors. */
 enum { DCN_MATH_AUTO = 0, DCN_MATH_FFMA = 1, DCN_MATH_TF32X3 = 2, DCN_MATH_BF16 = 3 };
 
 enum {

@@ -15,12 +15,13 @@ import torch
 from . import _lib
 
 _FP32_MATH = {'ffma': _lib.MATH_FFMA, 'tf32x3': _lib.MATH_TF32X3}
-_fp32_math = os.environ.get('DCN_B200_FP32_MATH', 'ffma').lower()
+_fp32_math = os.environ.get('DCN_B200_FP32_MATH', 'tf32x3').lower()
 _check_status = os.environ.get('DCN_B200_CHECK_STATUS', '0') == '1'
 
 
 def set_fp32_math(mode: str) -> None:
-    """Contraction arithmetic for fp32 tensors: 'ffma' or 'tf32x3'."""
+    """Contraction arithmetic for fp32 tensors: 'tf32x3' (tensor cores, three TF32 products
+    per step; the default) or 'ffma' (SIMT cores).  Both meet the fp32 error bound."""
     global _fp32_math
     if mode not in _FP32_MATH:
         raise ValueError(f'unknown fp32 math mode {mode!r}')

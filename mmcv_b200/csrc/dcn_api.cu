@@ -125,7 +125,7 @@ bool input_is_ready(const DcnFwdParams *p, const Geom &g, bool tf32) {
 
 int resolved_math(const DcnFwdParams *p) {
   return p->math_mode == DCN_MATH_AUTO
-             ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_FFMA)
+             ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_TF32X3)
              : p->math_mode;
 }
 
@@ -135,7 +135,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   if (math != DCN_MATH_BF16 && math != DCN_MATH_TF32X3) return false;
   const bool tf32 = math == DCN_MATH_TF32X3;
   const int ch = tf32 ? 32 : 64, cpv = tf32 ? 4 : 8;
-  if (g.Cg % ch != 0 || g.cpdg % cpv != 0) return false;
+  if (g.Cg % cpv != 0 || g.cpdg % cpv != 0) return false;
   if ((long long)g.N * g.H * g.W >= 2147483647LL) return false;
   if ((long long)g.H * g.W * g.C * (tf32 ? 4 : 2) >= 4294967295LL) return false;
   if (g.kh > 255 || g.kw > 255 || g.T > 4095) return false;
@@ -151,14 +151,15 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     tp->NT = (g.Cog + cap - 1) / cap;
     const int per = (g.Cog + tp->NT - 1) / tp->NT;
     tp->BN = (per + 31) / 32 * 32;
-    tp->KC = g.Cg / ch;
+    tp->KC = (g.Cg + ch - 1) / ch;
     tp->S = tp->KC * g.T;
     int ndgc = 1;
     for (int grp = 0; grp < g.groups; ++grp)
       for (int cc = 0; cc < tp->KC; ++cc) {
         const int c0 = grp * g.Cg + cc * ch;
-        const int lo = c0 / g.cpdg, hi = (c0 + ch - 1) / g.cpdg;
-        const int nd = (hi < g.dg ? hi : g.dg - 1) - lo + 1;
+        const int c1 = c0 + ch < (grp + 1) * g.Cg ? c0 + ch : (grp + 1) * g.Cg;  // chunk end
+        const int lo = c0 / g.cpdg, hi = (c1 - 1) / g.cpdg;
+        const int nd = hi - lo + 1;
         if (nd > ndgc) ndgc = nd;
       }
     if (ndgc > 15) return false;
@@ -266,7 +267,7 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
   pl->tc = plan_tc(p, pl->g, sms, &pl->tp);
   if (!pl->tc && p->math_mode == DCN_MATH_BF16)
     return fail(DCN_ERR_UNSUPPORTED,
-                "bf16 tensor-core contraction needs C/groups %% 64 == 0 and C/deformable_group %% 8 "
+                "bf16 tensor-core contraction needs C/groups %% 8 == 0 and C/deformable_group %% 8 "
                 "== 0 (got C/groups=%d, C/deformable_group=%d)", pl->g.Cg, pl->g.cpdg);
   // 3xTF32 on a shape the tensor-core kernel does not take runs on the FFMA kernel: both
   // meet the fp32 tolerance, so the request degrades instead of failing.

@@ -595,7 +595,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       for (int cc = 0; cc < tp.KC && ok; ++cc) {
         const int c0 = t.grp * g.Cg + cc * MT::kCh;
         const int dg_lo = c0 / g.cpdg;
-        const int dg_hi = min(g.dg - 1, (c0 + MT::kCh - 1) / g.cpdg);
+        const int dg_hi = (min(c0 + MT::kCh, (t.grp + 1) * g.Cg) - 1) / g.cpdg;
         const int nd = dg_hi - dg_lo + 1;
         if (dg_lo != cur_lo || nd != cur_nd) {
           pt.lap(0);
@@ -685,7 +685,9 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           cur_lo = dg_lo;
           cur_nd = nd;
         }
-        const int c = c0 + v * MT::kCpv;
+        // the last chunk of a group may be partly beyond its channels: those vectors are zero
+        const bool vvalid = cc * MT::kCh + v * MT::kCpv < g.Cg;
+        const int c = vvalid ? c0 + v * MT::kCpv : c0;
         const int dgl = c / g.cpdg - dg_lo;
         const uint32_t c2 = (uint32_t)c * MT::kEsz;
         for (int tap = 0; tap < g.T; ++tap, ++tcount) {
@@ -702,7 +704,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             uint4 q[kBatch][4], wq[kBatch];
 #pragma unroll
             for (int ps = 0; ps < kBatch; ++ps) {
-              wq[ps] = L.tab_w[slot0 + (p0 + ps) * 32];
+              wq[ps] = vvalid ? L.tab_w[slot0 + (p0 + ps) * 32] : z;
               const uint32_t o = L.tab_off[slot0 + (p0 + ps) * 32] + c2;
               q[ps][0] = wq[ps].x ? __ldg((const uint4 *)(xb + o)) : z;
               q[ps][1] = wq[ps].y ? __ldg((const uint4 *)(xb + (uint32_t)(o + cW2))) : z;
@@ -834,7 +836,7 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
     const int r = e / ch, j = e - r * ch;
     const int col = nt * BN + r;
     float val = 0.f;
-    if (col < Cog) {
+    if (col < Cog && cc * ch + j < Cg) {
       const long long co = (long long)grp * Cog + col;
       val = ld_as_float(w, (co * Cg + (cc * ch + j)) * Tt + tap);
     }

@@ -58,10 +58,11 @@ def rounded(t, dtype):
     return {k: (None if v is None else v.to(dtype).float()) for k, v in t.items()}
 
 
+@pytest.mark.parametrize('math', [_lib.MATH_FFMA, _lib.MATH_AUTO])
 @pytest.mark.parametrize('name', golden_case_names())
-def test_golden_fp32(name):
+def test_golden_fp32(name, math):
     m, t = golden_cases().get(name)
-    out = run_cuda(t, m, torch.float32)
+    out = run_cuda(t, m, torch.float32, math=math)
     ok, frac = fp32_close(out, t['out'])
     assert ok, f'{name}: error is {frac:.2f}x the bound'
 
@@ -96,6 +97,15 @@ def test_tensor_core_path_is_taken_and_matches(name, channels_last):
     assert rel_l2(out.float().cpu(), simt.float().cpu()) <= BF16_TOL
 
 
+def test_partly_filled_channel_chunk():
+    # 96 channels in two conv groups of 48: the 64-channel chunk of each group is 3/4 full
+    m, t = synth(2, 96, 17, 19, 80, 3, 1, 1, 1, 2, 4, 2.0, True, True, seed=5)
+    assert plan_path(t['x'], t['weight'], m, torch.bfloat16).path == _lib.PATH_TCGEN05
+    check_against_oracle(m, t, torch.bfloat16)
+    assert plan_path(t['x'], t['weight'], m, torch.float32).path == _lib.PATH_TCGEN05
+    check_against_oracle(m, t, torch.float32)
+
+
 @pytest.mark.parametrize('name', ['v2_c64', 'v2_c128_co40_dg4'])
 def test_fp32_tensors_with_bf16_contraction(name):
     m, t = golden_cases().get(name)
@@ -118,7 +128,7 @@ def test_fp32_tf32x3_contraction_meets_fp32_bound(name):
 
 
 def test_tf32x3_falls_back_to_ffma_on_odd_shapes():
-    m, t = golden_cases().get('v2_basic')          # 8 channels: not a tensor-core shape
+    m, t = golden_cases().get('v2_k1')             # 6 channels: not a tensor-core shape
     info = plan_path(t['x'], t['weight'], m, torch.float32, math=_lib.MATH_TF32X3)
     assert info.path == _lib.PATH_SIMT_DIRECT
     out = run_cuda(t, m, torch.float32, math=_lib.MATH_TF32X3)

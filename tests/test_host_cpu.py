@@ -49,8 +49,12 @@ def test_plan_routes_and_sizes():
     assert info.smem_bytes <= 232448 and info.stages_input == 1
     assert info.workspace_bytes >= 2 * 64 * 16 * 16 * 2 + 64 * 64 * 9 * 2
     rc, info = plan(params(dtype=_lib.DTYPE_F32))
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32   # 3xTF32
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_FFMA))
     assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT
-    rc, info = plan(params(C=48, Co=48))                 # channels not a multiple of 64
+    rc, info = plan(params(C=48, Co=48))                 # a partly filled last 64-channel chunk
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05
+    rc, info = plan(params(C=20, Co=20))                 # channels not a multiple of 8
     assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
@@ -58,7 +62,7 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
-    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=8, Co=8))
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=6, Co=6))
     assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT      # degrades to FFMA
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
     assert rc == 0 and (info.Ho, info.Wo) == (32, 32) and info.tile_n == 256
@@ -74,7 +78,7 @@ def test_plan_rejects_what_the_reference_rejects():
         assert text in lib.dcn_last_error().decode()
     rc, _ = plan(params(dtype=7))
     assert rc == -2
-    rc, _ = plan(params(C=48, Co=48, math=_lib.MATH_BF16))
+    rc, _ = plan(params(C=20, Co=20, math=_lib.MATH_BF16))
     assert rc == -2
     rc, _ = plan(params(math=_lib.MATH_TF32X3))          # bf16 tensors with the fp32-only mode
     assert rc == -1
