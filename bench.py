@@ -40,9 +40,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
 # committed ncu summary under profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    # 352.8 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
+    # 356.9 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
     # by the batch: traffic grows in proportion to the samples processed
-    'c5': 352.8e6 / 16,
+    'c5': 356.9e6 / 16,
 }
 
 
@@ -99,7 +99,7 @@ class ClockSampler:
         self.f = tempfile.NamedTemporaryFile('w+', suffix='.csv', delete=False)
         try:
             self.p = subprocess.Popen(['nvidia-smi', '-i', str(index), '--query-gpu=' + self.QUERY,
-                                       '--format=csv,noheader,nounits', '-lms', '100'],
+                                       '--format=csv,noheader,nounits', '-lms', '20'],
                                       stdout=self.f, stderr=subprocess.DEVNULL)
         except OSError:
             self.p = None
@@ -372,10 +372,14 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--counters', action='store_true',
+                    help='also report the in-kernel phase counters of the first CTA')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--fp32-math', default='tf32x3', choices=['tf32x3', 'ffma'],
                     help='contraction arithmetic for --dtype fp32')
     args = ap.parse_args()
+    if args.counters:
+        os.environ['DCN_B200_COUNTERS'] = '1'
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
     if args.workload == 'c4':
         if args.impl == 'reference':
@@ -573,6 +577,8 @@ def main():
             gpu_launches=args.steps * info.launches,
             clocks=clocks,
         )
+        if counters is not None:
+            line['phase_counters_cycles_block0_last_launch'] = counters
         if not args.no_cpu_baseline:
             line['cpu_baseline'] = cpu_reference_sample(wl)
         print(json.dumps(line), flush=True)
