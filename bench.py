@@ -491,35 +491,70 @@ def main():
         for i in range(3):
             kms[i] += buf[i] / reps
     clocks = sampler.stop() if sampler else None
+    counters = None
+    if args.counters and rank == 0:
+        c = (ctypes.c_uint64 * 24)()
+        _lib.check(lib.dcn_read_counters(ctypes.c_void_p(ws.data_ptr()), sptr, c))
+        names = ['producer_other', 'table_compute', 'producer_rendezvous', 'wait_free_stage',
+                 'gather_blend', 'stages', 'tables', 'publish_stage', 'mma_wait_weights',
+                 'mma_wait_operand', 'mma_wait_accumulator', 'mma_issue', 'epilogue_wait',
+                 'epilogue_work', 'loader_wait', 'loader_issue', 'table_load_issue',
+                 'offset_prefetch']
+        counters = {n: int(c[i]) for i, n in enumerate(names)}
 
-    # end-to-end through the public API: pinned host -> device, op, device -> pinned host
+    # End to end through the public API: every step copies the step's inputs from pinned host
+    # memory to the device, runs the op, and copies the result back to pinned host memory.
+    # The batch goes through in chunks on three streams (copy in, compute, copy out), so that
+    # the two copy directions and the kernels overlap, as an application would arrange it.
     e2e_steps = max(1, min(args.e2e_steps, args.steps))
     hx, hoff = x.cpu().pin_memory(), off.cpu().pin_memory()
     hmsk = msk.cpu().pin_memory() if msk is not None else None
     hout = torch.empty(out.shape, dtype=dtype).pin_memory()
     h2d = (hx.numel() + hoff.numel() + (hmsk.numel() if hmsk is not None else 0)) * esize
     d2h = hout.numel() * esize
+    chunk = max(1, min(n, max(1, n // 8)))
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
 
     def e2e_step():
-        dx = hx.to(dev, non_blocking=True)
-        doff = hoff.to(dev, non_blocking=True)
-        if hmsk is not None:
-            dm = hmsk.to(dev, non_blocking=True)
-            y = modulated_deform_conv2d(dx, doff, dm, w, b, st, pd, dl, wl['g'], wl['dg'])
-        else:
-            y = deform_conv2d(dx, doff, w, st, pd, dl, wl['g'], wl['dg'], False, 32)
-        hout.copy_(y, non_blocking=True)
+        keep = []          # device tensors stay referenced until the step has drained
+        for i0 in range(0, n, chunk):
+            i1 = min(n, i0 + chunk)
+            with torch.cuda.stream(s_in):
+                dx = hx[i0:i1].to(dev, non_blocking=True)
+                doff = hoff[i0:i1].to(dev, non_blocking=True)
+                dm = hmsk[i0:i1].to(dev, non_blocking=True) if hmsk is not None else None
+                ready = torch.cuda.Event()
+                ready.record(s_in)
+            stream.wait_event(ready)
+            if dm is not None:
+                y = modulated_deform_conv2d(dx, doff, dm, w, b, st, pd, dl, wl['g'], wl['dg'])
+            else:
+                y = deform_conv2d(dx, doff, w, st, pd, dl, wl['g'], wl['dg'], False, 32)
+            done = torch.cuda.Event()
+            done.record(stream)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                hout[i0:i1].copy_(y, non_blocking=True)
+            keep.append((dx, doff, dm, y))
+        stream.wait_stream(s_in)
+        stream.wait_stream(s_out)
+        return keep
 
     if args.dtype == 'fp32':
         _ext.set_fp32_math(args.fp32_math)
-    e2e_step()
+    keep = e2e_step()
     barrier()
+    del keep
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s_in.wait_stream(stream)
+    s_out.wait_stream(stream)
     f0.record(stream)
+    s_in.wait_event(f0)
     for _ in range(e2e_steps):
-        e2e_step()
+        keep = e2e_step()
     f1.record(stream)
     barrier()
+    del keep
     e2e_ms = f0.elapsed_time(f1) / e2e_steps
 
     t = torch.tensor([ms_total, e2e_ms, kms[0], kms[1], kms[2]], device=dev, dtype=torch.float64)
@@ -573,7 +608,9 @@ def main():
                           kernel='dcn_fwd_tc' if info.path == 1 else 'dcn_fwd_simt_direct'),
             e2e=dict(value=fl_total / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
                      h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms,
-                     steps=e2e_steps, api='mmcv_b200.ops.modulated_deform_conv2d'),
+                     steps=e2e_steps, chunks=(n + chunk - 1) // chunk,
+                     api='mmcv_b200.ops.modulated_deform_conv2d' if msk is not None
+                     else 'mmcv_b200.ops.deform_conv2d'),
             gpu_launches=args.steps * info.launches,
             clocks=clocks,
         )

@@ -297,7 +297,9 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   int rc = make_plan(p, kSmCountFallback, &pl);
   if (rc) return rc;
   memset(info, 0, sizeof(*info));
-  info->path = pl.tc ? DCN_PATH_TCGEN05 : DCN_PATH_SIMT_DIRECT;
+  info->path = pl.tc ? DCN_PATH_TCGEN05
+                     : (simt_tiled_supported(pl.g) && pl.g.P * pl.g.Co >= 4096 ? DCN_PATH_SIMT_TILED
+                                                                                : DCN_PATH_SIMT_DIRECT);
   info->launches = pl.launches;
   info->stages_input = pl.stage ? 1 : 0;
   info->tile_m = pl.tc ? kBM : 1;
@@ -352,7 +354,11 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   }
   if (!pl.tc) {
     if (ev) { cudaEventRecord(ev[1], s); cudaEventRecord(ev[2], s); }
-    e = launch_simt_direct(pl.g, ptrs, p->dtype, s);
+    // tiny problems stay on the one-thread-per-output kernel: a 64x64 tile would be mostly empty
+    const bool tiled = simt_tiled_supported(pl.g) && env_int("DCN_B200_SIMT_TILED", 1, 0, 1) &&
+                       pl.g.P * pl.g.Co >= 4096;
+    e = tiled ? launch_simt_tiled(pl.g, ptrs, p->dtype, s)
+              : launch_simt_direct(pl.g, ptrs, p->dtype, s);
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "SIMT kernel launch: %s", cudaGetErrorString(e));
     if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;

@@ -91,13 +91,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when the block is aborting.
+// Bounded wait.  Returns false when the block is aborting.  kBackoff: sleep between polls;
+// used by the roles that wait long and are not on the critical path (epilogue, loader), so
+// that their polling does not take issue slots from the producer warps.
+template <bool kBackoff = false>
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_s,
                                           int *status, int code) {
   if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (kBackoff) __nanosleep(200);
     if ((it & 31u) == 0u) {
       if (*abort_s) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
@@ -416,7 +420,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       const int ncols = min(tp.BN, g.Cog - t.nt * tp.BN);
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
       pt.lap(13);
-      if (!mbar_wait(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
+      if (!mbar_wait<true>(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
       pt.lap(12);
       tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t)(buf * tp.BN) + ((uint32_t)(warp * 32) << 16);
@@ -511,7 +515,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
         for (int ks = 0; ks < tp.S; ++ks) {
           pt.lap(15);
-          ok = mbar_wait(empty_b + 8 * sb, pb ^ 1u, abort_s, a.status, 7);
+          ok = mbar_wait<true>(empty_b + 8 * sb, pb ^ 1u, abort_s, a.status, 7);
           if (!ok) break;
           pt.lap(14);
           mbar_arrive_expect_tx(full_b + 8 * sb, b_stage_bytes);

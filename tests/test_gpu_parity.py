@@ -198,6 +198,19 @@ def test_config2_v1_fp32_tf32x3_two_samples():
     check_against_oracle(m, t, torch.float32, samples=[0, 7], math=_lib.MATH_TF32X3)
 
 
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+def test_tiled_ffma_kernel_config1_and_odd_channels(dtype):
+    # the FFMA mode on a tensor-core shape, and a channel count only the SIMT kernels take
+    m, t = synth(2, 64, 56, 56, 64, 3, 1, 1, 1, 1, 1, 2.0, True, True)
+    assert plan_path(t['x'], t['weight'], m, dtype, math=_lib.MATH_FFMA).path == _lib.PATH_SIMT_TILED
+    check_against_oracle(m, t, dtype, math=_lib.MATH_FFMA)
+    m, t = synth(2, 36, 23, 31, 70, 3, 2, 1, 1, 2, 3, 3.0, True, True, seed=9)
+    assert plan_path(t['x'], t['weight'], m, dtype).path == _lib.PATH_SIMT_TILED
+    check_against_oracle(m, t, dtype)
+    m, t = synth(1, 12, 30, 29, 10, 5, 1, 2, 1, 1, 1, 2.0, False, False, seed=10)   # 5x5, v1
+    check_against_oracle(m, t, dtype)
+
+
 def test_config2_v1_bf16_two_samples():
     m, t = synth(8, 256, 100, 168, 256, 3, 1, 1, 1, 1, 1, 1.5, False, False)
     check_against_oracle(m, t, torch.bfloat16, samples=[0, 7])

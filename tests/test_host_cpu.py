@@ -51,19 +51,21 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(dtype=_lib.DTYPE_F32))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32   # 3xTF32
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_FFMA))
-    assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT
+    assert rc == 0 and info.path == _lib.PATH_SIMT_TILED
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_FFMA, N=1, C=4, Co=4, H=5, W=5))
+    assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT      # too small for 64x64 tiles
     rc, info = plan(params(C=48, Co=48))                 # a partly filled last 64-channel chunk
     assert rc == 0 and info.path == _lib.PATH_TCGEN05
     rc, info = plan(params(C=20, Co=20))                 # channels not a multiple of 8
-    assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT
+    assert rc == 0 and info.path == _lib.PATH_SIMT_TILED
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
-    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=6, Co=6))
-    assert rc == 0 and info.path == _lib.PATH_SIMT_DIRECT      # degrades to FFMA
+    rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=6, Co=12))
+    assert rc == 0 and info.path == _lib.PATH_SIMT_TILED       # degrades to FFMA
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
     assert rc == 0 and (info.Ho, info.Wo) == (32, 32) and info.tile_n == 256
 
