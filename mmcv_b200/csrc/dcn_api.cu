@@ -164,7 +164,17 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
       }
     if (ndgc > 15) return false;
     tp->ndgc = ndgc;
-    tp->producer_warps = env_int("DCN_B200_PRODUCER_WARPS", 16, 8, 16) >= 16 ? 16 : 8;
+    // Producer layout (measured): three groups of four warps when the tap table is built
+    // once per tile (one deform-group set per chunk, bf16), else two groups of eight, which
+    // rebuild the table faster; TF32x3 writes two tiles per row and prefers the latter too.
+    const int cfg_default = (ndgc == 1 && !tf32) ? 342 : 282;
+    switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 999)) {
+      case 184: tp->producer_cfg = 184; break;
+      case 342: tp->producer_cfg = 342; break;
+      case 282: tp->producer_cfg = 282; break;
+      default: tp->producer_cfg = cfg_default; break;
+    }
+    const int a_min = tp->producer_cfg / 100;  // every producer group needs a stage of its own
     int cols = 32;
     while (cols < 2 * tp->BN) cols *= 2;
     tp->tmem_cols = cols;
@@ -173,7 +183,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     // of L1), deepest A ring first; only then fall back to the largest configuration.
     const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
     for (int bi = 0; bi < 2 && !found; ++bi)
-      for (int as = 4; as >= 2 && !found; --as)
+      for (int as = 4; as >= a_min && !found; --as)
         for (int bs = (bi == 0 ? 2 : 4); bs >= 2 && !found; --bs) {
           if ((a_forced && as != a_forced) || (b_forced && bs != b_forced)) continue;
           tp->a_stages = as;
@@ -306,7 +316,7 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   info->tile_n = pl.tc ? pl.tp.BN : 1;
   info->tile_k = pl.tc ? pl.tp.ch_per_stage : 1;
   info->grid = pl.tc ? pl.tp.grid : 0;
-  info->block = pl.tc ? (6 + pl.tp.producer_warps) * 32 : 256;
+  info->block = pl.tc ? tc_threads(pl.tp) : 256;
   info->smem_bytes = pl.tc ? (int64_t)pl.tp.smem : 0;
   info->Ho = pl.g.Ho;
   info->Wo = pl.g.Wo;

@@ -53,7 +53,7 @@ struct TcPlan {
   int tiles_x, tiles_y;    // tiles per sample
   int tiles_per_stage;     // 1: bf16 operands; 2: TF32x3 (high part and remainder)
   int ch_per_stage;        // input channels per k-stage: 64 (bf16) or 32 (TF32x3)
-  int producer_warps;      // 8 or 16
+  int producer_cfg;        // groups*100 + warps_per_group*10 + rows in flight per thread
 };
 
 enum { kBM = 128 };
@@ -116,6 +116,8 @@ cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
                       const void *wtiles, int *status, unsigned long long *counters,
                       cudaStream_t s);
 cudaError_t launch_clear_status(int *status, cudaStream_t s);
+
+int tc_threads(const TcPlan &tp);
 
 // Records `msg` as the calling thread's dcn_last_error() text and returns `code`.
 int set_error(int code, const char *msg);

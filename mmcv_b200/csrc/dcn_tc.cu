@@ -349,13 +349,21 @@ __device__ __forceinline__ TileId decode_item(long long item, const Geom &g, con
   return t;
 }
 
-template <typename TIO, int MODE, int NPW>
-__global__ void __launch_bounds__((kFirstProducerWarp + NPW) * 32, 1)
+// PCFG encodes the producer layout as groups*100 + warps_per_group*10 + rows_in_flight:
+// `groups` groups of `warps_per_group` warps fill alternate stages, and every thread keeps
+// `rows_in_flight` rows (four 16-byte loads each) in flight.
+template <typename TIO, int MODE, int PCFG>
+__global__ void __launch_bounds__((kFirstProducerWarp + (PCFG / 100) * ((PCFG / 10) % 10)) * 32, 1)
 dcn_fwd_tc(const __grid_constant__ TcArgs a) {
+  constexpr int kGroups = PCFG / 100;       // group i fills k-stages i, i+G, ...
+  constexpr int kWpg = (PCFG / 10) % 10;    // warps per group
+  constexpr int kBatch = PCFG % 10;         // rows of a thread in flight at a time
+  constexpr int NPW = kGroups * kWpg;
+  constexpr int kPasses = 32 / kWpg;        // rows of a stage per thread
+  constexpr int kRowStep = 4 * kWpg;        // distance between them
   using MT = ModeTraits<MODE>;
   constexpr int kAStageBytes = MT::kTiles * kTileBytes;
   constexpr int kProdThreads = NPW * 32;
-  constexpr int kGroups = NPW / 8;  // producer groups; group i fills k-stages i, i+G, ...
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const Geom &g = a.g;
@@ -374,7 +382,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < A; ++i) {
-      mbar_init(full_a + 8 * i, 8);  // the eight warps of one producer group
+      mbar_init(full_a + 8 * i, kWpg);  // the warps of one producer group
       mbar_init(empty_a + 8 * i, 1);
     }
     for (int i = 0; i < B; ++i) {
@@ -530,14 +538,16 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     // ------------------------------ producers ------------------------------
     const int ptid = threadIdx.x - kFirstProducerWarp * 32;
     const int pw = ptid >> 5;
-    const int gi = pw >> 3;      // producer group
-    const int pwl = pw & 7;      // warp within the group
+    const int gi = pw / kWpg;    // producer group
+    const int pwl = pw % kWpg;   // warp within the group
     const int sub = lane >> 3;   // row within the warp's group of four
     const int v = lane & 7;      // 16-byte vector (8 bf16 / 4 fp32 channels) of the 128-byte row
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
     const uint32_t cW2 = (uint32_t)g.C * MT::kEsz, cH2 = (uint32_t)g.W * (uint32_t)g.C * MT::kEsz;
-    // this thread's four rows of a stage and where their 16 bytes go (128-byte swizzle)
+    const uint32_t cHW2 = cH2 + cW2;
+    // this thread's first row of a stage and where its 16 bytes go (128-byte swizzle); its
+    // other rows are kRowStep rows further, which keeps the swizzle phase
     const int row0 = pwl * 4 + sub;
     const uint32_t soff0 = (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
     // rows whose tap entries this thread computes when a table is rebuilt
@@ -615,7 +625,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
             const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
             const int total = g.T * nd;
-            constexpr int kEnt = NPW == 8 ? 9 : 5;  // entries in flight per thread
+            constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : 5);  // entries in flight per thread
             int tap = 0, dgl = tpart, ti = 0, tj = 0;  // entry e <-> (tap, dgl), tap <-> (ti, tj)
             auto normalise = [&]() {
               while (dgl >= nd) {
@@ -701,19 +711,17 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           uint8_t *stage = L.a + (size_t)sa * kAStageBytes + soff0;
           const int slot0 = (tap * tp.ndgc + dgl) * kBM + row0;
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
-          // kBatch rows of this thread are in flight at a time (four 16-byte loads each)
-          constexpr int kBatch = NPW == 8 ? 4 : 2;
 #pragma unroll
-          for (int p0 = 0; p0 < 4; p0 += kBatch) {
+          for (int p0 = 0; p0 < kPasses; p0 += kBatch) {
             uint4 q[kBatch][4], wq[kBatch];
 #pragma unroll
             for (int ps = 0; ps < kBatch; ++ps) {
-              wq[ps] = vvalid ? L.tab_w[slot0 + (p0 + ps) * 32] : z;
-              const uint32_t o = L.tab_off[slot0 + (p0 + ps) * 32] + c2;
+              wq[ps] = vvalid ? L.tab_w[slot0 + (p0 + ps) * kRowStep] : z;
+              const uint32_t o = L.tab_off[slot0 + (p0 + ps) * kRowStep] + c2;
               q[ps][0] = wq[ps].x ? __ldg((const uint4 *)(xb + o)) : z;
               q[ps][1] = wq[ps].y ? __ldg((const uint4 *)(xb + (uint32_t)(o + cW2))) : z;
               q[ps][2] = wq[ps].z ? __ldg((const uint4 *)(xb + (uint32_t)(o + cH2))) : z;
-              q[ps][3] = wq[ps].w ? __ldg((const uint4 *)(xb + (uint32_t)(o + cH2 + cW2))) : z;
+              q[ps][3] = wq[ps].w ? __ldg((const uint4 *)(xb + (uint32_t)(o + cHW2))) : z;
             }
             if (p0 == 0) {
               // the stage must be free only now, with this batch's loads already in flight
@@ -723,7 +731,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             }
 #pragma unroll
             for (int ps = 0; ps < kBatch; ++ps) {
-              uint8_t *dst = stage + (p0 + ps) * 32 * 128;
+              uint8_t *dst = stage + (p0 + ps) * kRowStep * 128;
               if constexpr (MODE == kModeBf16) {
                 *reinterpret_cast<uint4 *>(dst) =
                     blend8_bf16(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
@@ -881,9 +889,10 @@ cudaError_t launch_clear_status(int *status, cudaStream_t s) {
 }
 
 namespace {
-template <typename TIO, int MODE, int NPW>
+template <typename TIO, int MODE, int PCFG>
 cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
-  auto kern = dcn_fwd_tc<TIO, MODE, NPW>;
+  auto kern = dcn_fwd_tc<TIO, MODE, PCFG>;
+  constexpr int kThreads = (kFirstProducerWarp + (PCFG / 100) * ((PCFG / 10) % 10)) * 32;
   // opt in to large dynamic shared memory once per device and instantiation
   static std::atomic<unsigned long long> done_mask{0};
   int dev = 0;
@@ -904,18 +913,27 @@ cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
     if (e != cudaSuccess) return e;
     carve_pct[dev & 63].store(pct, std::memory_order_release);
   }
-  kern<<<tp.grid, (kFirstProducerWarp + NPW) * 32, tp.smem, s>>>(a);
+  kern<<<tp.grid, kThreads, tp.smem, s>>>(a);
   return cudaGetLastError();
+}
+template <typename TIO, int MODE>
+cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
+  switch (tp.producer_cfg) {
+    case 184: return launch_one<TIO, MODE, 184>(a, tp, s);
+    case 342: return launch_one<TIO, MODE, 342>(a, tp, s);
+    default: return launch_one<TIO, MODE, 282>(a, tp, s);
+  }
 }
 template <typename TIO>
 cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
-  if (tp.tiles_per_stage == 2)
-    return tp.producer_warps == 16 ? launch_one<TIO, kModeTf32x3, 16>(a, tp, s)
-                                   : launch_one<TIO, kModeTf32x3, 8>(a, tp, s);
-  return tp.producer_warps == 16 ? launch_one<TIO, kModeBf16, 16>(a, tp, s)
-                                 : launch_one<TIO, kModeBf16, 8>(a, tp, s);
+  return tp.tiles_per_stage == 2 ? launch_mode<TIO, kModeTf32x3>(a, tp, s)
+                                 : launch_mode<TIO, kModeBf16>(a, tp, s);
 }
 }  // namespace
+
+int tc_threads(const TcPlan &tp) {
+  return (kFirstProducerWarp + (tp.producer_cfg / 100) * ((tp.producer_cfg / 10) % 10)) * 32;
+}
 
 cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,
                       const void *wtiles, int *status, unsigned long long *counters,
