@@ -145,6 +145,30 @@ int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_by
 #define DCN_STATIC_SCRATCH_BYTES (32u << 20)
 int dcn_fwd_static_scratch(const DcnFwdParams *p, void *stream, void **scratch);
 
+/*
+ * Backward building blocks (first version: the three sampling kernels; the two matrix
+ * products of the backward stay with the caller's BLAS, as in the reference, which calls
+ * addmm_ for them: mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:183-230).
+ * All take the forward problem description (`weight`, `bias`, `output` unused) and a sample
+ * range [n0, n1).  Gradients and columns are fp32 whatever the tensors' dtype.
+ *
+ * dcn_bwd_columns : columns[(n-n0)*C*T + c*T + tap][Ho*Wo], the sampled (and modulated)
+ *   input, K order as weight.flatten(1); replaces modulated_deformable_im2col
+ *   (mmcv/ops/csrc/common/cuda/modulated_deform_conv_cuda_kernel.cuh:186-245).
+ * dcn_bwd_input   : grad_input [N,C,H,W] (dense fp32) += scatter of grad_columns (same
+ *   layout as columns) to the bilinear corners; replaces modulated_deformable_col2im
+ *   (same file, :247-307).  Uses atomic adds: zero grad_input before the first call.
+ * dcn_bwd_coord   : grad_offset [N, dg*2*T, Ho, Wo] and grad_mask [N, dg*T, Ho, Wo] (dense
+ *   fp32; grad_mask may be NULL for the v1 operator), assigned for samples [n0, n1);
+ *   replaces modulated_deformable_col2im_coord (same file, :309-397).
+ * The unmodulated twins are mmcv/ops/csrc/common/cuda/deform_conv_cuda_kernel.cuh:243-365.
+ */
+int dcn_bwd_columns(const DcnFwdParams *p, int64_t n0, int64_t n1, float *columns, void *stream);
+int dcn_bwd_input(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *grad_columns,
+                  float *grad_input, void *stream);
+int dcn_bwd_coord(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *grad_columns,
+                  float *grad_offset, float *grad_mask, void *stream);
+
 /* Tracing aid.  When the environment variable DCN_B200_COUNTERS=1 is set, the first
  * block of the tensor-core kernel accumulates the clock cycles its roles spend in each
  * phase into 24 counters in the workspace header; this call synchronises `stream` and

@@ -4,8 +4,8 @@ Exposes the five functions that the reference's Python wrappers look up on
 ``mmcv._ext`` (``mmcv/ops/modulated_deform_conv.py:17-19``,
 ``mmcv/ops/deform_conv.py:19-22``) with the positional order and keyword names
 of the reference's module definition (``mmcv/ops/csrc/pytorch/pybind.cpp:525-545,
-641-656``).  The two forwards call the CUDA library through its C ABI; the three
-backward entries exist so that the wrappers import, and raise.
+641-656``).  All five call the CUDA library through its C ABI; the backward entries
+additionally use torch.matmul for the two matrix products the reference gives to addmm_.
 """
 import ctypes
 import os
@@ -210,13 +210,138 @@ def conv_offset_forward(x, weight, bias, stride, padding, dilation, sigmoid_from
     return out
 
 
-def _no_backward(name):
-    def fn(*args, **kwargs):
-        raise RuntimeError(f'dcn_b200: {name} is not implemented (forward-only build)')
-    fn.__name__ = name
-    return fn
+# ---------------------------------------------------------------------------------------
+# Backward.  Three sampling kernels of the library (columns, input scatter, coordinate
+# gradients) around two plain matrix products, which go to torch.matmul (cuBLAS) exactly
+# where the reference calls addmm_.  Everything is computed in fp32 and cast at the end.
+# ---------------------------------------------------------------------------------------
+_BWD_CHUNK_BYTES = 1 << 29   # column workspace per chunk of samples
 
 
-modulated_deform_conv_backward = _no_backward('modulated_deform_conv_backward')
-deform_conv_backward_input = _no_backward('deform_conv_backward_input')
-deform_conv_backward_parameters = _no_backward('deform_conv_backward_parameters')
+def _params(input, offset, mask, weight, stride, padding, dilation, groups, deform_groups):
+    p = _lib.DcnFwdParams()
+    p.input, p.offset, p.mask = _ptr(input), _ptr(offset), _ptr(mask)
+    p.weight = _ptr(weight)
+    p.dtype, p.math_mode = _dtype_code(input), _lib.MATH_FFMA
+    p.N, p.C, p.H, p.W = input.shape
+    p.Co, p.kh, p.kw = weight.shape[0], weight.shape[2], weight.shape[3]
+    p.stride_h, p.stride_w = stride
+    p.pad_h, p.pad_w = padding
+    p.dil_h, p.dil_w = dilation
+    p.groups, p.deform_groups = groups, deform_groups
+    for i, st in enumerate(input.stride()):
+        p.in_stride[i] = st
+    dev = input.device
+    p.device = dev.index if dev.index is not None else torch.cuda.current_device()
+    return p
+
+
+def _backward(input, offset, mask, weight, grad_output, stride, padding, dilation, groups,
+              deform_groups, want_input=True, want_weight=True):
+    """Returns fp32 (grad_input, grad_offset, grad_mask, grad_weight); entries not wanted are
+    None.  mask=None is the unmodulated operator."""
+    lib = _lib.load()
+    dev = _require_cuda(input=input, offset=offset, mask=mask, weight=weight,
+                        grad_output=grad_output)
+    input = _input_layout(input)
+    offset = offset.contiguous()
+    mask = None if mask is None else mask.contiguous()
+    N, C, H, W = input.shape
+    Co, Cg, kh, kw = weight.shape
+    T, K = kh * kw, Cg * kh * kw
+    Ho, Wo = grad_output.shape[2], grad_output.shape[3]
+    P = Ho * Wo
+    p = _params(input, offset, mask, weight, stride, padding, dilation, groups, deform_groups)
+    w2 = weight.detach().float().reshape(groups, Co // groups, K) if want_input else None
+    go_all = grad_output.detach().float().contiguous()
+    g_in = torch.zeros(N, C, H, W, device=dev, dtype=torch.float32) if want_input else None
+    g_off = torch.empty(offset.shape, device=dev, dtype=torch.float32) if want_input else None
+    g_msk = (torch.empty(mask.shape, device=dev, dtype=torch.float32)
+             if (want_input and mask is not None) else None)
+    g_w = torch.zeros(groups, Co // groups, K, device=dev, dtype=torch.float32) if want_weight else None
+    per_sample = C * T * P * 4
+    step = max(1, min(N, _BWD_CHUNK_BYTES // max(per_sample, 1)))
+    with torch.cuda.device(dev):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        for n0 in range(0, N, step):
+            n1 = min(N, n0 + step)
+            go = go_all[n0:n1].reshape(n1 - n0, groups, Co // groups, P)
+            if want_input:
+                # grad_columns[s, g] = W[g]^T @ grad_out[s, g]      (K x Cog) @ (Cog x P)
+                gcol = torch.matmul(w2.transpose(1, 2).unsqueeze(0), go).contiguous()
+                _lib.check(lib.dcn_bwd_coord(ctypes.byref(p), n0, n1, _ptr(gcol), _ptr(g_off),
+                                             _ptr(g_msk), stream))
+                _lib.check(lib.dcn_bwd_input(ctypes.byref(p), n0, n1, _ptr(gcol), _ptr(g_in),
+                                             stream))
+                del gcol
+            if want_weight:
+                col = torch.empty(n1 - n0, groups, K, P, device=dev, dtype=torch.float32)
+                _lib.check(lib.dcn_bwd_columns(ctypes.byref(p), n0, n1, _ptr(col), stream))
+                # grad_weight[g] += sum_s grad_out[s, g] @ columns[s, g]^T
+                g_w += torch.matmul(go, col.transpose(2, 3)).sum(0)
+                del col
+    if g_w is not None:
+        g_w = g_w.reshape(weight.shape)
+    return g_in, g_off, g_msk, g_w
+
+
+def modulated_deform_conv_backward(input, weight, bias, ones, offset, mask, columns, grad_input,
+                                   grad_weight, grad_bias, grad_offset, grad_mask, grad_output,
+                                   kernel_h, kernel_w, stride_h, stride_w, pad_h, pad_w,
+                                   dilation_h, dilation_w, group, deformable_group, with_bias):
+    """Same contract as the reference entry of this name
+    (mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:140-251): fills the five gradient
+    tensors in place (weight and bias gradients are accumulated, as in the reference)."""
+    if weight.size(2) != kernel_h or weight.size(3) != kernel_w:
+        raise RuntimeError(f"Input shape and kernel shape won't match: ({kernel_h} x {kernel_w} "
+                           f'vs {weight.size(2)} x {weight.size(3)}).')
+    if input.size(1) != weight.size(1) * group:
+        raise RuntimeError(f"Input shape and kernel channels won't match: ({input.size(1)} vs "
+                           f'{weight.size(1) * group}).')
+    gi, go_, gm, gw = _backward(input, offset, mask, weight, grad_output, (stride_h, stride_w),
+                                (pad_h, pad_w), (dilation_h, dilation_w), group, deformable_group)
+    grad_input.copy_(gi)
+    grad_offset.copy_(go_)
+    grad_mask.copy_(gm)
+    grad_weight.add_(gw.to(grad_weight.dtype))
+    if with_bias:
+        grad_bias.add_(grad_output.detach().float().sum((0, 2, 3)).to(grad_bias.dtype))
+
+
+def deform_conv_backward_input(input, offset, gradOutput, gradInput, gradOffset, weight, columns,
+                               kW, kH, dW, dH, padW, padH, dilationW, dilationH, group,
+                               deformable_group, im2col_step):
+    """Same contract as the reference entry of this name
+    (mmcv/ops/csrc/pytorch/deform_conv.cpp:262-393)."""
+    for name, t in (('input', input), ('offset', offset), ('gradOutput', gradOutput),
+                    ('gradInput', gradInput), ('gradOffset', gradOffset), ('weight', weight)):
+        if not t.is_contiguous():
+            raise RuntimeError(f'{name} must be contiguous')
+    if im2col_step <= 0 or input.size(0) % im2col_step != 0:
+        raise RuntimeError('batch size must be divisible by im2col_step')
+    gi, go_, _, _ = _backward(input, offset, None, weight, gradOutput, (dH, dW), (padH, padW),
+                              (dilationH, dilationW), group, deformable_group, want_weight=False)
+    gradInput.copy_(gi)
+    gradOffset.copy_(go_)
+
+
+def deform_conv_backward_parameters(input, offset, gradOutput, gradWeight, columns, ones, kW, kH,
+                                    dW, dH, padW, padH, dilationW, dilationH, group,
+                                    deformable_group, scale, im2col_step):
+    """Same contract as the reference entry of this name
+    (mmcv/ops/csrc/pytorch/deform_conv.cpp:395-525): gradWeight += scale * gradient."""
+    for name, t in (('input', input), ('offset', offset), ('gradOutput', gradOutput),
+                    ('gradWeight', gradWeight)):
+        if not t.is_contiguous():
+            raise RuntimeError(f'{name} must be contiguous')
+    if im2col_step <= 0 or input.size(0) % im2col_step != 0:
+        raise RuntimeError('batch size must be divisible by im2col_step')
+    _, _, _, gw = _backward(input, offset, None, weight_like(gradWeight), gradOutput, (dH, dW),
+                            (padH, padW), (dilationH, dilationW), group, deformable_group,
+                            want_input=False)
+    gradWeight.add_((gw * scale).to(gradWeight.dtype))
+
+
+def weight_like(grad_weight):
+    """The parameter-gradient entry receives no weight tensor; its shape is gradWeight's."""
+    return grad_weight

@@ -18,7 +18,8 @@ STATIC_SCRATCH_BYTES = 32 << 20
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_fwd_workspace_bytes', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
-           'dcn_read_counters', 'dcn_read_status',
+           'dcn_read_counters', 'dcn_read_status', 'dcn_bwd_columns', 'dcn_bwd_input',
+           'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
 
@@ -77,6 +78,9 @@ def load():
     lib.dcn_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_fwd_profiled.argtypes = [P(DcnFwdParams), vp, sz, vp, P(ctypes.c_float)]
     lib.dcn_fwd_static_scratch.argtypes = [P(DcnFwdParams), vp, P(vp)]
+    lib.dcn_bwd_columns.argtypes = [P(DcnFwdParams), i64, i64, vp, vp]
+    lib.dcn_bwd_input.argtypes = [P(DcnFwdParams), i64, i64, vp, vp, vp]
+    lib.dcn_bwd_coord.argtypes = [P(DcnFwdParams), i64, i64, vp, vp, vp, vp]
     lib.dcn_read_counters.argtypes = [vp, vp, P(ctypes.c_uint64)]
     lib.dcn_read_status.argtypes = [vp, vp, P(i32)]
     lib.dcn_modulated_deform_conv_forward.argtypes = (

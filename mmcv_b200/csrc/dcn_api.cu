@@ -421,6 +421,51 @@ int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_by
   return rc;
 }
 
+static int bwd_common(const DcnFwdParams *p, int64_t n0, int64_t n1, Geom *g) {
+  int rc = build_geom(p, g);
+  if (rc) return rc;
+  if (n0 < 0 || n1 < n0 || n1 > g->N) return fail(DCN_ERR_ARG, "sample range [%lld, %lld) is not inside the batch", (long long)n0, (long long)n1);
+  if (!p->input) return fail(DCN_ERR_ARG, "input must be non-NULL");
+  DeviceInfo *dev = nullptr;
+  rc = probe_device(p->device, &dev);
+  if (rc) return rc;
+  cudaError_t e = cudaSetDevice(p->device);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  return DCN_OK;
+}
+
+int dcn_bwd_columns(const DcnFwdParams *p, int64_t n0, int64_t n1, float *columns, void *stream) {
+  Geom g;
+  int rc = bwd_common(p, n0, n1, &g);
+  if (rc) return rc;
+  if (!columns) return fail(DCN_ERR_ARG, "columns must be non-NULL");
+  Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
+  cudaError_t e = launch_bwd_columns(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), columns, (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "column kernel launch: %s", cudaGetErrorString(e));
+}
+
+int dcn_bwd_input(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *grad_columns,
+                  float *grad_input, void *stream) {
+  Geom g;
+  int rc = bwd_common(p, n0, n1, &g);
+  if (rc) return rc;
+  if (!grad_columns || !grad_input) return fail(DCN_ERR_ARG, "grad_columns and grad_input must be non-NULL");
+  Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
+  cudaError_t e = launch_bwd_input(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), grad_columns, grad_input, (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "input-gradient kernel launch: %s", cudaGetErrorString(e));
+}
+
+int dcn_bwd_coord(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *grad_columns,
+                  float *grad_offset, float *grad_mask, void *stream) {
+  Geom g;
+  int rc = bwd_common(p, n0, n1, &g);
+  if (rc) return rc;
+  if (!grad_columns || !grad_offset) return fail(DCN_ERR_ARG, "grad_columns and grad_offset must be non-NULL");
+  Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
+  cudaError_t e = launch_bwd_coord(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), grad_columns, grad_offset, grad_mask, (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "coordinate-gradient kernel launch: %s", cudaGetErrorString(e));
+}
+
 int dcn_read_counters(const void *workspace, void *stream, uint64_t counters[24]) {
   if (!workspace || !counters) return fail(DCN_ERR_ARG, "workspace and counters must be non-NULL");
   cudaError_t e = cudaMemcpyAsync(counters, (const uint8_t *)workspace + 64, 24 * sizeof(uint64_t),

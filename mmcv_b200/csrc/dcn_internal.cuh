@@ -119,6 +119,13 @@ cudaError_t launch_clear_status(int *status, cudaStream_t s);
 
 int tc_threads(const TcPlan &tp);
 
+cudaError_t launch_bwd_columns(const Geom &g, const Ptrs &p, int dtype, int n0, int ns, float *col,
+                               cudaStream_t s);
+cudaError_t launch_bwd_input(const Geom &g, const Ptrs &p, int dtype, int n0, int ns,
+                             const float *gcol, float *gin, cudaStream_t s);
+cudaError_t launch_bwd_coord(const Geom &g, const Ptrs &p, int dtype, int n0, int ns,
+                             const float *gcol, float *goff, float *gmsk, cudaStream_t s);
+
 // Records `msg` as the calling thread's dcn_last_error() text and returns `code`.
 int set_error(int code, const char *msg);
 

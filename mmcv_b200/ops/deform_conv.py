@@ -8,6 +8,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch import Tensor
 from torch.autograd import Function
+from torch.autograd.function import once_differentiable
 from torch.nn.modules.utils import _pair, _single
 
 from .. import _ext as ext_module
@@ -43,23 +44,28 @@ class DeformConv2dFunction(Function):
         return output
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, grad_output):
         input, offset, weight = ctx.saved_tensors
-        grad_input = torch.zeros_like(input)
-        grad_offset = torch.zeros_like(offset)
-        grad_weight = torch.zeros_like(weight)
+        grad_input = grad_offset = grad_weight = None
         step = min(ctx.im2col_step, input.size(0))
+        assert (input.size(0) % step) == 0, 'batch size must be divisible by im2col_step'
         common = dict(kW=weight.size(3), kH=weight.size(2), dW=ctx.stride[1], dH=ctx.stride[0],
                       padW=ctx.padding[1], padH=ctx.padding[0], dilationW=ctx.dilation[1],
                       dilationH=ctx.dilation[0], group=ctx.groups,
                       deformable_group=ctx.deform_groups)
         grad_output = grad_output.contiguous()
-        ext_module.deform_conv_backward_input(input, offset, grad_output, grad_input,
-                                              grad_offset, weight, ctx.bufs_[0],
-                                              im2col_step=step, **common)
-        ext_module.deform_conv_backward_parameters(input, offset, grad_output, grad_weight,
-                                                   ctx.bufs_[0], ctx.bufs_[1], scale=1,
-                                                   im2col_step=step, **common)
+        if ctx.needs_input_grad[0] or ctx.needs_input_grad[1]:
+            grad_input = torch.zeros_like(input)
+            grad_offset = torch.zeros_like(offset)
+            ext_module.deform_conv_backward_input(input, offset, grad_output, grad_input,
+                                                  grad_offset, weight, ctx.bufs_[0],
+                                                  im2col_step=step, **common)
+        if ctx.needs_input_grad[2]:
+            grad_weight = torch.zeros_like(weight)
+            ext_module.deform_conv_backward_parameters(input, offset, grad_output, grad_weight,
+                                                       ctx.bufs_[0], ctx.bufs_[1], scale=1,
+                                                       im2col_step=step, **common)
         return grad_input, grad_offset, grad_weight, None, None, None, None, None, None, None
 
 

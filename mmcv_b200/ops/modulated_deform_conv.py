@@ -11,6 +11,7 @@ from typing import Optional, Tuple, Union
 import torch
 import torch.nn as nn
 from torch.autograd import Function
+from torch.autograd.function import once_differentiable
 from torch.nn.modules.utils import _pair, _single
 
 from .. import _ext as ext_module
@@ -58,6 +59,7 @@ class ModulatedDeformConv2dFunction(Function):
         return output
 
     @staticmethod
+    @once_differentiable
     def backward(ctx, grad_output):
         input, offset, mask, weight, bias = ctx.saved_tensors
         grads = [torch.zeros_like(t) for t in (input, offset, mask, weight, bias)]

@@ -119,21 +119,33 @@ def reference_kat(v2, v1):
     kat = {}
     a = module_literals(
         os.path.join(REF_ROOT, 'tests/test_ops/test_modulated_deform_conv.py'),
-        ['input_t', 'output_t'])
+        ['input_t', 'output_t', 'input_grad', 'dcn_w_grad', 'dcn_offset_w_grad',
+         'dcn_offset_b_grad'])
     # Same construction as the reference test (its lines 51-85), forward part.
     x = torch.tensor(a['input_t'], dtype=torch.float)
     dcn = v2.ModulatedDeformConv2dPack(1, 1, kernel_size=(2, 2), stride=1,
                                        padding=1, deform_groups=1, bias=False)
     dcn.weight.data.fill_(1.)
+    x.requires_grad = True
     y = dcn(x)
+    y.sum().backward()
     assert np.allclose(y.detach().numpy(), a['output_t'], 1e-2)
+    # the reference test's gradient vectors, confirmed against the reference itself
+    assert np.allclose(x.grad.numpy(), a['input_grad'], 1e-2)
+    assert np.allclose(dcn.weight.grad.numpy(), a['dcn_w_grad'], 1e-2)
+    assert np.allclose(dcn.conv_offset.weight.grad.numpy(), a['dcn_offset_w_grad'], 1e-2)
+    assert np.allclose(dcn.conv_offset.bias.grad.numpy(), a['dcn_offset_b_grad'], 1e-2)
+    for k in ('input_grad', 'dcn_w_grad', 'dcn_offset_w_grad', 'dcn_offset_b_grad'):
+        kat['v2_' + k] = np.array(a[k], dtype=np.float32)
+    x = x.detach()
     kat['v2_input'] = x.numpy()
     kat['v2_expected'] = np.array(a['output_t'], dtype=np.float32)
     kat['v2_ref_out'] = y.detach().numpy()
 
     b = module_literals(
         os.path.join(REF_ROOT, 'tests/test_ops/test_deform_conv.py'),
-        ['input', 'offset_weight', 'offset_bias', 'deform_weight', 'gt_out'])
+        ['input', 'offset_weight', 'offset_bias', 'deform_weight', 'gt_out', 'gt_x_grad',
+         'gt_offset_weight_grad', 'gt_offset_bias_grad', 'gt_deform_weight_grad'])
     batch = 10
     x = torch.tensor(np.repeat(b['input'], batch, axis=0), dtype=torch.float)
     m = v1.DeformConv2dPack(in_channels=1, out_channels=1, kernel_size=2,
@@ -141,9 +153,24 @@ def reference_kat(v2, v1):
     m.conv_offset.weight.data = torch.Tensor(b['offset_weight']).reshape(8, 1, 2, 2)
     m.conv_offset.bias.data = torch.Tensor(b['offset_bias']).reshape(8)
     m.weight.data = torch.Tensor(b['deform_weight']).reshape(1, 1, 2, 2)
+    x.requires_grad = True
     y = m(x)
+    y.backward(torch.ones_like(y))
     # The reference runs this case on CPU with a relative tolerance of 1e-1.
     assert np.allclose(y.detach().numpy(), np.repeat(b['gt_out'], batch, axis=0), 1e-1)
+    assert np.allclose(x.grad.numpy(), np.repeat(b['gt_x_grad'], batch, axis=0), 1e-1)
+    assert np.allclose(m.conv_offset.weight.grad.numpy() / batch, b['gt_offset_weight_grad'], 1e-1)
+    assert np.allclose(m.weight.grad.numpy() / batch, b['gt_deform_weight_grad'], 1e-1)
+    kat['v1_x_grad'] = np.array(b['gt_x_grad'], dtype=np.float32)
+    kat['v1_offset_weight_grad'] = np.array(b['gt_offset_weight_grad'], dtype=np.float32)
+    kat['v1_offset_bias_grad'] = np.array(b['gt_offset_bias_grad'], dtype=np.float32).reshape(-1)
+    kat['v1_deform_weight_grad'] = np.array(b['gt_deform_weight_grad'], dtype=np.float32)
+    # full-precision gradients of the reference on this case (the vectors above are rounded)
+    kat['v1_ref_x_grad'] = x.grad.numpy().copy()
+    kat['v1_ref_offset_weight_grad'] = m.conv_offset.weight.grad.numpy().copy()
+    kat['v1_ref_offset_bias_grad'] = m.conv_offset.bias.grad.numpy().copy()
+    kat['v1_ref_deform_weight_grad'] = m.weight.grad.numpy().copy()
+    x = x.detach()
     kat['v1_input'] = np.array(b['input'], dtype=np.float32)
     kat['v1_offset_weight'] = np.array(b['offset_weight'], dtype=np.float32).reshape(8, 1, 2, 2)
     kat['v1_offset_bias'] = np.array(b['offset_bias'], dtype=np.float32)

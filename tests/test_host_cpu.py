@@ -116,11 +116,27 @@ def test_kernel_shape_mismatch_is_runtime_error():
             pad_w=1, dilation_h=1, dilation_w=1, group=2, deformable_group=1, with_bias=False)
 
 
-def test_backward_entries_exist_and_raise():
-    for name in ('modulated_deform_conv_backward', 'deform_conv_backward_input',
-                 'deform_conv_backward_parameters'):
-        with pytest.raises(RuntimeError, match='not implemented'):
-            getattr(_ext, name)()
+def test_backward_entries_fail_loudly_on_cpu_tensors():
+    x = torch.randn(1, 4, 5, 5)
+    w = torch.randn(4, 4, 3, 3)
+    e = x.new_empty(0)
+    off, msk = torch.zeros(1, 18, 5, 5), torch.ones(1, 9, 5, 5)
+    with pytest.raises(RuntimeError, match='CUDA tensor'):
+        _ext.modulated_deform_conv_backward(
+            x, w, e, e, off, msk, e, torch.zeros_like(x), torch.zeros_like(w), e,
+            torch.zeros_like(off), torch.zeros_like(msk), torch.zeros(1, 4, 5, 5), kernel_h=3,
+            kernel_w=3, stride_h=1, stride_w=1, pad_h=1, pad_w=1, dilation_h=1, dilation_w=1,
+            group=1, deformable_group=1, with_bias=False)
+    with pytest.raises(RuntimeError, match='CUDA tensor'):
+        _ext.deform_conv_backward_input(x, off, torch.zeros(1, 4, 5, 5), torch.zeros_like(x),
+                                        torch.zeros_like(off), w, e, kW=3, kH=3, dW=1, dH=1,
+                                        padW=1, padH=1, dilationW=1, dilationH=1, group=1,
+                                        deformable_group=1, im2col_step=1)
+    with pytest.raises(RuntimeError, match='CUDA tensor'):
+        _ext.deform_conv_backward_parameters(x, off, torch.zeros(1, 4, 5, 5), torch.zeros_like(w),
+                                             e, e, kW=3, kH=3, dW=1, dH=1, padW=1, padH=1,
+                                             dilationW=1, dilationH=1, group=1,
+                                             deformable_group=1, scale=1, im2col_step=1)
 
 
 def test_module_interface_matches_reference_contract():
