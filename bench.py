@@ -329,6 +329,78 @@ def run_c4(args, rank, world, local):
         dist.destroy_process_group()
 
 
+def run_backward(args, wl):
+    """Forward + backward of one layer through autograd on one GPU (training step of the
+    operator): device time per step and the reference CPU path on a two-sample slice."""
+    import oracle
+    from mmcv_b200.ops import deform_conv2d, modulated_deform_conv2d
+    dev = torch.device('cuda', 0)
+    dtype = torch.bfloat16 if args.dtype == 'bf16' else torch.float32
+    x, off, msk, w, b = make_inputs(wl, 0, wl['N'], dev, dtype)
+    leaves = [t.requires_grad_(True) for t in (x, off, msk, w, b) if t is not None]
+    st, pd, dl = (wl['s'],) * 2, (wl['p'],) * 2, (wl['d'],) * 2
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        if msk is not None:
+            y = modulated_deform_conv2d(x, off, msk, w, b, st, pd, dl, wl['g'], wl['dg'])
+        else:
+            y = deform_conv2d(x, off, w, st, pd, dl, wl['g'], wl['dg'], False, 32)
+        y.backward(torch.ones_like(y))
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / args.steps
+    fl, _, Ho, Wo = flops_and_bytes(wl, wl['N'], 2)
+    line = dict(metric='dcn_fwd_bwd_tflops', value=3 * fl / (ms * 1e-3) / 1e12, unit='TFLOP/s',
+                n_gpus=1, steps=args.steps, warmup=args.warmup, ms_per_step=ms,
+                higher_is_better=True, dtype=args.dtype, data='synthetic',
+                config=dict(workload=args.workload + ': ' + wl['desc'] + ' ' + args.dtype +
+                            ', forward + backward (3x forward FLOPs)'))
+    if oracle.have_ref() and not args.no_cpu_baseline:
+        ext = oracle.load_ref()
+        n = min(2, wl['N'])
+        c = lambda t: None if t is None else t[:n].detach().float().cpu().contiguous()
+        cx, coff, cm = c(x), c(off), c(msk)
+        cw, cb = w.detach().float().cpu(), (None if b is None else b.detach().float().cpu())
+        gy = torch.ones(n, wl['Co'], Ho, Wo)
+        e = cx.new_empty(0)
+        t0 = time.perf_counter()
+        oracle.ref_forward(cx, coff, cm, cw, cb, wl['s'], wl['p'], wl['d'], wl['g'], wl['dg'])
+        if cm is not None:
+            ext.modulated_deform_conv_backward(
+                cx, cw, cb if cb is not None else e, e.clone(), coff, cm, e.clone(),
+                torch.zeros_like(cx), torch.zeros_like(cw),
+                torch.zeros_like(cb) if cb is not None else e.clone(), torch.zeros_like(coff),
+                torch.zeros_like(cm), gy, kernel_h=wl['k'], kernel_w=wl['k'], stride_h=wl['s'],
+                stride_w=wl['s'], pad_h=wl['p'], pad_w=wl['p'], dilation_h=wl['d'],
+                dilation_w=wl['d'], group=wl['g'], deformable_group=wl['dg'],
+                with_bias=cb is not None)
+        else:
+            kw = dict(kW=wl['k'], kH=wl['k'], dW=wl['s'], dH=wl['s'], padW=wl['p'], padH=wl['p'],
+                      dilationW=wl['d'], dilationH=wl['d'], group=wl['g'],
+                      deformable_group=wl['dg'], im2col_step=n)
+            ext.deform_conv_backward_input(cx, coff, gy, torch.zeros_like(cx),
+                                           torch.zeros_like(coff), cw, e.clone(), **kw)
+            ext.deform_conv_backward_parameters(cx, coff, gy, torch.zeros_like(cw), e.clone(),
+                                                e.clone(), scale=1.0, **kw)
+        dt = time.perf_counter() - t0
+        fl2, _, _, _ = flops_and_bytes(wl, n, 2)
+        line['cpu_baseline'] = dict(value=3 * fl2 / dt / 1e12, unit='TFLOP/s',
+                                    cores=torch.get_num_threads(), kind='reference',
+                                    sample=f'{n} of {wl["N"]} samples, forward + backward, fp32, 1 call '
+                                           f'({dt:.2f} s)')
+    print(json.dumps(line), flush=True)
+
+
 def run_reference(args, wl, rank, world):
     if rank != 0:
         return
@@ -372,6 +444,8 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--backward', action='store_true',
+                    help='time forward + backward through autograd instead of the forward')
     ap.add_argument('--counters', action='store_true',
                     help='also report the in-kernel phase counters of the first CTA')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
@@ -392,6 +466,9 @@ def main():
     wl = dict(WORKLOADS[args.workload])
     if args.batch:
         wl['N'] = args.batch
+    if args.backward:
+        run_backward(args, wl)
+        return
 
     rank = int(os.environ.get('RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
