@@ -13,10 +13,20 @@ from torch.nn.modules.utils import _pair, _single
 
 from .. import _ext as ext_module
 from .modulated_deform_conv import (_rename_kw, _upgrade_offset_keys, branch_dtype,
-                                    conv_output_size, fused_branch_applies, shared_layout)
+                                    conv_output_size, fused_branch_applies, register_layer,
+                                    shared_layout)
 
 
 class DeformConv2dFunction(Function):
+
+    @staticmethod
+    def symbolic(g, input, offset, weight, stride, padding, dilation, groups, deform_groups,
+                 bias=False, im2col_step=32):
+        """ONNX export node, same name and attributes as the reference emits
+        (mmcv/ops/deform_conv.py:28-50)."""
+        return g.op('mmcv::MMCVDeformConv2d', input, offset, weight, stride_i=stride,
+                    padding_i=padding, dilation_i=dilation, groups_i=groups,
+                    deform_groups_i=deform_groups, bias_i=bias, im2col_step_i=im2col_step)
 
     @staticmethod
     def forward(ctx, input, offset, weight, stride=1, padding=0, dilation=1, groups=1,
@@ -165,3 +175,6 @@ class DeformConv2dPack(DeformConv2d):
         _upgrade_offset_keys(state_dict, prefix, local_metadata)
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
                                       unexpected_keys, error_msgs)
+
+
+register_layer('DCN', DeformConv2dPack)

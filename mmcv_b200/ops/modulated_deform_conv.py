@@ -33,6 +33,16 @@ def conv_output_size(input, weight, stride, padding, dilation):
 class ModulatedDeformConv2dFunction(Function):
 
     @staticmethod
+    def symbolic(g, input, offset, mask, weight, bias, stride, padding, dilation, groups,
+                 deform_groups):
+        """ONNX export node, same name and attributes as the reference emits
+        (mmcv/ops/modulated_deform_conv.py:25-37)."""
+        tensors = [input, offset, mask, weight] + ([bias] if bias is not None else [])
+        return g.op('mmcv::MMCVModulatedDeformConv2d', *tensors, stride_i=stride,
+                    padding_i=padding, dilation_i=dilation, groups_i=groups,
+                    deform_groups_i=deform_groups)
+
+    @staticmethod
     def forward(ctx, input, offset, mask, weight, bias=None, stride=1, padding=0,
                 dilation=1, groups=1, deform_groups=1):
         if input is not None and input.dim() != 4:
@@ -156,6 +166,18 @@ def _upgrade_offset_keys(state_dict, prefix, local_metadata):
                 state_dict[new] = state_dict.pop(old)
 
 
+def register_layer(name, cls):
+    """Registers the layer under the reference's registry name ('DCN', 'DCNv2') when the
+    registry package (mmengine) is installed, so that config-driven construction
+    (mmcv/cnn/bricks/conv.py:14-51) finds it; a no-op otherwise."""
+    try:
+        from mmengine.registry import MODELS
+    except Exception:   # mmengine is optional here
+        return cls
+    MODELS.register_module(name, force=True, module=cls)
+    return cls
+
+
 class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
     """DCNv2 layer that predicts its own offsets and mask with a plain convolution
     (registry name 'DCNv2'; reference lines 289-363)."""
@@ -201,3 +223,6 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
         _upgrade_offset_keys(state_dict, prefix, local_metadata)
         super()._load_from_state_dict(state_dict, prefix, local_metadata, strict, missing_keys,
                                       unexpected_keys, error_msgs)
+
+
+register_layer('DCNv2', ModulatedDeformConv2dPack)

@@ -135,3 +135,39 @@ def test_pack_layers_with_fused_branch():
                                   None if msk is None else msk.contiguous(),
                                   layer.weight.float().cpu(), bias, 1, 1, 1, 1, dg)
         assert rel_l2(fused, ref) <= 2e-2
+
+
+def test_forward_is_capturable_in_a_cuda_graph():
+    # the C ABI neither allocates nor synchronises: a forward with a caller-held workspace can
+    # be captured once and replayed on new input contents
+    import ctypes
+    from mmcv_b200 import _lib
+    from test_zz_no_alloc import _params
+    lib = _lib.load()
+    dev = torch.device('cuda:0')
+    m, t = golden_cases().get('v2_c64')
+    t = {k: (None if v is None else v.to(dev, torch.bfloat16).contiguous())
+         for k, v in t.items() if k in ('x', 'offset', 'mask', 'weight', 'bias')}
+    out = torch.zeros(1, 64, 12, 12, device=dev, dtype=torch.bfloat16)
+    p = _params(t, m, out, 0)
+    n = ctypes.c_size_t(0)
+    _lib.check(lib.dcn_fwd_workspace_bytes(ctypes.byref(p), ctypes.byref(n)))
+    ws = torch.empty(n.value, dtype=torch.uint8, device=dev)
+    side = torch.cuda.Stream(dev)
+    with torch.cuda.stream(side):
+        sptr = ctypes.c_void_p(side.cuda_stream)
+        _lib.check(lib.dcn_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), n.value, sptr))
+        side.synchronize()
+        eager = out.clone()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            _lib.check(lib.dcn_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), n.value,
+                                   ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)))
+        out.zero_()
+        graph.replay()
+        side.synchronize()
+        assert torch.equal(out, eager)
+        t['x'].mul_(2)                  # new input contents, same buffers
+        graph.replay()
+        side.synchronize()
+    assert rel_l2(out.float().cpu(), (2 * eager.float()).cpu()) < 1e-2

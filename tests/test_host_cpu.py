@@ -206,3 +206,21 @@ def test_reference_wrappers_accept_this_extension():
             v1.DeformConv2dPack(4, 4, 3, padding=1)(torch.randn(1, 4, 6, 6))
     finally:
         ref_wrappers.unload()
+
+
+def test_onnx_symbolic_names_match_the_reference():
+    from mmcv_b200.ops import DeformConv2dFunction, ModulatedDeformConv2dFunction
+
+    class G:
+        def op(self, name, *tensors, **attrs):
+            return name, len(tensors), attrs
+
+    name, n, attrs = ModulatedDeformConv2dFunction.symbolic(G(), 1, 2, 3, 4, 5, (1, 1), (1, 1),
+                                                            (1, 1), 1, 2)
+    assert name == 'mmcv::MMCVModulatedDeformConv2d' and n == 5
+    assert set(attrs) == {'stride_i', 'padding_i', 'dilation_i', 'groups_i', 'deform_groups_i'}
+    name, n, attrs = ModulatedDeformConv2dFunction.symbolic(G(), 1, 2, 3, 4, None, 1, 1, 1, 1, 1)
+    assert n == 4
+    name, n, attrs = DeformConv2dFunction.symbolic(G(), 1, 2, 3, 1, 0, 1, 1, 1)
+    assert name == 'mmcv::MMCVDeformConv2d' and n == 3
+    assert attrs['bias_i'] is False and attrs['im2col_step_i'] == 32
