@@ -170,4 +170,8 @@ def test_forward_is_capturable_in_a_cuda_graph():
         t['x'].mul_(2)                  # new input contents, same buffers
         graph.replay()
         side.synchronize()
-    assert rel_l2(out.float().cpu(), (2 * eager.float()).cpu()) < 1e-2
+        replayed = out.clone()
+        _lib.check(lib.dcn_fwd(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), n.value, sptr))
+        side.synchronize()
+    assert not torch.equal(replayed, eager)
+    assert torch.equal(replayed, out)   # replay on new contents == eager run on them
