@@ -21,17 +21,18 @@ extern "C" {
 
 #define DCN_ABI_VERSION 1
 
-enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1 };
+enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
 /* Arithmetic of the contraction.
- *   BF16   tcgen05 kind::f16 MMA on bf16 operands, fp32 accumulation in tensor memory.
+ *   BF16   tcgen05 kind::f16 MMA on 16-bit operands in the tensors' own 16-bit type (bf16
+ *          or fp16), fp32 accumulation in tensor memory.
  *   TF32X3 fp32 tensors only: tcgen05 kind::tf32 MMA, every operand split into a TF32 high
  *          part and a remainder, three products per step (hi*hi + lo*hi + hi*lo); meets the
  *          same fp32 error bound as FFMA.  Shapes the tensor-core kernel does not take
  *          (it needs C/groups % 4 == 0 and C/deformable_group % 4 == 0) run on the FFMA
  *          kernel instead.
  *   FFMA   fp32 fused multiply-add on the SIMT cores, any shape.
- *   AUTO   BF16 for bf16 tensors, TF32X3 for fp32 tensors. */
+ *   AUTO   BF16 for bf16 and fp16 tensors, TF32X3 for fp32 tensors. */
 enum { DCN_MATH_AUTO = 0, DCN_MATH_FFMA = 1, DCN_MATH_TF32X3 = 2, DCN_MATH_BF16 = 3 };
 
 enum {

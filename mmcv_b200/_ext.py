@@ -39,7 +39,10 @@ def _dtype_code(t):
         return _lib.DTYPE_F32
     if t.dtype == torch.bfloat16:
         return _lib.DTYPE_BF16
-    raise RuntimeError(f'dcn_b200: unsupported dtype {t.dtype} (float32 and bfloat16 only)')
+    if t.dtype == torch.float16:
+        return _lib.DTYPE_F16
+    raise RuntimeError(f'dcn_b200: unsupported dtype {t.dtype} (float32, bfloat16 and float16 '
+                       'only)')
 
 
 def _require_cuda(**tensors):
@@ -75,7 +78,7 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
         if t is not None and t.dtype != input.dtype:
             raise RuntimeError(f'dcn_b200: {name} has dtype {t.dtype}, input has {input.dtype}')
     if math_mode is None:
-        math_mode = _lib.MATH_AUTO if code == _lib.DTYPE_BF16 else _FP32_MATH[_fp32_math]
+        math_mode = _FP32_MATH[_fp32_math] if code == _lib.DTYPE_F32 else _lib.MATH_AUTO
     p = _lib.DcnFwdParams()
     p.input, p.offset, p.mask = _ptr(input), _ptr(offset), _ptr(mask)
     p.weight, p.bias, p.output = _ptr(weight), _ptr(bias), _ptr(output)

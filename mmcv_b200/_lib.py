@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, 'lib', 'libdcn_b200.so')
 
-DTYPE_F32, DTYPE_BF16 = 0, 1
+DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
 MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1

@@ -53,8 +53,9 @@ int env_int(const char *name, int dflt, int lo, int hi) {
 
 int build_geom(const DcnFwdParams *p, Geom *g) {
   if (!p) return fail(DCN_ERR_ARG, "params is NULL");
-  if (p->dtype != DCN_DTYPE_F32 && p->dtype != DCN_DTYPE_BF16)
-    return fail(DCN_ERR_UNSUPPORTED, "unsupported element type %d (fp32 and bf16 only)", p->dtype);
+  if (p->dtype != DCN_DTYPE_F32 && p->dtype != DCN_DTYPE_BF16 && p->dtype != DCN_DTYPE_F16)
+    return fail(DCN_ERR_UNSUPPORTED, "unsupported element type %d (fp32, bf16 and fp16 only)",
+                p->dtype);
   if (p->math_mode < DCN_MATH_AUTO || p->math_mode > DCN_MATH_BF16)
     return fail(DCN_ERR_ARG, "unknown math mode %d", p->math_mode);
   if (p->kh <= 0 || p->kw <= 0)
@@ -118,14 +119,15 @@ int build_geom(const DcnFwdParams *p, Geom *g) {
 
 // The input can be gathered from where it lies: channels-last, dense, and already in the
 // element type the mode samples (bf16 for the bf16 contraction, fp32 for TF32x3).
-bool input_is_ready(const DcnFwdParams *p, const Geom &g, bool tf32) {
-  return p->dtype == (tf32 ? DCN_DTYPE_F32 : DCN_DTYPE_BF16) && g.in_sc == 1 && g.in_sw == g.C &&
+bool input_is_ready(const DcnFwdParams *p, const Geom &g, int op_format) {
+  const int want = op_format == 2 ? DCN_DTYPE_F32 : (op_format == 0 ? DCN_DTYPE_F16 : DCN_DTYPE_BF16);
+  return p->dtype == want && g.in_sc == 1 && g.in_sw == g.C &&
          g.in_sh == (long long)g.W * g.C && g.in_sn == (long long)g.H * g.W * g.C;
 }
 
 int resolved_math(const DcnFwdParams *p) {
   return p->math_mode == DCN_MATH_AUTO
-             ? (p->dtype == DCN_DTYPE_BF16 ? DCN_MATH_BF16 : DCN_MATH_TF32X3)
+             ? (p->dtype == DCN_DTYPE_F32 ? DCN_MATH_TF32X3 : DCN_MATH_BF16)
              : p->math_mode;
 }
 
@@ -147,6 +149,9 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   for (int cap = 256; cap >= 32 && !found; cap /= 2) {
     memset(tp, 0, sizeof(*tp));
     tp->tiles_per_stage = tf32 ? 2 : 1;
+    // 16-bit operands are in the tensors' own 16-bit type; fp32 tensors asked to run the
+    // 16-bit contraction use bf16
+    tp->op_format = tf32 ? 2 : (p->dtype == DCN_DTYPE_F16 ? 0 : 1);
     tp->ch_per_stage = ch;
     tp->NT = (g.Cog + cap - 1) / cap;
     const int per = (g.Cog + tp->NT - 1) / tp->NT;
@@ -228,7 +233,7 @@ void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPla
     ws->wtile_off = off;
     ws->wtile_bytes = (size_t)g.groups * tp.NT * tp.S * tp.BN * 128 * tp.tiles_per_stage;
     off = align_up(off + ws->wtile_bytes, 256);
-    if (!input_is_ready(p, g, tp.tiles_per_stage == 2)) {
+    if (!input_is_ready(p, g, tp.op_format)) {
       ws->xcl_off = off;
       ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * (tp.tiles_per_stage == 2 ? 4 : 2);
       off = align_up(off + ws->xcl_bytes, 256);
@@ -376,7 +381,7 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   const void *xcl = p->input;
   if (pl.stage) {
     void *dst = ws + pl.ws.xcl_off;
-    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.tiles_per_stage == 2, s);
+    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.op_format, s);
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
     xcl = dst;
   }

@@ -179,6 +179,9 @@ cudaError_t launch_bwd_columns(const Geom &g, const Ptrs &p, int dtype, int n0, 
   if (dtype == DCN_DTYPE_F32)
     dcn_bwd_columns_kernel<float><<<grid_for(total), 256, 0, s>>>(
         g, (const float *)p.input, (const float *)p.offset, (const float *)p.mask, n0, ns, col);
+  else if (dtype == DCN_DTYPE_F16)
+    dcn_bwd_columns_kernel<__half><<<grid_for(total), 256, 0, s>>>(
+        g, (const __half *)p.input, (const __half *)p.offset, (const __half *)p.mask, n0, ns, col);
   else
     dcn_bwd_columns_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>(
         g, (const __nv_bfloat16 *)p.input, (const __nv_bfloat16 *)p.offset,
@@ -193,6 +196,9 @@ cudaError_t launch_bwd_input(const Geom &g, const Ptrs &p, int dtype, int n0, in
   if (dtype == DCN_DTYPE_F32)
     dcn_bwd_input_kernel<float><<<grid_for(total), 256, 0, s>>>(
         g, (const float *)p.offset, (const float *)p.mask, n0, ns, gcol, gin);
+  else if (dtype == DCN_DTYPE_F16)
+    dcn_bwd_input_kernel<__half><<<grid_for(total), 256, 0, s>>>(
+        g, (const __half *)p.offset, (const __half *)p.mask, n0, ns, gcol, gin);
   else
     dcn_bwd_input_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>(
         g, (const __nv_bfloat16 *)p.offset, (const __nv_bfloat16 *)p.mask, n0, ns, gcol, gin);
@@ -206,6 +212,10 @@ cudaError_t launch_bwd_coord(const Geom &g, const Ptrs &p, int dtype, int n0, in
   if (dtype == DCN_DTYPE_F32)
     dcn_bwd_coord_kernel<float><<<grid_for(total), 256, 0, s>>>(
         g, (const float *)p.input, (const float *)p.offset, (const float *)p.mask, n0, ns, gcol,
+        goff, gmsk);
+  else if (dtype == DCN_DTYPE_F16)
+    dcn_bwd_coord_kernel<__half><<<grid_for(total), 256, 0, s>>>(
+        g, (const __half *)p.input, (const __half *)p.offset, (const __half *)p.mask, n0, ns, gcol,
         goff, gmsk);
   else
     dcn_bwd_coord_kernel<__nv_bfloat16><<<grid_for(total), 256, 0, s>>>(

@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -51,7 +52,8 @@ struct TcPlan {
   size_t smem;
   int tw_log2;             // tile = (128 >> tw_log2) x (1 << tw_log2) output pixels of one sample
   int tiles_x, tiles_y;    // tiles per sample
-  int tiles_per_stage;     // 1: bf16 operands; 2: TF32x3 (high part and remainder)
+  int tiles_per_stage;     // 1: 16-bit operands; 2: TF32x3 (high part and remainder)
+  int op_format;           // tensor-core operand format: 0 fp16, 1 bf16, 2 tf32
   int ch_per_stage;        // input channels per k-stage: 64 (bf16) or 32 (TF32x3)
   int producer_cfg;        // groups*100 + warps_per_group*10 + rows in flight per thread
 };
@@ -91,6 +93,12 @@ __device__ __forceinline__ float ld_as_float(const float *p, long long i) { retu
 __device__ __forceinline__ float ld_as_float(const __nv_bfloat16 *p, long long i) {
   return __bfloat162float(p[i]);
 }
+__device__ __forceinline__ float ld_as_float(const __half *p, long long i) {
+  return __half2float(p[i]);
+}
+__device__ __forceinline__ void st_from_float(__half *p, long long i, float v) {
+  p[i] = __float2half_rn(v);
+}
 __device__ __forceinline__ void st_from_float(float *p, long long i, float v) { p[i] = v; }
 __device__ __forceinline__ void st_from_float(__nv_bfloat16 *p, long long i, float v) {
   p[i] = __float2bfloat16_rn(v);
@@ -109,7 +117,7 @@ size_t simt_tiled_smem(const Geom &g);
 bool simt_tiled_supported(const Geom &g);
 
 cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
-                                  bool to_fp32, cudaStream_t s);
+                                  int op_format, cudaStream_t s);
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight,
                                 int dtype, void *wtiles, cudaStream_t s);
 cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,

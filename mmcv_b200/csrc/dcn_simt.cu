@@ -78,6 +78,10 @@ cudaError_t launch_simt_direct(const Geom &g, const Ptrs &p, int dtype, cudaStre
     dcn_fwd_simt_direct<float><<<(int)blocks, block, 0, s>>>(
         g, (const float *)p.input, (const float *)p.offset, (const float *)p.mask,
         (const float *)p.weight, (const float *)p.bias, (float *)p.output);
+  else if (dtype == DCN_DTYPE_F16)
+    dcn_fwd_simt_direct<__half><<<(int)blocks, block, 0, s>>>(
+        g, (const __half *)p.input, (const __half *)p.offset, (const __half *)p.mask,
+        (const __half *)p.weight, (const __half *)p.bias, (__half *)p.output);
   else
     dcn_fwd_simt_direct<__nv_bfloat16><<<(int)blocks, block, 0, s>>>(
         g, (const __nv_bfloat16 *)p.input, (const __nv_bfloat16 *)p.offset,
@@ -243,6 +247,13 @@ cudaError_t launch_simt_tiled(const Geom &g, const Ptrs &p, int dtype, cudaStrea
     dcn_fwd_simt_tiled<float><<<(unsigned)blocks, 256, smem, s>>>(
         g, (const float *)p.input, (const float *)p.offset, (const float *)p.mask,
         (const float *)p.weight, (const float *)p.bias, (float *)p.output, tiles_x, tiles_y, n_ctile);
+  } else if (dtype == DCN_DTYPE_F16) {
+    e = cudaFuncSetAttribute(dcn_fwd_simt_tiled<__half>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    dcn_fwd_simt_tiled<__half><<<(unsigned)blocks, 256, smem, s>>>(
+        g, (const __half *)p.input, (const __half *)p.offset, (const __half *)p.mask,
+        (const __half *)p.weight, (const __half *)p.bias, (__half *)p.output, tiles_x, tiles_y,
+        n_ctile);
   } else {
     e = cudaFuncSetAttribute(dcn_fwd_simt_tiled<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;

@@ -38,13 +38,17 @@ constexpr int kTileBytes = kBM * 128;  // one operand tile: 128 rows of 128 byte
 
 // Arithmetic modes of the contraction.
 //  kModeBf16:   bf16 operands, one operand tile per stage, 64 channels per stage;
+//  kModeF16:    the same with fp16 operands;
 //  kModeTf32x3: fp32 data split into a TF32 high part and a remainder (a = hi + lo, both
 //               held as fp32 bit patterns; the tensor core reads their top 19 bits), two
 //               operand tiles per stage, 32 channels per stage, three MMAs per k-step:
 //               hi*hi + lo*hi + hi*lo with fp32 accumulation.
-enum { kModeBf16 = 0, kModeTf32x3 = 1 };
+enum { kModeBf16 = 0, kModeTf32x3 = 1, kModeF16 = 2 };
 template <int MODE> struct ModeTraits;
 template <> struct ModeTraits<kModeBf16> {
+  static constexpr int kCh = 64, kCpv = 8, kEsz = 2, kTiles = 1;
+};
+template <> struct ModeTraits<kModeF16> {
   static constexpr int kCh = 64, kCpv = 8, kEsz = 2, kTiles = 1;
 };
 template <> struct ModeTraits<kModeTf32x3> {
@@ -156,12 +160,27 @@ __device__ __forceinline__ unsigned short ldg_raw_ordered(const __nv_bfloat16 *p
   asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
   return v;
 }
-__device__ __forceinline__ float raw_to_float(uint32_t v) { return __uint_as_float(v); }
-__device__ __forceinline__ float raw_to_float(unsigned short v) {
-  return __uint_as_float((uint32_t)v << 16);
+__device__ __forceinline__ unsigned short ldg_raw_ordered(const __half *p) {
+  unsigned short v;
+  asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
+  return v;
 }
-template <typename T> struct RawOf { using type = uint32_t; };
-template <> struct RawOf<__nv_bfloat16> { using type = unsigned short; };
+template <typename T> struct RawOf {
+  using type = uint32_t;
+  static __device__ __forceinline__ float to_float(uint32_t v) { return __uint_as_float(v); }
+};
+template <> struct RawOf<__nv_bfloat16> {
+  using type = unsigned short;
+  static __device__ __forceinline__ float to_float(unsigned short v) {
+    return __uint_as_float((uint32_t)v << 16);
+  }
+};
+template <> struct RawOf<__half> {
+  using type = unsigned short;
+  static __device__ __forceinline__ float to_float(unsigned short v) {
+    return __half2float(__ushort_as_half(v));
+  }
+};
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -260,6 +279,27 @@ __device__ __forceinline__ uint4 blend8_bf16(const uint4 &w, const uint4 &q0, co
     t = __hfma2(w2, as_bf162(a2[i]), t);
     t = __hfma2(w3, as_bf162(a3[i]), t);
     r[i] = bf162_bits(t);
+  }
+  return o;
+}
+
+// The same blend on packed fp16 FMAs (fp16 tensors).
+__device__ __forceinline__ uint4 blend8_f16(const uint4 &w, const uint4 &q0, const uint4 &q1,
+                                            const uint4 &q2, const uint4 &q3) {
+  uint4 o;
+  const __half2 *wh = reinterpret_cast<const __half2 *>(&w);
+  const __half2 *a0 = reinterpret_cast<const __half2 *>(&q0);
+  const __half2 *a1 = reinterpret_cast<const __half2 *>(&q1);
+  const __half2 *a2 = reinterpret_cast<const __half2 *>(&q2);
+  const __half2 *a3 = reinterpret_cast<const __half2 *>(&q3);
+  __half2 *r = reinterpret_cast<__half2 *>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __half2 t = __hmul2(wh[0], a0[i]);
+    t = __hfma2(wh[1], a1[i], t);
+    t = __hfma2(wh[2], a2[i], t);
+    t = __hfma2(wh[3], a3[i], t);
+    r[i] = t;
   }
   return o;
 }
@@ -455,8 +495,8 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       // fp32 accumulate, both operands K-major, M = 128 pixels, N = BN channels;
-      // operand format 1 = bf16, 2 = tf32
-      constexpr uint32_t kFmt = MODE == kModeBf16 ? 1u : 2u;
+      // operand format 0 = fp16, 1 = bf16, 2 = tf32
+      constexpr uint32_t kFmt = MODE == kModeBf16 ? 1u : (MODE == kModeF16 ? 0u : 2u);
       const uint32_t idesc = (1u << 4) | (kFmt << 7) | (kFmt << 10) |
                              ((uint32_t)(tp.BN >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
       uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
@@ -484,7 +524,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           const uint64_t adesc = smem_desc_sw128(smem_u32(L.a + (size_t)sa * kAStageBytes));
           const uint64_t bdesc = smem_desc_sw128(smem_u32(L.b + (size_t)sb * b_stage_bytes));
           // four k-steps of 32 bytes per 128-byte row: 16 bf16 or 8 tf32 elements each
-          if constexpr (MODE == kModeBf16) {
+          if constexpr (MODE != kModeTf32x3) {
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
@@ -667,8 +707,8 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                 float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
                 int h_low = 0, w_low = 0;
                 if (rvalid)
-                  tap_weights(raw_to_float(oh[k]), raw_to_float(ow[k]),
-                              mskp ? raw_to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
+                  tap_weights(RawOf<TIO>::to_float(oh[k]), RawOf<TIO>::to_float(ow[k]),
+                              mskp ? RawOf<TIO>::to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
                               wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
                 uint4 wq;
                 if constexpr (MODE == kModeBf16) {
@@ -677,6 +717,17 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   wq.z = bf162_bits(__float2bfloat162_rn(wt.z));
                   wq.w = bf162_bits(__float2bfloat162_rn(wt.w));
                   // a weight that rounds to (signed) zero is dropped: the corner is not read
+                  wq.x = (wq.x & 0x7fff7fffu) ? wq.x : 0u;
+                  wq.y = (wq.y & 0x7fff7fffu) ? wq.y : 0u;
+                  wq.z = (wq.z & 0x7fff7fffu) ? wq.z : 0u;
+                  wq.w = (wq.w & 0x7fff7fffu) ? wq.w : 0u;
+                } else if constexpr (MODE == kModeF16) {
+                  const __half2 h0 = __float2half2_rn(wt.x), h1 = __float2half2_rn(wt.y),
+                                h2 = __float2half2_rn(wt.z), h3 = __float2half2_rn(wt.w);
+                  wq.x = *reinterpret_cast<const uint32_t *>(&h0);
+                  wq.y = *reinterpret_cast<const uint32_t *>(&h1);
+                  wq.z = *reinterpret_cast<const uint32_t *>(&h2);
+                  wq.w = *reinterpret_cast<const uint32_t *>(&h3);
                   wq.x = (wq.x & 0x7fff7fffu) ? wq.x : 0u;
                   wq.y = (wq.y & 0x7fff7fffu) ? wq.y : 0u;
                   wq.z = (wq.z & 0x7fff7fffu) ? wq.z : 0u;
@@ -735,6 +786,9 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
               if constexpr (MODE == kModeBf16) {
                 *reinterpret_cast<uint4 *>(dst) =
                     blend8_bf16(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
+              } else if constexpr (MODE == kModeF16) {
+                *reinterpret_cast<uint4 *>(dst) =
+                    blend8_f16(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3]);
               } else {
                 uint4 hi, lo;
                 blend4_tf32(wq[ps], q[ps][0], q[ps][1], q[ps][2], q[ps][3], hi, lo);
@@ -806,25 +860,28 @@ dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, in
   }
 }
 
+namespace {
+template <typename T, typename TO>
+void stage_launch(const Geom &g, const void *input, void *xcl, dim3 grid, cudaStream_t s) {
+  dcn_stage_input_cl<T, TO><<<grid, 256, 0, s>>>((const T *)input, (TO *)xcl, g.C, g.H, g.W,
+                                                  g.in_sn, g.in_sc, g.in_sh, g.in_sw);
+}
+template <typename TO>
+void stage_from(const Geom &g, const void *input, int dtype, void *xcl, dim3 grid, cudaStream_t s) {
+  if (dtype == DCN_DTYPE_F32) stage_launch<float, TO>(g, input, xcl, grid, s);
+  else if (dtype == DCN_DTYPE_F16) stage_launch<__half, TO>(g, input, xcl, grid, s);
+  else stage_launch<__nv_bfloat16, TO>(g, input, xcl, grid, s);
+}
+}  // namespace
+
+// op_format: element type of the channels-last copy (0 fp16, 1 bf16, 2 fp32 for TF32x3)
 cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
-                                  bool to_fp32, cudaStream_t s) {
+                                  int op_format, cudaStream_t s) {
   if (g.N == 0) return cudaSuccess;
   dim3 grid((g.H * g.W + 31) / 32, (g.C + 31) / 32, g.N);
-  if (dtype == DCN_DTYPE_F32 && to_fp32)
-    dcn_stage_input_cl<float, float><<<grid, 256, 0, s>>>(
-        (const float *)input, (float *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh, g.in_sw);
-  else if (dtype == DCN_DTYPE_F32)
-    dcn_stage_input_cl<float, __nv_bfloat16><<<grid, 256, 0, s>>>(
-        (const float *)input, (__nv_bfloat16 *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh,
-        g.in_sw);
-  else if (to_fp32)
-    dcn_stage_input_cl<__nv_bfloat16, float><<<grid, 256, 0, s>>>(
-        (const __nv_bfloat16 *)input, (float *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc, g.in_sh,
-        g.in_sw);
-  else
-    dcn_stage_input_cl<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>(
-        (const __nv_bfloat16 *)input, (__nv_bfloat16 *)xcl, g.C, g.H, g.W, g.in_sn, g.in_sc,
-        g.in_sh, g.in_sw);
+  if (op_format == 2) stage_from<float>(g, input, dtype, xcl, grid, s);
+  else if (op_format == 0) stage_from<__half>(g, input, dtype, xcl, grid, s);
+  else stage_from<__nv_bfloat16>(g, input, dtype, xcl, grid, s);
   return cudaGetLastError();
 }
 
@@ -836,7 +893,8 @@ cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, v
 template <typename T>
 __global__ void __launch_bounds__(256)
 dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int Cog, int Tt,
-                 int BN, int NT, int S, int tf32) {
+                 int BN, int NT, int S, int op_format) {
+  const int tf32 = op_format == 2;
   const int blk = blockIdx.x;  // (grp*NT + nt)*S + ks
   const int ks = blk % S;
   const int gn = blk / S;
@@ -859,7 +917,10 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
       *reinterpret_cast<float *>(out + (size_t)BN * 128 + byte) = val - __uint_as_float(hb);
     } else {
       const int byte = r * 128 + (((j >> 3) ^ (r & 7)) << 4) + (j & 7) * 2;
-      *reinterpret_cast<__nv_bfloat16 *>(out + byte) = __float2bfloat16_rn(val);
+      if (op_format == 0)
+        *reinterpret_cast<__half *>(out + byte) = __float2half_rn(val);
+      else
+        *reinterpret_cast<__nv_bfloat16 *>(out + byte) = __float2bfloat16_rn(val);
     }
   }
 }
@@ -867,14 +928,16 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight, int dtype,
                                 void *wtiles, cudaStream_t s) {
   const int blocks = g.groups * tp.NT * tp.S;
-  const int tf32 = tp.tiles_per_stage == 2 ? 1 : 0;
   if (dtype == DCN_DTYPE_F32)
     dcn_weight_tiles<float><<<blocks, 256, 0, s>>>((const float *)weight, (uint8_t *)wtiles, g.Cg,
-                                                   g.Cog, g.T, tp.BN, tp.NT, tp.S, tf32);
+                                                   g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.op_format);
+  else if (dtype == DCN_DTYPE_F16)
+    dcn_weight_tiles<__half><<<blocks, 256, 0, s>>>((const __half *)weight, (uint8_t *)wtiles, g.Cg,
+                                                    g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.op_format);
   else
     dcn_weight_tiles<__nv_bfloat16><<<blocks, 256, 0, s>>>(
         (const __nv_bfloat16 *)weight, (uint8_t *)wtiles, g.Cg, g.Cog, g.T, tp.BN, tp.NT, tp.S,
-        tf32);
+        tp.op_format);
   return cudaGetLastError();
 }
 
@@ -926,8 +989,9 @@ cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 }
 template <typename TIO>
 cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
-  return tp.tiles_per_stage == 2 ? launch_mode<TIO, kModeTf32x3>(a, tp, s)
-                                 : launch_mode<TIO, kModeBf16>(a, tp, s);
+  if (tp.op_format == 2) return launch_mode<TIO, kModeTf32x3>(a, tp, s);
+  if (tp.op_format == 0) return launch_mode<TIO, kModeF16>(a, tp, s);
+  return launch_mode<TIO, kModeBf16>(a, tp, s);
 }
 }  // namespace
 
@@ -950,7 +1014,9 @@ cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
   a.output = p.output;
   a.status = status;
   a.counters = counters;
-  return dtype == DCN_DTYPE_F32 ? launch_io<float>(a, tp, s) : launch_io<__nv_bfloat16>(a, tp, s);
+  if (dtype == DCN_DTYPE_F32) return launch_io<float>(a, tp, s);
+  if (dtype == DCN_DTYPE_F16) return launch_io<__half>(a, tp, s);
+  return launch_io<__nv_bfloat16>(a, tp, s);
 }
 
 }  // namespace dcn

@@ -91,9 +91,10 @@ modulated_deform_conv2d = ModulatedDeformConv2dFunction.apply
 def fused_branch_applies(x, conv):
     """The offset branch runs on this library's kernel when nothing needs its gradient
     (inference); otherwise it stays an nn.Conv2d so that autograd sees it."""
-    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16):
+    if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         return False
-    if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') != torch.bfloat16:
+    if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') not in (
+            torch.bfloat16, torch.float16):
         return False
     needs_grad = torch.is_grad_enabled() and (
         x.requires_grad or any(p.requires_grad for p in conv.parameters()))
@@ -103,13 +104,13 @@ def fused_branch_applies(x, conv):
 def shared_layout(x):
     """bf16 inputs are put in channels-last order once, so that the offset branch and the
     deformable convolution both read them without a restaging pass of their own."""
-    if x.dtype == torch.bfloat16 and x.size(1) % 64 == 0:
+    if x.dtype in (torch.bfloat16, torch.float16) and x.size(1) % 8 == 0:
         return x.contiguous(memory_format=torch.channels_last)
     return x
 
 
 def branch_dtype(x):
-    return torch.bfloat16 if torch.is_autocast_enabled('cuda') else x.dtype
+    return torch.get_autocast_dtype('cuda') if torch.is_autocast_enabled('cuda') else x.dtype
 
 
 def _rename_kw(kwargs, old, new):

@@ -1,6 +1,6 @@
 """Generate the committed golden fixtures from the UNMODIFIED reference.
 
-Needs a reference checkout (default /root/reference) and the reference CPU
+Needs a reference checkout (its root in $DCN_REFERENCE_ROOT) and the reference CPU
 extension built by ``python oracle/build_oracle.py``.  Writes
 
 * ``reference_kat.npz`` -- the known-answer vectors that the reference's own

@@ -68,6 +68,28 @@ def test_functional_v1_small_input_is_padded():
     assert ok, frac
 
 
+def test_reference_half_test_flow_under_autocast(kat):
+    # the reference's AMP test (its test file, lines 87-128): fp32 module, autocast to half,
+    # forward and backward against the same vectors at its 1e-2 tolerance
+    from mmcv_b200.ops import ModulatedDeformConv2dPack
+    for in_dtype in (torch.float, torch.half):
+        x = torch.tensor(kat['v2_input'], device='cuda').type(in_dtype)
+        x.requires_grad = True
+        dcn = ModulatedDeformConv2dPack(1, 1, kernel_size=(2, 2), stride=1, padding=1,
+                                        deform_groups=1, bias=False).cuda()
+        dcn.weight.data.fill_(1.)
+        with torch.autocast('cuda', dtype=torch.half):
+            out = dcn(x)
+            out.sum().backward()
+        assert out.dtype == torch.half
+        c = lambda v: v.detach().float().cpu().numpy()
+        assert np.allclose(c(out), kat['v2_expected'], 1e-2)
+        assert np.allclose(c(x.grad), kat['v2_input_grad'], 1e-2)
+        assert np.allclose(c(dcn.weight.grad), kat['v2_dcn_w_grad'], 1e-2)
+        assert np.allclose(c(dcn.conv_offset.weight.grad), kat['v2_dcn_offset_w_grad'], 1e-2)
+        assert np.allclose(c(dcn.conv_offset.bias.grad), kat['v2_dcn_offset_b_grad'], 1e-2)
+
+
 def test_autocast_dtype_follows_offset():
     from mmcv_b200.ops import ModulatedDeformConv2dPack
     torch.manual_seed(1)

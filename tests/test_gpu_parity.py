@@ -19,7 +19,8 @@ BF16_TOL = 2e-2
 def plan_path(x, w, m, dtype, math=_lib.MATH_AUTO):
     lib = _lib.load()
     p = _lib.DcnFwdParams()
-    p.dtype = _lib.DTYPE_F32 if dtype == torch.float32 else _lib.DTYPE_BF16
+    p.dtype = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16,
+               torch.float16: _lib.DTYPE_F16}[dtype]
     p.math_mode = math
     p.N, p.C, p.H, p.W = x.shape
     p.Co, p.kh, p.kw = w.shape[0], w.shape[2], w.shape[3]
@@ -78,6 +79,33 @@ def test_golden_bf16(name):
     finite = torch.isfinite(ref)
     assert torch.equal(torch.isfinite(out.float().cpu()), finite)
     assert rel_l2(out.float().cpu()[finite], ref[finite]) <= BF16_TOL
+
+
+@pytest.mark.parametrize('name', golden_case_names())
+def test_golden_fp16(name):
+    # fp16 tensors (the reference's half coverage): checker in fp32 on the fp16-rounded inputs;
+    # fp16 keeps 3 more mantissa bits than bf16, so the bound is tighter
+    m, t = golden_cases().get(name)
+    r = rounded(t, torch.float16)
+    ref = oracle.best_forward(r['x'], r['offset'], r['mask'], r['weight'], r['bias'],
+                              m['stride'], m['padding'], m['dilation'], m['groups'],
+                              m['deform_groups'])
+    out = run_cuda(t, m, torch.float16)
+    finite = torch.isfinite(ref)
+    assert torch.equal(torch.isfinite(out.float().cpu()), finite)
+    assert rel_l2(out.float().cpu()[finite], ref[finite]) <= 4e-3
+
+
+def test_config3_fp16_on_tensor_cores():
+    m, t = synth(4, 512, 64, 64, 512, 3, 2, 2, 2, 1, 4, 8.0, True, True, int_frac=0.05,
+                 mask_sigma=2.0)
+    assert plan_path(t['x'], t['weight'], m, torch.float16).path == _lib.PATH_TCGEN05
+    out = run_cuda(t, m, torch.float16).float().cpu()
+    r = rounded(t, torch.float16)
+    ref = oracle.best_forward(r['x'], r['offset'], r['mask'], r['weight'], r['bias'],
+                              m['stride'], m['padding'], m['dilation'], m['groups'],
+                              m['deform_groups'])
+    assert rel_l2(out, ref) <= 4e-3
 
 
 @pytest.mark.parametrize('name', ['v2_c64', 'v2_c128_co40_dg4', 'v2_c128_g2_dg2_s2', 'v1_c64'])

@@ -80,6 +80,8 @@ def test_plan_rejects_what_the_reference_rejects():
         assert text in lib.dcn_last_error().decode()
     rc, _ = plan(params(dtype=7))
     assert rc == -2
+    rc, info = plan(params(dtype=_lib.DTYPE_F16))
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05
     rc, _ = plan(params(C=20, Co=20, math=_lib.MATH_BF16))
     assert rc == -2
     rc, _ = plan(params(math=_lib.MATH_TF32X3))          # bf16 tensors with the fp32-only mode
