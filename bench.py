@@ -310,7 +310,8 @@ def run_c4(args, rank, world, local):
             config=dict(workload='c4: 13 ModulatedDeformConv2dPack layers (ResNet-50-DCNv2 stages '
                                  '3-5), N=16, bf16, offset branch on the same kernel',
                         global_batch=n_total, parallelism=f'batch-shard x{world}, no collective',
-                        l2='layer inputs 53-107 MB each, 13 distinct tensors per step (> L2)'),
+                        l2='layer inputs 53-107 MB each, 13 distinct tensors per step (> L2)',
+                        frozen_weights=bool(args.frozen_weights)),
             layer_roofline=dict(ms=roof * 1e3, frac=roof * 1e3 / ms if world == 1 else None,
                                 flops=fl_r, note='sum over the 26 launches of max(FLOPs at bf16 '
                                                  'peak, compulsory bytes at HBM bandwidth)'),
@@ -322,7 +323,7 @@ def run_c4(args, rank, world, local):
                      h2d_bytes_per_step=sum(h.numel() * 2 for h in hin),
                      d2h_bytes_per_step=hout.numel() * 2, ms_per_step=e2e_ms,
                      api='mmcv_b200.ops.ModulatedDeformConv2dPack'),
-            gpu_launches=args.steps * 13 * 8, clocks=clocks)
+            gpu_launches=args.steps * 13 * (4 if args.frozen_weights else 6), clocks=clocks)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
@@ -446,6 +447,9 @@ def main():
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--backward', action='store_true',
                     help='time forward + backward through autograd instead of the forward')
+    ap.add_argument('--frozen-weights', action='store_true',
+                    help='c4 only: run the stack inside mmcv_b200.frozen_weights() (weights cast '
+                         'and re-laid-out once, as in serving)')
     ap.add_argument('--counters', action='store_true',
                     help='also report the in-kernel phase counters of the first CTA')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
@@ -460,8 +464,11 @@ def main():
             raise SystemExit('the reference arm is quoted on the single-layer workloads')
         if not torch.cuda.is_available():
             raise SystemExit('bench.py needs a CUDA device: there is no CPU path')
-        run_c4(args, int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1')),
-               int(os.environ.get('LOCAL_RANK', '0')))
+        import contextlib
+        import mmcv_b200
+        with (mmcv_b200.frozen_weights() if args.frozen_weights else contextlib.nullcontext()):
+            run_c4(args, int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1')),
+                   int(os.environ.get('LOCAL_RANK', '0')))
         return
     wl = dict(WORKLOADS[args.workload])
     if args.batch:

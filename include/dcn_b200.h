@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DCN_ABI_VERSION 1
+#define DCN_ABI_VERSION 2
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
@@ -81,6 +81,10 @@ typedef struct DcnFwdParams {
   int64_t offset_batch_stride, mask_batch_stride, out_batch_stride;
   int32_t act, act_lo, act_hi; /* DCN_ACT_* on output channels [act_lo, act_hi) */
   int32_t device;              /* CUDA device ordinal the pointers live on */
+  /* Optional: the weight image dcn_prepare_weights() wrote for these weights and this
+   * problem shape; dcn_fwd then skips its own re-layout of `weight`.  NULL = none. */
+  const void *weight_image;
+  int64_t weight_image_bytes;
 } DcnFwdParams;
 
 /* What a call will do; filled by dcn_fwd_plan without touching the device. */
@@ -116,6 +120,19 @@ int dcn_fwd_workspace_bytes(const DcnFwdParams *p, size_t *bytes);
  */
 int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes,
             void *stream);
+
+/*
+ * Weights change once per optimiser step at most, the forward runs every call: these two
+ * let a caller keep the re-laid-out (tiled, swizzled, type-converted) weights.
+ * dcn_weight_image_bytes reports the image size for the problem (0 when the problem runs on
+ * a kernel that reads `weight` directly); dcn_prepare_weights enqueues the re-layout of
+ * p->weight into `image` (device memory, 256-byte aligned).  The image depends on the
+ * weights' values, dtype and shape, groups, and the math mode; pass it back in
+ * DcnFwdParams.weight_image together with its size.  (No counterpart in the reference, which
+ * feeds `weight` to its GEMM as is.)
+ */
+int dcn_weight_image_bytes(const DcnFwdParams *p, size_t *bytes);
+int dcn_prepare_weights(const DcnFwdParams *p, void *image, size_t image_bytes, void *stream);
 
 /* Measurement aid: dcn_fwd with every kernel bracketed by CUDA events on `stream`.
  * Waits for the work to finish and reports the device time of each launch in

@@ -9,6 +9,14 @@ from . import _lib
 __version__ = '0.1.0'
 
 
+def frozen_weights():
+    """Context manager for serving and evaluation: while it is active, each layer's weights
+    are cast and re-laid-out for the tensor-core kernel once instead of on every call
+    (see ``mmcv_b200._ext.frozen_weights``)."""
+    from . import _ext
+    return _ext.frozen_weights()
+
+
 def install():
     """Make an installed ``mmcv`` use this library for the deformable-conv forward.
 

@@ -7,6 +7,7 @@ of the reference's module definition (``mmcv/ops/csrc/pytorch/pybind.cpp:525-545
 641-656``).  All five call the CUDA library through its C ABI; the backward entries
 additionally use torch.matmul for the two matrix products the reference gives to addmm_.
 """
+import contextlib
 import ctypes
 import os
 
@@ -64,6 +65,66 @@ def _ptr(t):
     return None if t is None else ctypes.c_void_p(t.data_ptr())
 
 
+class _FrozenWeights:
+    """What frozen_weights() keeps: dtype casts of parameters and their weight images, each
+    keyed by the source's device address and held together with the source tensor, so that
+    the address cannot be handed to another tensor while the entry lives."""
+
+    def __init__(self):
+        self.casts = {}
+        self.images = {}
+
+
+_frozen = None
+
+
+@contextlib.contextmanager
+def frozen_weights():
+    """Inside this block the caller promises that no weight changes (serving, evaluation).
+    Each layer's weights are then cast and re-laid-out for the tensor-core kernel once, on
+    first use, instead of on every call; everything cached is dropped at exit.  Writing to a
+    weight inside the block leaves the cached copy stale: leave the block first."""
+    global _frozen
+    outer, _frozen = _frozen, (_frozen or _FrozenWeights())
+    try:
+        yield
+    finally:
+        _frozen = outer
+
+
+def cast_weight(t, dtype):
+    """t in `dtype`; cached while frozen_weights() is active."""
+    if t is None or t.dtype == dtype:
+        return t
+    if _frozen is None or torch.is_grad_enabled() and t.requires_grad:
+        return t.to(dtype)
+    key = (t.data_ptr(), t.dtype, dtype, tuple(t.shape))
+    hit = _frozen.casts.get(key)
+    if hit is None:
+        hit = _frozen.casts[key] = (t, t.detach().to(dtype))
+    return hit[1]
+
+
+def _weight_image(lib, p, weight, dev, stream):
+    """Attach the cached weight image for this problem to p (making it on first use)."""
+    key = (weight.data_ptr(), p.dtype, p.math_mode, p.N, p.C, p.H, p.W, p.Co, p.kh, p.kw,
+           p.stride_h, p.stride_w, p.pad_h, p.pad_w, p.dil_h, p.dil_w, p.groups,
+           p.deform_groups, tuple(p.in_stride), bool(p.offset), bool(p.mask))
+    hit = _frozen.images.get(key)
+    if hit is None:
+        nbytes = ctypes.c_size_t(0)
+        _lib.check(lib.dcn_weight_image_bytes(ctypes.byref(p), ctypes.byref(nbytes)))
+        image = None
+        if nbytes.value:
+            image = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+            _lib.check(lib.dcn_prepare_weights(ctypes.byref(p), _ptr(image), nbytes.value,
+                                               stream))
+        hit = _frozen.images[key] = (weight, image)
+    if hit[1] is not None:
+        p.weight_image = _ptr(hit[1])
+        p.weight_image_bytes = hit[1].numel()
+
+
 def forward(input, offset, mask, weight, bias, output, stride, padding, dilation,
             groups, deform_groups, math_mode=None, act=_lib.ACT_NONE, act_range=(0, 0),
             offset_batch_stride=0, mask_batch_stride=0, out_batch_stride=0):
@@ -102,6 +163,8 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     with torch.cuda.device(dev):
         ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        if _frozen is not None and input.numel():
+            _weight_image(lib, p, weight, dev, stream)
         _lib.check(lib.dcn_fwd(ctypes.byref(p), _ptr(ws), nbytes.value, stream))
         if _check_status:
             st = ctypes.c_int32(0)
@@ -264,7 +327,9 @@ def _backward(input, offset, mask, weight, grad_output, stride, padding, dilatio
     g_w = torch.zeros(groups, Co // groups, K, device=dev, dtype=torch.float32) if want_weight else None
     per_sample = C * T * P * 4
     step = max(1, min(N, _BWD_CHUNK_BYTES // max(per_sample, 1)))
-    with torch.cuda.device(dev):
+    # autocast stays off in here: a backward called inside an autocast block would otherwise
+    # turn the fp32 matrix products below into half tensors
+    with torch.cuda.device(dev), torch.autocast('cuda', enabled=False):
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         for n0 in range(0, N, step):
             n1 = min(N, n0 + step)

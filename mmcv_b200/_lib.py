@@ -14,10 +14,11 @@ MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
+ABI_VERSION = 2   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
-           'dcn_fwd_workspace_bytes', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
+           'dcn_fwd_workspace_bytes', 'dcn_weight_image_bytes', 'dcn_prepare_weights', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
            'dcn_read_counters', 'dcn_read_status', 'dcn_bwd_columns', 'dcn_bwd_input',
            'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
@@ -43,6 +44,7 @@ class DcnFwdParams(ctypes.Structure):
         ('out_batch_stride', ctypes.c_int64),
         ('act', ctypes.c_int32), ('act_lo', ctypes.c_int32),
         ('act_hi', ctypes.c_int32), ('device', ctypes.c_int32),
+        ('weight_image', ctypes.c_void_p), ('weight_image_bytes', ctypes.c_int64),
     ]
 
 
@@ -72,10 +74,15 @@ def load():
     P = ctypes.POINTER
     vp, i32, i64, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_size_t
     lib.dcn_abi_version.restype = ctypes.c_int
+    if lib.dcn_abi_version() != ABI_VERSION:
+        raise RuntimeError(f'dcn_b200: {LIB_PATH} has ABI version {lib.dcn_abi_version()}, '
+                           f'this package needs {ABI_VERSION}; rebuild with mmcv_b200.build_ext')
     lib.dcn_last_error.restype = ctypes.c_char_p
     lib.dcn_fwd_plan.argtypes = [P(DcnFwdParams), P(DcnPlanInfo)]
     lib.dcn_fwd_workspace_bytes.argtypes = [P(DcnFwdParams), P(sz)]
     lib.dcn_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
+    lib.dcn_weight_image_bytes.argtypes = [P(DcnFwdParams), P(sz)]
+    lib.dcn_prepare_weights.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_fwd_profiled.argtypes = [P(DcnFwdParams), vp, sz, vp, P(ctypes.c_float)]
     lib.dcn_fwd_static_scratch.argtypes = [P(DcnFwdParams), vp, P(vp)]
     lib.dcn_bwd_columns.argtypes = [P(DcnFwdParams), i64, i64, vp, vp]

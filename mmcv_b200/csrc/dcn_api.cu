@@ -272,6 +272,7 @@ struct Plan {
   Workspace ws;
   int launches;
   bool stage;
+  bool have_image;
 };
 
 int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
@@ -288,7 +289,8 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
   // meet the fp32 tolerance, so the request degrades instead of failing.
   layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);
   pl->stage = pl->tc && pl->ws.xcl_bytes != 0;
-  pl->launches = pl->tc ? (3 + (pl->stage ? 1 : 0)) : 2;  // status clear + prep + main
+  pl->have_image = pl->tc && p->weight_image != nullptr;
+  pl->launches = pl->tc ? (2 + (pl->have_image ? 0 : 1) + (pl->stage ? 1 : 0)) : 2;
   return DCN_OK;
 }
 
@@ -386,13 +388,21 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
     xcl = dst;
   }
   if (ev) cudaEventRecord(ev[1], s);
-  e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, ws + pl.ws.wtile_off, s);
-  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
+  const void *wimage = ws + pl.ws.wtile_off;
+  if (pl.have_image) {
+    if ((size_t)p->weight_image_bytes != pl.ws.wtile_bytes || ((uintptr_t)p->weight_image & 255))
+      return fail(DCN_ERR_ARG, "weight_image must be %zu bytes and 256-byte aligned (got %lld)",
+                  pl.ws.wtile_bytes, (long long)p->weight_image_bytes);
+    wimage = p->weight_image;
+  } else {
+    e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, ws + pl.ws.wtile_off, s);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
+  }
   if (ev) cudaEventRecord(ev[2], s);
   // phase counters live in the workspace header, bytes [64, 256); off unless asked for
   unsigned long long *counters =
       env_int("DCN_B200_COUNTERS", 0, 0, 1) ? (unsigned long long *)(ws + 64) : nullptr;
-  e = launch_tc(pl.g, pl.tp, ptrs, p->dtype, xcl, ws + pl.ws.wtile_off, status, counters, s);
+  e = launch_tc(pl.g, pl.tp, ptrs, p->dtype, xcl, wimage, status, counters, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
   if (ev) cudaEventRecord(ev[3], s);
   return DCN_OK;
@@ -400,6 +410,33 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
 
 int dcn_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream) {
   return run_fwd(p, workspace, workspace_bytes, stream, nullptr);
+}
+
+int dcn_weight_image_bytes(const DcnFwdParams *p, size_t *bytes) {
+  if (!bytes) return fail(DCN_ERR_ARG, "bytes is NULL");
+  Plan pl;
+  int rc = make_plan(p, kSmCountFallback, &pl);
+  if (rc) return rc;
+  *bytes = pl.tc ? pl.ws.wtile_bytes : 0;
+  return DCN_OK;
+}
+
+int dcn_prepare_weights(const DcnFwdParams *p, void *image, size_t image_bytes, void *stream) {
+  if (!p) return fail(DCN_ERR_ARG, "params is NULL");
+  DeviceInfo *dev = nullptr;
+  int rc = probe_device(p->device, &dev);
+  if (rc) return rc;
+  Plan pl;
+  rc = make_plan(p, dev->sms, &pl);
+  if (rc) return rc;
+  if (!pl.tc) return fail(DCN_ERR_ARG, "this problem runs on a kernel that reads the weights directly");
+  if (!p->weight || !image || image_bytes < pl.ws.wtile_bytes || ((uintptr_t)image & 255))
+    return fail(DCN_ERR_ARG, "weight and a 256-byte aligned image of %zu bytes are required",
+                pl.ws.wtile_bytes);
+  cudaError_t e = cudaSetDevice(p->device);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, image, (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
 }
 
 int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream,

@@ -37,7 +37,7 @@ class DeformConv2dFunction(Function):
         ctx.stride, ctx.padding, ctx.dilation = _pair(stride), _pair(padding), _pair(dilation)
         ctx.groups, ctx.deform_groups, ctx.im2col_step = groups, deform_groups, im2col_step
         input = input.type_as(offset)   # offset's dtype decides (autocast)
-        weight = weight.type_as(input)
+        weight = ext_module.cast_weight(weight, input.dtype)
         ctx.save_for_backward(input, offset, weight)
         output = input.new_empty(conv_output_size(input, weight, ctx.stride, ctx.padding,
                                                   ctx.dilation))
@@ -163,7 +163,8 @@ class DeformConv2dPack(DeformConv2d):
             dtype = branch_dtype(x)
             x = shared_layout(x.to(dtype))
             offset = ext_module.conv_offset_forward(
-                x, self.conv_offset.weight.to(dtype), self.conv_offset.bias.to(dtype),
+                x, ext_module.cast_weight(self.conv_offset.weight, dtype),
+                ext_module.cast_weight(self.conv_offset.bias, dtype),
                 _pair(self.stride), _pair(self.padding), _pair(self.dilation))
         else:
             offset = self.conv_offset(x)

@@ -54,7 +54,8 @@ class ModulatedDeformConv2dFunction(Function):
             bias = input.new_empty(0)
         # offset's dtype decides (this is how autocast reaches the op)
         input = input.type_as(offset)
-        weight, bias, mask = weight.type_as(input), bias.type_as(input), mask.type_as(input)
+        weight = ext_module.cast_weight(weight, input.dtype)
+        bias, mask = ext_module.cast_weight(bias, input.dtype), mask.type_as(input)
         ctx.save_for_backward(input, offset, mask, weight, bias)
         output = input.new_empty(conv_output_size(input, weight, ctx.stride, ctx.padding,
                                                   ctx.dilation))
@@ -208,7 +209,8 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
             dtype = branch_dtype(x)
             x = shared_layout(x.to(dtype))
             out = ext_module.conv_offset_forward(
-                x, self.conv_offset.weight.to(dtype), self.conv_offset.bias.to(dtype),
+                x, ext_module.cast_weight(self.conv_offset.weight, dtype),
+                ext_module.cast_weight(self.conv_offset.bias, dtype),
                 self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
             offset, mask = out[:, :two_thirds], out[:, two_thirds:]
         else:

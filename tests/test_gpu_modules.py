@@ -197,3 +197,68 @@ def test_forward_is_capturable_in_a_cuda_graph():
         side.synchronize()
     assert not torch.equal(replayed, eager)
     assert torch.equal(replayed, out)   # replay on new contents == eager run on them
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_frozen_weights_reuse_the_weight_image(dtype):
+    # inside frozen_weights() the weight re-layout runs once per layer; results are the same
+    # bits as without it, and leaving the block drops the cached copies
+    import mmcv_b200
+    from mmcv_b200 import _ext
+    from mmcv_b200.ops import ModulatedDeformConv2dPack
+    torch.manual_seed(5)
+    layer = ModulatedDeformConv2dPack(64, 64, 3, padding=1, deform_groups=2).cuda()
+    layer.conv_offset.weight.data.normal_(0, 0.05)
+    x = torch.randn(2, 64, 24, 40, device='cuda', dtype=dtype)
+    with torch.no_grad(), torch.autocast('cuda', dtype=dtype, enabled=dtype != torch.float32):
+        want = layer(x)
+        with mmcv_b200.frozen_weights():
+            first = layer(x)
+            cached = len(_ext._frozen.images)
+            second = layer(x)
+            assert cached == 2 and len(_ext._frozen.images) == 2   # offset branch + layer
+        assert _ext._frozen is None
+        assert torch.equal(first, want) and torch.equal(second, want)
+        layer.weight.data.mul_(2)
+        assert not torch.equal(layer(x), want)
+
+
+def test_weight_image_through_the_c_abi():
+    import ctypes
+    from mmcv_b200 import _lib
+    lib = _lib.load()
+    torch.manual_seed(6)
+    N, C, H, W, Co = 2, 32, 20, 20, 48
+    x = torch.randn(N, C, H, W, device='cuda', dtype=torch.bfloat16)
+    w = torch.randn(Co, C, 3, 3, device='cuda', dtype=torch.bfloat16) * 0.1
+    off = torch.randn(N, 18, H, W, device='cuda', dtype=torch.bfloat16)
+    msk = torch.rand(N, 9, H, W, device='cuda', dtype=torch.bfloat16)
+    outs = [torch.empty(N, Co, H, W, device='cuda', dtype=torch.bfloat16) for _ in range(2)]
+    p = _lib.DcnFwdParams()
+    p.input, p.offset, p.mask, p.weight = x.data_ptr(), off.data_ptr(), msk.data_ptr(), w.data_ptr()
+    p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
+    p.N, p.C, p.H, p.W, p.Co, p.kh, p.kw = N, C, H, W, Co, 3, 3
+    p.stride_h = p.stride_w = p.pad_h = p.pad_w = p.dil_h = p.dil_w = 1
+    p.groups = p.deform_groups = 1
+    for i, s in enumerate(x.stride()):
+        p.in_stride[i] = s
+    nws, nimg = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    _lib.check(lib.dcn_fwd_workspace_bytes(ctypes.byref(p), ctypes.byref(nws)))
+    _lib.check(lib.dcn_weight_image_bytes(ctypes.byref(p), ctypes.byref(nimg)))
+    assert nimg.value > 0
+    ws = torch.empty(nws.value, dtype=torch.uint8, device='cuda')
+    image = torch.empty(nimg.value, dtype=torch.uint8, device='cuda')
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    p.output = outs[0].data_ptr()
+    _lib.check(lib.dcn_fwd(ctypes.byref(p), ws.data_ptr(), nws.value, stream))
+    _lib.check(lib.dcn_prepare_weights(ctypes.byref(p), image.data_ptr(), nimg.value, stream))
+    info = _lib.DcnPlanInfo()
+    _lib.check(lib.dcn_fwd_plan(ctypes.byref(p), ctypes.byref(info)))
+    p.output, p.weight_image, p.weight_image_bytes = outs[1].data_ptr(), image.data_ptr(), nimg.value
+    info2 = _lib.DcnPlanInfo()
+    _lib.check(lib.dcn_fwd_plan(ctypes.byref(p), ctypes.byref(info2)))
+    assert info2.launches == info.launches - 1
+    _lib.check(lib.dcn_fwd(ctypes.byref(p), ws.data_ptr(), nws.value, stream))
+    assert torch.equal(outs[0], outs[1])
+    p.weight_image_bytes = nimg.value - 16
+    assert lib.dcn_fwd(ctypes.byref(p), ws.data_ptr(), nws.value, stream) == -1   # DCN_ERR_ARG

@@ -19,7 +19,7 @@ def test_library_exports_every_declared_symbol():
     lib = _lib.load()
     for name in declared:
         assert hasattr(lib, name)
-    assert lib.dcn_abi_version() == 1
+    assert lib.dcn_abi_version() == int(re.search(r'#define DCN_ABI_VERSION (\d+)', header).group(1))
 
 
 def params(dtype=_lib.DTYPE_BF16, N=2, C=64, H=16, W=16, Co=64, k=3, s=1, p=1, d=1, g=1, dg=1,
