@@ -220,6 +220,16 @@ __device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint
       ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// True in exactly one lane of the (fully converged) warp.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
                : "memory");
@@ -493,7 +503,9 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     }
   } else if (warp == kMmaWarp) {
     // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
+    // The whole warp walks the loop (so that barrier addresses, descriptors and counters are
+    // warp-uniform values) and one elected lane issues the tensor-core instructions.
+    {
       // fp32 accumulate, both operands K-major, M = 128 pixels, N = BN channels;
       // operand format 0 = fp16, 1 = bf16, 2 = tf32
       constexpr uint32_t kFmt = MODE == kModeBf16 ? 1u : (MODE == kModeF16 ? 0u : 2u);
@@ -502,7 +514,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
       long long li = 0;
       bool ok = true;
-      PhaseTimer pt(a.counters, blockIdx.x == 0);
+      PhaseTimer pt(a.counters, blockIdx.x == 0 && lane == 0);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++li) {
         const int buf = (int)(li & 1);
         const uint32_t par = (uint32_t)((li >> 1) & 1);
@@ -523,31 +535,33 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           tc_fence_after();
           const uint64_t adesc = smem_desc_sw128(smem_u32(L.a + (size_t)sa * kAStageBytes));
           const uint64_t bdesc = smem_desc_sw128(smem_u32(L.b + (size_t)sb * b_stage_bytes));
-          // four k-steps of 32 bytes per 128-byte row: 16 bf16 or 8 tf32 elements each
-          if constexpr (MODE != kModeTf32x3) {
+          if (elect_one()) {
+            // four k-steps of 32 bytes per 128-byte row: 16 bf16 or 8 tf32 elements each
+            if constexpr (MODE != kModeTf32x3) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                        (ks | k) != 0 ? 1u : 0u);
-          } else {
-            // operand tiles of a stage: [hi][lo]; products hi*hi + lo*hi + hi*lo
-            const uint64_t adesc_lo = adesc + (uint64_t)(kTileBytes >> 4);
-            const uint64_t bdesc_lo = bdesc + (uint64_t)(b_tile_bytes >> 4);
+              for (int k = 0; k < 4; ++k)
+                umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                          (ks | k) != 0 ? 1u : 0u);
+            } else {
+              // operand tiles of a stage: [hi][lo]; products hi*hi + lo*hi + hi*lo
+              const uint64_t adesc_lo = adesc + (uint64_t)(kTileBytes >> 4);
+              const uint64_t bdesc_lo = bdesc + (uint64_t)(b_tile_bytes >> 4);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
-                        (ks | k) != 0 ? 1u : 0u);
-              umma_tf32(d_tmem, adesc_lo + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, 1u);
-              umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc_lo + (uint64_t)(2 * k), idesc, 1u);
+              for (int k = 0; k < 4; ++k) {
+                umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
+                          (ks | k) != 0 ? 1u : 0u);
+                umma_tf32(d_tmem, adesc_lo + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc, 1u);
+                umma_tf32(d_tmem, adesc + (uint64_t)(2 * k), bdesc_lo + (uint64_t)(2 * k), idesc, 1u);
+              }
             }
+            umma_commit(empty_a + 8 * sa);
+            umma_commit(empty_b + 8 * sb);
+            if (ks == tp.S - 1) umma_commit(tmem_full + 8 * buf);
           }
-          umma_commit(empty_a + 8 * sa);
-          umma_commit(empty_b + 8 * sb);
+          __syncwarp();
           if (++sa == (uint32_t)A) { sa = 0; pa ^= 1u; }
           if (++sb == (uint32_t)B) { sb = 0; pb ^= 1u; }
         }
-        if (!ok) break;
-        umma_commit(tmem_full + 8 * buf);
       }
     }
     __syncwarp();
