@@ -30,6 +30,9 @@ namespace dcn {
 namespace {
 
 constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+// How long one mbarrier.try_wait may keep the thread suspended in hardware (it wakes at once
+// when the phase completes): waiting warps then take no issue slots from the producers.
+constexpr uint32_t kSuspendHintNs = 20000u;
 constexpr int kEpilogueWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
@@ -88,10 +91,10 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(bar), "r"(parity)
+      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
       : "memory");
   return ok != 0;
 }
@@ -134,13 +137,15 @@ struct PhaseTimer {
   }
   __device__ __forceinline__ void lap(int i) {
     if (c) {
+      // fire-and-forget reductions: a read-modify-write here would put a memory round
+      // trip into the phase that follows
       const long long t1 = clock64();
-      c[i] += (unsigned long long)(t1 - t0);
+      atomicAdd(c + i, (unsigned long long)(t1 - t0));
       t0 = t1;
     }
   }
   __device__ __forceinline__ void count(int i) {
-    if (c) c[i] += 1;
+    if (c) atomicAdd(c + i, 1ull);
   }
 };
 
@@ -155,14 +160,14 @@ __device__ __forceinline__ uint32_t ldg_raw_ordered(const float *p) {
   asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
-__device__ __forceinline__ unsigned short ldg_raw_ordered(const __nv_bfloat16 *p) {
-  unsigned short v;
-  asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
+__device__ __forceinline__ uint32_t ldg_raw_ordered(const __nv_bfloat16 *p) {
+  uint32_t v;  // a 32-bit register: two 16-bit results packed into one would be a use
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
-__device__ __forceinline__ unsigned short ldg_raw_ordered(const __half *p) {
-  unsigned short v;
-  asm volatile("ld.global.nc.b16 %0, [%1];" : "=h"(v) : "l"(p));
+__device__ __forceinline__ uint32_t ldg_raw_ordered(const __half *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
   return v;
 }
 template <typename T> struct RawOf {
@@ -170,15 +175,13 @@ template <typename T> struct RawOf {
   static __device__ __forceinline__ float to_float(uint32_t v) { return __uint_as_float(v); }
 };
 template <> struct RawOf<__nv_bfloat16> {
-  using type = unsigned short;
-  static __device__ __forceinline__ float to_float(unsigned short v) {
-    return __uint_as_float((uint32_t)v << 16);
-  }
+  using type = uint32_t;
+  static __device__ __forceinline__ float to_float(uint32_t v) { return __uint_as_float(v << 16); }
 };
 template <> struct RawOf<__half> {
-  using type = unsigned short;
-  static __device__ __forceinline__ float to_float(unsigned short v) {
-    return __half2float(__ushort_as_half(v));
+  using type = uint32_t;
+  static __device__ __forceinline__ float to_float(uint32_t v) {
+    return __half2float(__ushort_as_half((unsigned short)v));
   }
 };
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -340,6 +343,9 @@ __device__ __forceinline__ void blend4_tf32(const uint4 &w, const uint4 &q0, con
 }
 
 constexpr int kRowInvalid = INT_MIN;
+// Entries of one (tap, deform group) block of the tap table: the rows plus a skew of four, so
+// that the blocks of two deform groups read by one warp fall into different banks.
+constexpr int kTabStride = kBM + 4;
 
 struct SmemLayout {
   uint8_t *a, *b;
@@ -349,6 +355,7 @@ struct SmemLayout {
   uint64_t *bars;
   uint32_t *tmem_slot;
   int *abort_flag;
+  float *bias_s;       // bias of the tile's output channels as fp32, one copy per epilogue warp
 };
 
 __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int T) {
@@ -356,14 +363,15 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
   uint8_t *p = base;
   L.a = p; p += (size_t)tp.a_stages * tp.tiles_per_stage * kTileBytes;
   L.b = p; p += (size_t)tp.b_stages * tp.tiles_per_stage * tp.BN * 128;
-  L.tab_w = (uint4 *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint4);
-  L.tab_off = (uint32_t *)p; p += (size_t)T * tp.ndgc * kBM * sizeof(uint32_t);
+  L.tab_w = (uint4 *)p; p += (size_t)T * tp.ndgc * kTabStride * sizeof(uint4);
+  L.tab_off = (uint32_t *)p; p += (size_t)T * tp.ndgc * kTabStride * sizeof(uint32_t);
   L.row_h = (int *)p; p += kBM * sizeof(int);
   L.row_w = (int *)p; p += kBM * sizeof(int);
   L.row_pix = (int *)p; p += kBM * sizeof(int);
   L.bars = (uint64_t *)p; p += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t);
   L.tmem_slot = (uint32_t *)p; p += 8;
-  L.abort_flag = (int *)p;
+  L.abort_flag = (int *)p; p += 8;
+  L.bias_s = (float *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
   return L;
 }
 
@@ -372,9 +380,10 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
 size_t tc_smem_bytes(const TcPlan &tp, int T) {
   size_t s = 1024;  // slack for manual 1024-byte alignment
   s += (size_t)tp.tiles_per_stage * ((size_t)tp.a_stages * kTileBytes + (size_t)tp.b_stages * tp.BN * 128);
-  s += (size_t)T * tp.ndgc * kBM * (sizeof(uint4) + sizeof(uint32_t));
+  s += (size_t)T * tp.ndgc * kTabStride * (sizeof(uint4) + sizeof(uint32_t));
   s += 3 * kBM * sizeof(int);
   s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t) + 16;
+  s += (size_t)kEpilogueWarps * tp.BN * sizeof(float) + 16;  // bias staging, one copy per epilogue warp
   return s;
 }
 
@@ -462,21 +471,38 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
 
   if (warp < kEpilogueWarps) {
     // ------------------------------ epilogue ------------------------------
+    // Thread = one pixel (accumulator row); per 32 output channels one tcgen05.ld, then bias,
+    // activation, rounding and a store per channel (NCHW: a warp's 32 pixels of one channel
+    // are one or two contiguous runs).  The tile's bias is staged in shared memory as fp32 so
+    // that the inner loop has no global loads in front of its stores.
     TIO *out = (TIO *)a.output;
     const TIO *bias = (const TIO *)a.bias;
     const int row = warp * 32 + lane;
     const int ty = row >> tp.tw_log2, tx = row & tw_mask;
+    const bool act_any = g.act == DCN_ACT_SIGMOID && g.act_hi > g.act_lo;
+    float *bias_w = L.bias_s + warp * tp.BN;
     PhaseTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     long long li = 0;
+    int staged_co0 = -1;
     for (long long item = blockIdx.x; item < items; item += gridDim.x, ++li) {
       const TileId t = decode_item(item, g, tp);
       const int buf = (int)(li & 1);
       const uint32_t par = (uint32_t)((li >> 1) & 1);
       const int ho = t.ho0 + ty, wo = t.wo0 + tx;
       const bool valid = ho < g.Ho && wo < g.Wo;
-      const long long obase = (long long)t.n * g.out_sn + (long long)ho * g.Wo + wo;
       const int ncols = min(tp.BN, g.Cog - t.nt * tp.BN);
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
+      TIO *orow = out + (long long)t.n * g.out_sn + (long long)co0 * plane + (long long)ho * g.Wo + wo;
+      if (co0 != staged_co0) {
+        // (re)stage the bias: every epilogue warp keeps a copy of its own, so that no
+        // rendezvous between warps is needed
+        __syncwarp();
+        for (int i = lane; i < tp.BN; i += 32)
+          bias_w[i] = (bias && i < ncols) ? ld_as_float(bias, co0 + i) : 0.f;
+        __syncwarp();
+        staged_co0 = co0;
+      }
+      const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
       pt.lap(13);
       if (!mbar_wait<true>(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
       pt.lap(12);
@@ -486,14 +512,18 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         uint32_t r[32];
         tmem_ld32(taddr + (uint32_t)c0, r);
         tmem_ld_wait();
+        const float4 *bs = reinterpret_cast<const float4 *>(bias_w + c0);
+        TIO *oc = orow + (long long)c0 * plane;
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          if (c0 + j < ncols) {
-            const int co = co0 + c0 + j;
-            float v = __uint_as_float(r[j]);
-            if (bias) v += ld_as_float(bias, co);
-            v = apply_act(g, co, v);
-            if (valid) st_from_float(out, obase + (long long)co * plane, v);
+        for (int j4 = 0; j4 < 8; ++j4) {
+          const float4 b4 = bs[j4];
+          float v[4] = {__uint_as_float(r[4 * j4]) + b4.x, __uint_as_float(r[4 * j4 + 1]) + b4.y,
+                        __uint_as_float(r[4 * j4 + 2]) + b4.z, __uint_as_float(r[4 * j4 + 3]) + b4.w};
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int j = 4 * j4 + k;
+            if (act_tile) v[k] = apply_act(g, co0 + c0 + j, v[k]);
+            if (valid && c0 + j < ncols) st_from_float(oc, (long long)j * plane, v[k]);
           }
         }
       }
@@ -679,7 +709,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
             const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
             const int total = g.T * nd;
-            constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : 5);  // entries in flight per thread
+            constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : (NPW <= 16 ? 5 : 3));  // entries in flight per thread
             int tap = 0, dgl = tpart, ti = 0, tj = 0;  // entry e <-> (tap, dgl), tap <-> (ti, tj)
             auto normalise = [&]() {
               while (dgl >= nd) {
@@ -752,7 +782,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   wq.z = wt.z == 0.f ? 0u : __float_as_uint(wt.z);
                   wq.w = wt.w == 0.f ? 0u : __float_as_uint(wt.w);
                 }
-                const int slot = (etap * tp.ndgc + edgl) * kBM + trow;
+                const int slot = (etap * tp.ndgc + edgl) * kTabStride + trow;
                 L.tab_w[slot] = wq;
                 L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * MT::kEsz);
               }
@@ -774,7 +804,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           pt.lap(0);
           pt.count(5);
           uint8_t *stage = L.a + (size_t)sa * kAStageBytes + soff0;
-          const int slot0 = (tap * tp.ndgc + dgl) * kBM + row0;
+          const int slot0 = (tap * tp.ndgc + dgl) * kTabStride + row0;
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
 #pragma unroll
           for (int p0 = 0; p0 < kPasses; p0 += kBatch) {
@@ -998,6 +1028,8 @@ cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   switch (tp.producer_cfg) {
     case 184: return launch_one<TIO, MODE, 184>(a, tp, s);
     case 342: return launch_one<TIO, MODE, 342>(a, tp, s);
+    case 381: return launch_one<TIO, MODE, 381>(a, tp, s);
+    case 382: return launch_one<TIO, MODE, 382>(a, tp, s);
     default: return launch_one<TIO, MODE, 282>(a, tp, s);
   }
 }
