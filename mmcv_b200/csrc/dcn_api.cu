@@ -176,8 +176,6 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 999)) {
       case 184: tp->producer_cfg = 184; break;
       case 342: tp->producer_cfg = 342; break;
-      case 381: tp->producer_cfg = 381; break;
-      case 382: tp->producer_cfg = 382; break;
       case 282: tp->producer_cfg = 282; break;
       default: tp->producer_cfg = cfg_default; break;
     }

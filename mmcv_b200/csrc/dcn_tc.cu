@@ -709,7 +709,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
             const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
             const int total = g.T * nd;
-            constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : (NPW <= 16 ? 5 : 3));  // entries in flight per thread
+            constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : 5);  // entries in flight per thread
             int tap = 0, dgl = tpart, ti = 0, tj = 0;  // entry e <-> (tap, dgl), tap <-> (ti, tj)
             auto normalise = [&]() {
               while (dgl >= nd) {
@@ -1028,8 +1028,6 @@ cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   switch (tp.producer_cfg) {
     case 184: return launch_one<TIO, MODE, 184>(a, tp, s);
     case 342: return launch_one<TIO, MODE, 342>(a, tp, s);
-    case 381: return launch_one<TIO, MODE, 381>(a, tp, s);
-    case 382: return launch_one<TIO, MODE, 382>(a, tp, s);
     default: return launch_one<TIO, MODE, 282>(a, tp, s);
   }
 }

@@ -12,6 +12,7 @@ from torch.autograd.function import once_differentiable
 from torch.nn.modules.utils import _pair, _single
 
 from .. import _ext as ext_module
+from . import modulated_deform_conv as mdc
 from .modulated_deform_conv import (_rename_kw, _upgrade_offset_keys, branch_dtype,
                                     conv_output_size, fused_branch_applies, register_layer,
                                     shared_layout)
@@ -162,10 +163,13 @@ class DeformConv2dPack(DeformConv2d):
         if fused_branch_applies(x, self.conv_offset):
             dtype = branch_dtype(x)
             x = shared_layout(x.to(dtype))
-            offset = ext_module.conv_offset_forward(
-                x, ext_module.cast_weight(self.conv_offset.weight, dtype),
-                ext_module.cast_weight(self.conv_offset.bias, dtype),
-                _pair(self.stride), _pair(self.padding), _pair(self.dilation))
+            if mdc.OFFSET_BRANCH == 'kernel':
+                offset = ext_module.conv_offset_forward(
+                    x, ext_module.cast_weight(self.conv_offset.weight, dtype),
+                    ext_module.cast_weight(self.conv_offset.bias, dtype),
+                    _pair(self.stride), _pair(self.padding), _pair(self.dilation))
+            else:
+                offset, _ = mdc.library_offset_branch(x, self.conv_offset, dtype)
         else:
             offset = self.conv_offset(x)
         return deform_conv2d(x, offset, self.weight, self.stride, self.padding, self.dilation,

@@ -6,10 +6,12 @@ dtype, reference lines 136-139), error types and state-dict layout are the
 reference's; the computation goes to the sm_100a library through ``_ext``.
 """
 import math
+import os
 from typing import Optional, Tuple, Union
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 from torch.autograd import Function
 from torch.autograd.function import once_differentiable
 from torch.nn.modules.utils import _pair, _single
@@ -89,9 +91,34 @@ class ModulatedDeformConv2dFunction(Function):
 modulated_deform_conv2d = ModulatedDeformConv2dFunction.apply
 
 
+# How an inference-time Pack layer computes its offset branch: 'library' = the branch's own
+# nn.Conv2d arithmetic (cuDNN) on the channels-last copy of the input that the deformable
+# kernel reads as well; 'kernel' = one launch of this library's implicit-GEMM kernel with zero
+# offsets and the sigmoid fused.  Measured on B200 the library convolution is about three times
+# faster for these 18- and 27-channel outputs, so it is the default.
+OFFSET_BRANCH = os.environ.get('DCN_B200_OFFSET_BRANCH', 'library')
+
+
+def library_offset_branch(x, conv, dtype, sigmoid_from=None):
+    """conv(x) for an inference-time offset branch: x is already in the layout shared with
+    the deformable kernel.  Returns NCHW-contiguous (offset, mask) tensors; mask is None when
+    sigmoid_from is None (the v1 layer)."""
+    out = F.conv2d(x, ext_module.cast_weight(conv.weight, dtype),
+                   ext_module.cast_weight(conv.bias, dtype), conv.stride, conv.padding,
+                   conv.dilation, conv.groups)
+    if sigmoid_from is None:
+        return out.contiguous(), None
+    offset = out[:, :sigmoid_from].contiguous()
+    mask = torch.empty((out.size(0), out.size(1) - sigmoid_from) + tuple(out.shape[2:]),
+                       dtype=out.dtype, device=out.device)
+    torch.sigmoid(out[:, sigmoid_from:], out=mask)
+    return offset, mask
+
+
 def fused_branch_applies(x, conv):
-    """The offset branch runs on this library's kernel when nothing needs its gradient
-    (inference); otherwise it stays an nn.Conv2d so that autograd sees it."""
+    """The inference path of a Pack layer (shared channels-last input, no autograd graph)
+    applies when nothing needs the branch's gradient; otherwise the branch stays a plain
+    nn.Conv2d call so that autograd sees it."""
     if not x.is_cuda or x.dtype not in (torch.float32, torch.bfloat16, torch.float16):
         return False
     if torch.is_autocast_enabled('cuda') and torch.get_autocast_dtype('cuda') not in (
@@ -204,15 +231,17 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
         two_thirds = self.conv_offset.out_channels // 3 * 2
         # chunk(3) + cat of the first two chunks == the first two thirds of the channels
         if fused_branch_applies(x, self.conv_offset):
-            # one launch of the implicit-GEMM kernel: convolution + sigmoid of the mask third;
-            # offset and mask are then channel slices of its output, passed without copies
+            # the branch and the deformable kernel read one channels-last copy of the input
             dtype = branch_dtype(x)
             x = shared_layout(x.to(dtype))
-            out = ext_module.conv_offset_forward(
-                x, ext_module.cast_weight(self.conv_offset.weight, dtype),
-                ext_module.cast_weight(self.conv_offset.bias, dtype),
-                self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
-            offset, mask = out[:, :two_thirds], out[:, two_thirds:]
+            if OFFSET_BRANCH == 'kernel':
+                out = ext_module.conv_offset_forward(
+                    x, ext_module.cast_weight(self.conv_offset.weight, dtype),
+                    ext_module.cast_weight(self.conv_offset.bias, dtype),
+                    self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
+                offset, mask = out[:, :two_thirds], out[:, two_thirds:]
+            else:
+                offset, mask = library_offset_branch(x, self.conv_offset, dtype, two_thirds)
         else:
             out = self.conv_offset(x)
             offset = out[:, :two_thirds].contiguous()

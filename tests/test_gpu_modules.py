@@ -125,14 +125,18 @@ def test_offset_branch_on_the_same_kernel(dtype):
         assert rel_l2(out, ref) <= 2e-2
 
 
-def test_pack_layers_with_fused_branch():
-    # inference path of the Pack layers: the offset branch runs on this library's kernel and
-    # feeds the deformable convolution through channel slices (no copies).  The branch is
-    # checked against F.conv2d; the layer output against the CPU checker fed the branch's
-    # own (bf16) offsets and mask, which isolates the sampling kernel from branch rounding.
+@pytest.mark.parametrize('branch_mode', ['library', 'kernel'])
+def test_pack_layers_inference_path(branch_mode, monkeypatch):
+    # inference path of the Pack layers: the offset branch (library convolution by default, or
+    # this library's kernel with zero offsets and a fused sigmoid) and the deformable kernel
+    # read one channels-last copy of the input.  The branch is checked against F.conv2d; the
+    # layer output against the CPU checker fed the branch's own (bf16) offsets and mask, which
+    # isolates the sampling kernel from branch rounding.
     import torch.nn.functional as F
     from mmcv_b200 import _ext
     from mmcv_b200.ops import DeformConv2dPack, ModulatedDeformConv2dPack
+    from mmcv_b200.ops import modulated_deform_conv as mdc
+    monkeypatch.setattr(mdc, 'OFFSET_BRANCH', branch_mode)
     torch.manual_seed(0)
     for cls, dg in ((ModulatedDeformConv2dPack, 2), (DeformConv2dPack, 1)):
         layer = cls(64, 96, 3, padding=1, deform_groups=dg).cuda().to(torch.bfloat16)
@@ -142,9 +146,16 @@ def test_pack_layers_with_fused_branch():
         modulated = cls is ModulatedDeformConv2dPack
         k = layer.conv_offset.out_channels // 3 * 2 if modulated else None
         with torch.no_grad():
-            fused = layer(x).float().cpu()
-            branch = _ext.conv_offset_forward(x, layer.conv_offset.weight, layer.conv_offset.bias,
-                                              (1, 1), (1, 1), (1, 1), sigmoid_from=k).float().cpu()
+            got = layer(x).float().cpu()
+            if branch_mode == 'kernel':
+                branch = _ext.conv_offset_forward(x, layer.conv_offset.weight,
+                                                  layer.conv_offset.bias, (1, 1), (1, 1), (1, 1),
+                                                  sigmoid_from=k).float().cpu()
+            else:
+                off_, msk_ = mdc.library_offset_branch(mdc.shared_layout(x), layer.conv_offset,
+                                                       torch.bfloat16, k)
+                assert off_.is_contiguous() and (msk_ is None or msk_.is_contiguous())
+                branch = (torch.cat([off_, msk_], 1) if modulated else off_).float().cpu()
         o = F.conv2d(x.float().cpu(), layer.conv_offset.weight.float().cpu(),
                      layer.conv_offset.bias.float().cpu(), 1, 1)
         if modulated:
@@ -156,7 +167,7 @@ def test_pack_layers_with_fused_branch():
         ref = oracle.best_forward(x.float().cpu(), off.contiguous(),
                                   None if msk is None else msk.contiguous(),
                                   layer.weight.float().cpu(), bias, 1, 1, 1, 1, dg)
-        assert rel_l2(fused, ref) <= 2e-2
+        assert rel_l2(got, ref) <= 2e-2
 
 
 def test_forward_is_capturable_in_a_cuda_graph():
@@ -216,7 +227,7 @@ def test_frozen_weights_reuse_the_weight_image(dtype):
             first = layer(x)
             cached = len(_ext._frozen.images)
             second = layer(x)
-            assert cached == 2 and len(_ext._frozen.images) == 2   # offset branch + layer
+            assert cached == 1 and len(_ext._frozen.images) == 1   # the layer's own weights
         assert _ext._frozen is None
         assert torch.equal(first, want) and torch.equal(second, want)
         layer.weight.data.mul_(2)
