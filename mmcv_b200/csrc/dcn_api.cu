@@ -169,17 +169,17 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
       }
     if (ndgc > 15) return false;
     tp->ndgc = ndgc;
-    // Producer layout (measured): three groups of four warps when the tap table is built
-    // once per tile (one deform-group set per chunk, bf16), else two groups of eight, which
-    // rebuild the table faster; TF32x3 writes two tiles per row and prefers the latter too.
-    const int cfg_default = (ndgc == 1 && !tf32) ? 342 : 282;
-    switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 999)) {
-      case 184: tp->producer_cfg = 184; break;
+    // Producer layout (measured best on every workload tried): two groups of eight warps,
+    // two rows per thread in flight, rows software-pipelined.  The batched layouts (282: same
+    // warps, 342: three groups of four) stay selectable for comparison.
+    const int cfg_default = 1282;
+    switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 9999)) {
       case 342: tp->producer_cfg = 342; break;
+      case 1282: tp->producer_cfg = 1282; break;
       case 282: tp->producer_cfg = 282; break;
       default: tp->producer_cfg = cfg_default; break;
     }
-    const int a_min = tp->producer_cfg / 100;  // every producer group needs a stage of its own
+    const int a_min = (tp->producer_cfg / 100) % 10;  // every producer group needs a stage of its own
     int cols = 32;
     while (cols < 2 * tp->BN) cols *= 2;
     tp->tmem_cols = cols;

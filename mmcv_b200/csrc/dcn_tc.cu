@@ -184,6 +184,20 @@ template <> struct RawOf<__half> {
     return __half2float(__ushort_as_half((unsigned short)v));
   }
 };
+// 16-byte read-only load, zero when `take` is 0.  `tok` is passed through untouched; code that
+// must come after this load's issue takes `tok` as an input.
+__device__ __forceinline__ uint4 ldg16_pinned(const void *p, uint32_t take, uint32_t &tok) {
+  uint4 r;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %5, 0;\n\t"
+      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
+      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
+      : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
+      : "l"(p), "r"(take), "r"(tok));
+  asm volatile("" : "+r"(tok));
+  return r;
+}
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
@@ -408,13 +422,16 @@ __device__ __forceinline__ TileId decode_item(long long item, const Geom &g, con
   return t;
 }
 
-// PCFG encodes the producer layout as groups*100 + warps_per_group*10 + rows_in_flight:
+// PCFG encodes the producer layout as [1]*1000 + groups*100 + warps_per_group*10 + rows_in_flight:
 // `groups` groups of `warps_per_group` warps fill alternate stages, and every thread keeps
-// `rows_in_flight` rows (four 16-byte loads each) in flight.
+// `rows_in_flight` rows (four 16-byte loads each) in flight; with the leading 1 the rows of a
+// stage are software-pipelined (the next row's loads are issued before a row is blended),
+// without it they are loaded and blended in batches.
 template <typename TIO, int MODE, int PCFG>
-__global__ void __launch_bounds__((kFirstProducerWarp + (PCFG / 100) * ((PCFG / 10) % 10)) * 32, 1)
+__global__ void __launch_bounds__((kFirstProducerWarp + ((PCFG / 100) % 10) * ((PCFG / 10) % 10)) * 32, 1)
 dcn_fwd_tc(const __grid_constant__ TcArgs a) {
-  constexpr int kGroups = PCFG / 100;       // group i fills k-stages i, i+G, ...
+  constexpr int kGroups = (PCFG / 100) % 10;  // group i fills k-stages i, i+G, ...
+  constexpr bool kPipe = PCFG >= 1000;        // gather software-pipelined over the passes
   constexpr int kWpg = (PCFG / 10) % 10;    // warps per group
   constexpr int kBatch = PCFG % 10;         // rows of a thread in flight at a time
   constexpr int NPW = kGroups * kWpg;
@@ -806,6 +823,49 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
           uint8_t *stage = L.a + (size_t)sa * kAStageBytes + soff0;
           const int slot0 = (tap * tp.ndgc + dgl) * kTabStride + row0;
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+          if constexpr (kPipe) {
+            // kBatch register sets rotate over the passes: the loads of pass p + kBatch - 1 are
+            // issued before pass p is blended, so that a pass's loads fly during the blends of
+            // the passes before it.  (Carrying the rotation across stage boundaries as well
+            // measured slower.)
+            uint4 q[kBatch][4], wq[kBatch];
+            uint32_t tok = 0;
+            auto issue = [&](int p) {
+              const int sl = p % kBatch;
+              wq[sl] = vvalid ? L.tab_w[slot0 + p * kRowStep] : z;
+              const uint32_t o = L.tab_off[slot0 + p * kRowStep] + c2;
+              q[sl][0] = ldg16_pinned(xb + o, wq[sl].x, tok);
+              q[sl][1] = ldg16_pinned(xb + (uint32_t)(o + cW2), wq[sl].y, tok);
+              q[sl][2] = ldg16_pinned(xb + (uint32_t)(o + cH2), wq[sl].z, tok);
+              q[sl][3] = ldg16_pinned(xb + (uint32_t)(o + cHW2), wq[sl].w, tok);
+            };
+#pragma unroll
+            for (int p = 0; p < kBatch - 1; ++p) issue(p);
+#pragma unroll
+            for (int p = 0; p < kPasses; ++p) {
+              if (p + kBatch - 1 < kPasses) issue(p + kBatch - 1);
+              if (p == 0) {
+                // the stage must be free only now, with the first loads already in flight
+                pt.lap(4);
+                ok = mbar_wait(empty_a + 8 * sa, pa ^ 1u, abort_s, a.status, 8);
+                pt.lap(3);
+              }
+              const int sl = p % kBatch;
+              uint4 w = wq[sl];
+              w.x |= tok;   // tok is 0: pins the blend behind the issue above
+              uint8_t *dst = stage + p * kRowStep * 128;
+              if constexpr (MODE == kModeBf16) {
+                *reinterpret_cast<uint4 *>(dst) = blend8_bf16(w, q[sl][0], q[sl][1], q[sl][2], q[sl][3]);
+              } else if constexpr (MODE == kModeF16) {
+                *reinterpret_cast<uint4 *>(dst) = blend8_f16(w, q[sl][0], q[sl][1], q[sl][2], q[sl][3]);
+              } else {
+                uint4 hi, lo;
+                blend4_tf32(w, q[sl][0], q[sl][1], q[sl][2], q[sl][3], hi, lo);
+                *reinterpret_cast<uint4 *>(dst) = hi;
+                *reinterpret_cast<uint4 *>(dst + kTileBytes) = lo;
+              }
+            }
+          } else {
 #pragma unroll
           for (int p0 = 0; p0 < kPasses; p0 += kBatch) {
             uint4 q[kBatch][4], wq[kBatch];
@@ -840,6 +900,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                 *reinterpret_cast<uint4 *>(dst + kTileBytes) = lo;
               }
             }
+          }
           }
           if (!ok) break;
           pt.lap(4);
@@ -999,7 +1060,7 @@ namespace {
 template <typename TIO, int MODE, int PCFG>
 cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   auto kern = dcn_fwd_tc<TIO, MODE, PCFG>;
-  constexpr int kThreads = (kFirstProducerWarp + (PCFG / 100) * ((PCFG / 10) % 10)) * 32;
+  constexpr int kThreads = (kFirstProducerWarp + ((PCFG / 100) % 10) * ((PCFG / 10) % 10)) * 32;
   // opt in to large dynamic shared memory once per device and instantiation
   static std::atomic<unsigned long long> done_mask{0};
   int dev = 0;
@@ -1026,9 +1087,10 @@ cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 template <typename TIO, int MODE>
 cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   switch (tp.producer_cfg) {
-    case 184: return launch_one<TIO, MODE, 184>(a, tp, s);
     case 342: return launch_one<TIO, MODE, 342>(a, tp, s);
-    default: return launch_one<TIO, MODE, 282>(a, tp, s);
+    case 1282: return launch_one<TIO, MODE, 1282>(a, tp, s);
+    case 282: return launch_one<TIO, MODE, 282>(a, tp, s);
+    default: return launch_one<TIO, MODE, 1282>(a, tp, s);
   }
 }
 template <typename TIO>
@@ -1040,7 +1102,7 @@ cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 }  // namespace
 
 int tc_threads(const TcPlan &tp) {
-  return (kFirstProducerWarp + (tp.producer_cfg / 100) * ((tp.producer_cfg / 10) % 10)) * 32;
+  return (kFirstProducerWarp + ((tp.producer_cfg / 100) % 10) * ((tp.producer_cfg / 10) % 10)) * 32;
 }
 
 cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,
