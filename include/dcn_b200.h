@@ -203,6 +203,17 @@ int dcn_read_counters(const void *workspace, void *stream, uint64_t counters[24]
 int dcn_read_status(const void *workspace, void *stream, int32_t *status);
 
 /*
+ * Layout helper: copies a 4-D tensor [N, C, H, W] (element strides `in_stride`, dtype
+ * DCN_DTYPE_*) into a dense channels-last image [N, H, W, C] of the same type at `output`
+ * (16-byte aligned), on `stream`.  dcn_fwd reads such a copy without restaging it, so a caller
+ * that feeds the same activations to several layers (the Pack layers: offset branch +
+ * deformable kernel) makes it once.  (No counterpart in the reference, which keeps NCHW.)
+ */
+int dcn_to_channels_last(const void *input, void *output, int32_t dtype, int64_t N, int64_t C,
+                         int64_t H, int64_t W, const int64_t in_stride[4], int32_t device,
+                         void *stream);
+
+/*
  * The two reference entry points with flat arguments, in the reference's own
  * argument order and meaning.  `elem` is DCN_DTYPE_*; sizes are in elements.
  *

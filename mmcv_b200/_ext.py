@@ -175,6 +175,25 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     return ws
 
 
+def to_channels_last(x):
+    """x [N, C, H, W] as a dense channels-last tensor (same shape, NHWC memory), made by this
+    library's layout kernel; x itself when it already is one."""
+    if x.dim() != 4:
+        raise RuntimeError(f'dcn_b200: expected a 4-D tensor, got {x.dim()}-D')
+    if x.is_contiguous(memory_format=torch.channels_last) or x.numel() == 0:
+        return x
+    lib = _lib.load()
+    dev = _require_cuda(input=x)
+    out = torch.empty_like(x, memory_format=torch.channels_last)
+    strides = (ctypes.c_int64 * 4)(*x.stride())
+    with torch.cuda.device(dev):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dcn_to_channels_last(
+            _ptr(x), _ptr(out), _dtype_code(x), x.size(0), x.size(1), x.size(2), x.size(3),
+            strides, dev.index if dev.index is not None else torch.cuda.current_device(), stream))
+    return out
+
+
 def _per_sample(t):
     """(tensor, batch stride in elements) for a tensor whose samples are each contiguous;
     a channel slice of a larger NCHW tensor qualifies and is passed without a copy."""

@@ -19,7 +19,7 @@ ABI_VERSION = 2   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_fwd_workspace_bytes', 'dcn_weight_image_bytes', 'dcn_prepare_weights', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
-           'dcn_read_counters', 'dcn_read_status', 'dcn_bwd_columns', 'dcn_bwd_input',
+           'dcn_read_counters', 'dcn_read_status', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
            'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
@@ -83,6 +83,7 @@ def load():
     lib.dcn_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_weight_image_bytes.argtypes = [P(DcnFwdParams), P(sz)]
     lib.dcn_prepare_weights.argtypes = [P(DcnFwdParams), vp, sz, vp]
+    lib.dcn_to_channels_last.argtypes = [vp, vp, i32, i64, i64, i64, i64, P(i64), i32, vp]
     lib.dcn_fwd_profiled.argtypes = [P(DcnFwdParams), vp, sz, vp, P(ctypes.c_float)]
     lib.dcn_fwd_static_scratch.argtypes = [P(DcnFwdParams), vp, P(vp)]
     lib.dcn_bwd_columns.argtypes = [P(DcnFwdParams), i64, i64, vp, vp]

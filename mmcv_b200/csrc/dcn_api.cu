@@ -526,6 +526,33 @@ int dcn_read_status(const void *workspace, void *stream, int32_t *status) {
   return DCN_OK;
 }
 
+int dcn_to_channels_last(const void *input, void *output, int32_t dtype, int64_t N, int64_t C,
+                         int64_t H, int64_t W, const int64_t in_stride[4], int32_t device,
+                         void *stream) {
+  if (dtype != DCN_DTYPE_F32 && dtype != DCN_DTYPE_BF16 && dtype != DCN_DTYPE_F16)
+    return fail(DCN_ERR_UNSUPPORTED, "dtype %d is not supported (fp32, bf16, fp16)", dtype);
+  if (N < 0 || C < 1 || H < 1 || W < 1 || !in_stride)
+    return fail(DCN_ERR_ARG, "bad shape [%lld, %lld, %lld, %lld]", (long long)N, (long long)C,
+                (long long)H, (long long)W);
+  if (N > 2147483647LL || C > 2147483647LL || H * W > 2147483647LL)
+    return fail(DCN_ERR_UNSUPPORTED, "tensor too large for 32-bit pixel and channel indices");
+  if (N == 0) return DCN_OK;
+  if (!input || !output || ((uintptr_t)output & 15))
+    return fail(DCN_ERR_ARG, "input and a 16-byte aligned output are required");
+  DeviceInfo *dev = nullptr;
+  int rc = probe_device(device, &dev);
+  if (rc) return rc;
+  cudaError_t e = cudaSetDevice(device);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  Geom g;
+  memset(&g, 0, sizeof(g));
+  g.N = (int)N; g.C = (int)C; g.H = (int)H; g.W = (int)W;
+  g.in_sn = in_stride[0]; g.in_sc = in_stride[1]; g.in_sh = in_stride[2]; g.in_sw = in_stride[3];
+  const int op_format = dtype == DCN_DTYPE_F32 ? 2 : (dtype == DCN_DTYPE_F16 ? 0 : 1);
+  e = launch_stage_input_cl(g, input, dtype, output, op_format, (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "layout copy launch: %s", cudaGetErrorString(e));
+}
+
 static void fill_dense(DcnFwdParams *q, int32_t elem, int64_t batch, int64_t channels,
                        int64_t height, int64_t width, int64_t channels_out, int32_t device) {
   memset(q, 0, sizeof(*q));

@@ -965,6 +965,83 @@ dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, in
   }
 }
 
+// The same for 16-bit tensors whose planes are contiguous and whose pixel count is a multiple
+// of eight: 64 channels x 64 pixels per block through an 8 KiB shared-memory tile.  A lane
+// loads eight pixels of two neighbouring channels (two 16-byte loads), interleaves them into
+// eight (channel pair) words and writes those to the pixels' rows; the rows are then read and
+// stored as 16-byte vectors, 128 contiguous bytes per quarter warp.  16-byte chunks of a row
+// are XORed with (pixel & 7), which keeps both shared-memory phases free of bank conflicts.
+__global__ void __launch_bounds__(256)
+dcn_stage_input_cl_16bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int C,
+                         long long HW, long long sn, long long sc) {
+  __shared__ __align__(16) uint32_t tile[64][32];
+  const int n = blockIdx.z;
+  const long long q0 = (long long)blockIdx.x * 64;
+  const int c0 = blockIdx.y * 64;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  {
+    const long long q = q0 + warp * 8;
+    const int ch = c0 + 2 * lane;
+    uint4 va = make_uint4(0u, 0u, 0u, 0u), vb = va;
+    if (q < HW && ch < C) {
+      const uint8_t *src = x + ((long long)n * sn + (long long)ch * sc + q) * 2;
+      va = __ldg(reinterpret_cast<const uint4 *>(src));
+      vb = __ldg(reinterpret_cast<const uint4 *>(src + sc * 2));
+    }
+    const uint32_t a[4] = {va.x, va.y, va.z, va.w}, b[4] = {vb.x, vb.y, vb.z, vb.w};
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int p = warp * 8 + i;
+      tile[p][(((lane >> 2) ^ (p & 7)) << 2) | (lane & 3)] =
+          __byte_perm(a[i >> 1], b[i >> 1], (i & 1) ? 0x7632 : 0x5410);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int vec = threadIdx.x + k * 256;
+    const int p = vec >> 3, o = vec & 7;
+    const uint4 d = *reinterpret_cast<const uint4 *>(&tile[p][(o ^ (p & 7)) << 2]);
+    if (q0 + p < HW && c0 + o * 8 < C)
+      *reinterpret_cast<uint4 *>(y + (((long long)n * HW + q0 + p) * C + c0 + o * 8) * 2) = d;
+  }
+}
+
+// The fp32 counterpart (TF32x3 keeps fp32 data): 32 channels x 64 pixels per block; a lane loads
+// four pixels of one channel per 16-byte load and writes one word per pixel row.
+__global__ void __launch_bounds__(256)
+dcn_stage_input_cl_32bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int C,
+                         long long HW, long long sn, long long sc) {
+  __shared__ __align__(16) uint32_t tile[64][32];
+  const int n = blockIdx.z;
+  const long long q0 = (long long)blockIdx.x * 64;
+  const int c0 = blockIdx.y * 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int pl = warp * 8 + h * 4;  // first of four pixels
+    const int ch = c0 + lane;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (q0 + pl < HW && ch < C)
+      v = __ldg(reinterpret_cast<const uint4 *>(x + ((long long)n * sn + (long long)ch * sc + q0 + pl) * 4));
+    const uint32_t e[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int p = pl + i;
+      tile[p][(((lane >> 2) ^ (p & 7)) << 2) | (lane & 3)] = e[i];
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int vec = threadIdx.x + k * 256;
+    const int p = vec >> 3, o = vec & 7;
+    const uint4 d = *reinterpret_cast<const uint4 *>(&tile[p][(o ^ (p & 7)) << 2]);
+    if (q0 + p < HW && c0 + o * 4 < C)
+      *reinterpret_cast<uint4 *>(y + (((long long)n * HW + q0 + p) * C + c0 + o * 4) * 4) = d;
+  }
+}
+
 namespace {
 template <typename T, typename TO>
 void stage_launch(const Geom &g, const void *input, void *xcl, dim3 grid, cudaStream_t s) {
@@ -983,6 +1060,29 @@ void stage_from(const Geom &g, const void *input, int dtype, void *xcl, dim3 gri
 cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
                                   int op_format, cudaStream_t s) {
   if (g.N == 0) return cudaSuccess;
+  {
+    // 16-bit in, the same 16-bit type out, contiguous planes
+    const bool same16 = dtype != DCN_DTYPE_F32 && op_format != 2 &&
+                        (op_format == 0) == (dtype == DCN_DTYPE_F16);
+    const long long HW = (long long)g.H * g.W;
+    if (same16 && g.in_sw == 1 && g.in_sh == g.W && HW % 8 == 0 && g.C % 8 == 0 &&
+        g.in_sn % 8 == 0 && g.in_sc % 8 == 0 && ((uintptr_t)input & 15) == 0 && g.N <= 65535 &&
+        (g.C + 63) / 64 <= 65535) {
+      dim3 grid((unsigned)((HW + 63) / 64), (unsigned)((g.C + 63) / 64), (unsigned)g.N);
+      dcn_stage_input_cl_16bit<<<grid, 256, 0, s>>>((const uint8_t *)input, (uint8_t *)xcl, g.C, HW,
+                                                    g.in_sn, g.in_sc);
+      return cudaGetLastError();
+    }
+    // fp32 in, fp32 out
+    if (dtype == DCN_DTYPE_F32 && op_format == 2 && g.in_sw == 1 && g.in_sh == g.W && HW % 4 == 0 &&
+        g.C % 4 == 0 && g.in_sn % 4 == 0 && g.in_sc % 4 == 0 && ((uintptr_t)input & 15) == 0 &&
+        g.N <= 65535 && (g.C + 31) / 32 <= 65535) {
+      dim3 grid((unsigned)((HW + 63) / 64), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
+      dcn_stage_input_cl_32bit<<<grid, 256, 0, s>>>((const uint8_t *)input, (uint8_t *)xcl, g.C, HW,
+                                                    g.in_sn, g.in_sc);
+      return cudaGetLastError();
+    }
+  }
   dim3 grid((g.H * g.W + 31) / 32, (g.C + 31) / 32, g.N);
   if (op_format == 2) stage_from<float>(g, input, dtype, xcl, grid, s);
   else if (op_format == 0) stage_from<__half>(g, input, dtype, xcl, grid, s);

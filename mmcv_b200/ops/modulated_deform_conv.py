@@ -133,7 +133,7 @@ def shared_layout(x):
     """bf16 inputs are put in channels-last order once, so that the offset branch and the
     deformable convolution both read them without a restaging pass of their own."""
     if x.dtype in (torch.bfloat16, torch.float16) and x.size(1) % 8 == 0:
-        return x.contiguous(memory_format=torch.channels_last)
+        return ext_module.to_channels_last(x)
     return x
 
 

@@ -273,3 +273,21 @@ def test_weight_image_through_the_c_abi():
     assert torch.equal(outs[0], outs[1])
     p.weight_image_bytes = nimg.value - 16
     assert lib.dcn_fwd(ctypes.byref(p), ws.data_ptr(), nws.value, stream) == -1   # DCN_ERR_ARG
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize('shape', [(2, 64, 16, 24), (3, 72, 9, 8), (1, 20, 7, 5), (2, 130, 6, 6),
+                                   (2, 8, 4, 2)])
+def test_channels_last_copy_is_exact(dtype, shape):
+    # the layout kernel (tiled for contiguous planes, element-wise otherwise) moves bits only
+    from mmcv_b200 import _ext
+    torch.manual_seed(3)
+    x = torch.randn(*shape, device='cuda').to(dtype)
+    got = _ext.to_channels_last(x)
+    assert got.is_contiguous(memory_format=torch.channels_last)
+    assert torch.equal(got, x)
+    # a strided view (channel slice of a wider tensor) and a channels-last input
+    wide = torch.randn(shape[0], shape[1] + 8, shape[2], shape[3], device='cuda').to(dtype)
+    view = wide[:, 8:]
+    assert torch.equal(_ext.to_channels_last(view), view)
+    assert _ext.to_channels_last(got) is got
