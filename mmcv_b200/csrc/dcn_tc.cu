@@ -1107,7 +1107,11 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
   const int cc = ks / Tt, tap = ks - cc * Tt;
   const int ch = tf32 ? 32 : 64;  // channels per row
   uint8_t *out = dst + (size_t)blk * BN * 128 * (tf32 ? 2 : 1);
-  for (int e = threadIdx.x; e < BN * ch; e += blockDim.x) {
+  // blockIdx.y: which sixteen rows of the image (many small blocks: the strided reads of the
+  // weights are latency-bound, so parallelism is what makes this pass short)
+  const int e_end = min(BN, ((int)blockIdx.y + 1) * 16) * ch;
+#pragma unroll 4
+  for (int e = (int)blockIdx.y * 16 * ch + threadIdx.x; e < e_end; e += blockDim.x) {
     const int r = e / ch, j = e - r * ch;
     const int col = nt * BN + r;
     float val = 0.f;
@@ -1132,7 +1136,7 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
 
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight, int dtype,
                                 void *wtiles, cudaStream_t s) {
-  const int blocks = g.groups * tp.NT * tp.S;
+  const dim3 blocks((unsigned)(g.groups * tp.NT * tp.S), (unsigned)((tp.BN + 15) / 16));
   if (dtype == DCN_DTYPE_F32)
     dcn_weight_tiles<float><<<blocks, 256, 0, s>>>((const float *)weight, (uint8_t *)wtiles, g.Cg,
                                                    g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.op_format);
