@@ -159,23 +159,33 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     tp->KC = (g.Cg + ch - 1) / ch;
     tp->S = tp->KC * g.T;
     int ndgc = 1;
-    for (int grp = 0; grp < g.groups; ++grp)
+    bool chunks_share_groups = false;  // two consecutive chunks of a tile with the same deform groups
+    for (int grp = 0; grp < g.groups; ++grp) {
+      int prev_lo = -1, prev_nd = 0;
       for (int cc = 0; cc < tp->KC; ++cc) {
         const int c0 = grp * g.Cg + cc * ch;
         const int c1 = c0 + ch < (grp + 1) * g.Cg ? c0 + ch : (grp + 1) * g.Cg;  // chunk end
         const int lo = c0 / g.cpdg, hi = (c1 - 1) / g.cpdg;
         const int nd = hi - lo + 1;
         if (nd > ndgc) ndgc = nd;
+        if (lo == prev_lo && nd == prev_nd) chunks_share_groups = true;
+        prev_lo = lo;
+        prev_nd = nd;
       }
+    }
     if (ndgc > 15) return false;
     tp->ndgc = ndgc;
     // Producer layout (measured best on every workload tried): two groups of eight warps,
-    // two rows per thread in flight, rows software-pipelined.  The batched layouts (282: same
-    // warps, 342: three groups of four) stay selectable for comparison.
-    const int cfg_default = 1282;
+    // two rows per thread in flight, rows software-pipelined.  When every chunk of a tile has
+    // deform groups of its own, the tap table is rebuilt per chunk anyway, and each group
+    // keeps a table of just its own taps (3282): one group rebuilds while the other gathers.
+    // When chunks share deform groups the table is shared and lives as long as they do (1282).
+    // The batched layouts (282: same warps, 342: three groups of four) stay selectable.
+    const int cfg_default = chunks_share_groups ? 1282 : 3282;
     switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 9999)) {
       case 342: tp->producer_cfg = 342; break;
       case 1282: tp->producer_cfg = 1282; break;
+      case 3282: tp->producer_cfg = 3282; break;
       case 282: tp->producer_cfg = 282; break;
       default: tp->producer_cfg = cfg_default; break;
     }

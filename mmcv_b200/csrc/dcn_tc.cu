@@ -360,6 +360,13 @@ constexpr int kRowInvalid = INT_MIN;
 // Entries of one (tap, deform group) block of the tap table: the rows plus a skew of four, so
 // that the blocks of two deform groups read by one warp fall into different banks.
 constexpr int kTabStride = kBM + 4;
+// (tap, deform group) blocks of the tap table: all taps, or, when every producer group keeps a
+// table of its own taps (producer_cfg thousands digit & 2), groups x ceil(taps / groups).
+__host__ __device__ inline int tab_blocks(const TcPlan &tp, int T) {
+  const int G = (tp.producer_cfg / 100) % 10;
+  const bool own = ((tp.producer_cfg / 1000) & 2) != 0;
+  return (own ? G * ((T + G - 1) / G) : T) * tp.ndgc;
+}
 
 struct SmemLayout {
   uint8_t *a, *b;
@@ -377,12 +384,12 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
   uint8_t *p = base;
   L.a = p; p += (size_t)tp.a_stages * tp.tiles_per_stage * kTileBytes;
   L.b = p; p += (size_t)tp.b_stages * tp.tiles_per_stage * tp.BN * 128;
-  L.tab_w = (uint4 *)p; p += (size_t)T * tp.ndgc * kTabStride * sizeof(uint4);
-  L.tab_off = (uint32_t *)p; p += (size_t)T * tp.ndgc * kTabStride * sizeof(uint32_t);
+  L.tab_w = (uint4 *)p; p += (size_t)tab_blocks(tp, T) * kTabStride * sizeof(uint4);
+  L.tab_off = (uint32_t *)p; p += (size_t)tab_blocks(tp, T) * kTabStride * sizeof(uint32_t);
   L.row_h = (int *)p; p += kBM * sizeof(int);
   L.row_w = (int *)p; p += kBM * sizeof(int);
   L.row_pix = (int *)p; p += kBM * sizeof(int);
-  L.bars = (uint64_t *)p; p += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t);
+  L.bars = (uint64_t *)p; p += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 8) * sizeof(uint64_t);
   L.tmem_slot = (uint32_t *)p; p += 8;
   L.abort_flag = (int *)p; p += 8;
   L.bias_s = (float *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
@@ -394,9 +401,9 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
 size_t tc_smem_bytes(const TcPlan &tp, int T) {
   size_t s = 1024;  // slack for manual 1024-byte alignment
   s += (size_t)tp.tiles_per_stage * ((size_t)tp.a_stages * kTileBytes + (size_t)tp.b_stages * tp.BN * 128);
-  s += (size_t)T * tp.ndgc * kTabStride * (sizeof(uint4) + sizeof(uint32_t));
+  s += (size_t)tab_blocks(tp, T) * kTabStride * (sizeof(uint4) + sizeof(uint32_t));
   s += 3 * kBM * sizeof(int);
-  s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 5) * sizeof(uint64_t) + 16;
+  s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 8) * sizeof(uint64_t) + 16;
   s += (size_t)kEpilogueWarps * tp.BN * sizeof(float) + 16;  // bias staging, one copy per epilogue warp
   return s;
 }
@@ -431,7 +438,8 @@ template <typename TIO, int MODE, int PCFG>
 __global__ void __launch_bounds__((kFirstProducerWarp + ((PCFG / 100) % 10) * ((PCFG / 10) % 10)) * 32, 1)
 dcn_fwd_tc(const __grid_constant__ TcArgs a) {
   constexpr int kGroups = (PCFG / 100) % 10;  // group i fills k-stages i, i+G, ...
-  constexpr bool kPipe = PCFG >= 1000;        // gather software-pipelined over the passes
+  constexpr bool kPipe = ((PCFG / 1000) & 1) != 0;  // gather software-pipelined over the passes
+  constexpr bool kOwn = ((PCFG / 1000) & 2) != 0;   // every group keeps a table of its own taps (below)
   constexpr int kWpg = (PCFG / 10) % 10;    // warps per group
   constexpr int kBatch = PCFG % 10;         // rows of a thread in flight at a time
   constexpr int NPW = kGroups * kWpg;
@@ -470,6 +478,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       mbar_init(tmem_empty + 8 * i, kEpilogueWarps);
     }
     mbar_init(prod_bar, kProdThreads);
+    for (int i = 0; i < 3; ++i) mbar_init(prod_bar + 8 * (1 + i), kWpg * 32);  // one per producer group
     *L.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -652,35 +661,43 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     const int row0 = pwl * 4 + sub;
     const uint32_t soff0 = (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
     // rows whose tap entries this thread computes when a table is rebuilt
-    const int trow = ptid & (kBM - 1);
-    const int tpart = ptid >> 7, tparts = kProdThreads >> 7;
+    // (with per-group tables: the threads of a group share out the group's own entries)
+    const int btid = kOwn ? ptid - gi * kWpg * 32 : ptid;
+    const int trow = btid & (kBM - 1);
+    const int tpart = btid >> 7, tparts = (kOwn ? kWpg * 32 : kProdThreads) >> 7;
+    // first (tap, deform group) block of this group's table
+    const int tab0 = kOwn ? gi * ((g.T + kGroups - 1) / kGroups) * tp.ndgc : 0;
     uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = 0, pp = 0;
     bool ok = true;
     // Producer-only rendezvous on an mbarrier, so that it is bounded like every other wait.
+    const uint32_t my_bar = kOwn ? prod_bar + 8 * (1 + gi) : prod_bar;  // the group's, or everybody's
     auto psync = [&]() -> bool {
-      mbar_arrive(prod_bar);
-      const bool r = mbar_wait(prod_bar, pp, abort_s, a.status, 9);
+      mbar_arrive(my_bar);
+      const bool r = mbar_wait(my_bar, pp, abort_s, a.status, 9);
       pp ^= 1u;
       return r;
     };
     uint32_t tcount = 0;  // global k-stage counter of this CTA (same in every producer)
+    bool built = false;   // (per-group tables) this group has a table that may still be read
     PhaseTimer pt(a.counters, blockIdx.x == 0 && ptid == 0);
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const TileId t = decode_item(item, g, tp);
-      // all producers are done with the previous tile's tables before they are rebuilt
       pt.lap(0);
-      if (!(ok = psync())) break;
-      pt.lap(2);
-      if (ptid < kBM) {
-        const int ho = t.ho0 + (ptid >> tp.tw_log2), wo = t.wo0 + (ptid & tw_mask);
-        const bool valid = ho < g.Ho && wo < g.Wo;
-        L.row_h[ptid] = valid ? ho * g.stride_h - g.pad_h : kRowInvalid;
-        L.row_w[ptid] = wo * g.stride_w - g.pad_w;
-        L.row_pix[ptid] = valid ? ho * g.Wo + wo : 0;
+      if constexpr (!kOwn) {
+        // all producers are done with the previous tile's tables before they are rebuilt
+        if (!(ok = psync())) break;
+        pt.lap(2);
+        if (ptid < kBM) {
+          const int ho = t.ho0 + (ptid >> tp.tw_log2), wo = t.wo0 + (ptid & tw_mask);
+          const bool valid = ho < g.Ho && wo < g.Wo;
+          L.row_h[ptid] = valid ? ho * g.stride_h - g.pad_h : kRowInvalid;
+          L.row_w[ptid] = wo * g.stride_w - g.pad_w;
+          L.row_pix[ptid] = valid ? ho * g.Wo + wo : 0;
+        }
+        pt.lap(0);
+        if (!(ok = psync())) break;
+        pt.lap(2);
       }
-      pt.lap(0);
-      if (!(ok = psync())) break;
-      pt.lap(2);
       // Ask L2 for the offsets and masks of the tile after this one (of this one too, the
       // first time): the tap tables are built from them and would otherwise wait on DRAM.
       for (long long nitem = (item == (long long)blockIdx.x ? item : item + gridDim.x);
@@ -712,27 +729,50 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         const int dg_lo = c0 / g.cpdg;
         const int dg_hi = (min(c0 + MT::kCh, (t.grp + 1) * g.Cg) - 1) / g.cpdg;
         const int nd = dg_hi - dg_lo + 1;
-        if (dg_lo != cur_lo || nd != cur_nd) {
+        // Shared table: rebuilt when the chunk's deform groups differ from the previous
+        // chunk's.  Per-group tables hold only the group's own taps of one chunk (the taps of
+        // the stages it fills), so they are rebuilt every chunk, by the group alone: while one
+        // group rebuilds, the other keeps gathering.  (Chosen by the plan when every chunk has
+        // deform groups of its own anyway.)
+        const int own_t0 = kOwn ? (gi + kGroups - (int)(tcount % kGroups)) % kGroups : 0;
+        if (kOwn || dg_lo != cur_lo || nd != cur_nd) {
           pt.lap(0);
-          if (cur_lo >= 0 && !(ok = psync())) break;
+          if ((kOwn ? built : cur_lo >= 0) && !(ok = psync())) break;
+          built = true;
           pt.lap(2);
           pt.count(6);
           {
             // Each thread fills the entries e = tpart, tpart + tparts, ... of its row.  The
             // offset/mask loads of a batch of entries are all issued before any is used, so
             // their DRAM latency overlaps.
-            const int hb = L.row_h[trow], wb = L.row_w[trow], pix = L.row_pix[trow];
-            const bool rvalid = hb != kRowInvalid;
+            int hb, wb, pix;
+            bool rvalid;
+            if constexpr (kOwn) {
+              const int ho = t.ho0 + (trow >> tp.tw_log2), wo = t.wo0 + (trow & tw_mask);
+              rvalid = ho < g.Ho && wo < g.Wo;
+              hb = ho * g.stride_h - g.pad_h;
+              wb = wo * g.stride_w - g.pad_w;
+              pix = rvalid ? ho * g.Wo + wo : 0;
+            } else {
+              hb = L.row_h[trow]; wb = L.row_w[trow]; pix = L.row_pix[trow];
+              rvalid = hb != kRowInvalid;
+            }
             const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
             const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
-            const int total = g.T * nd;
+            constexpr int kTapStep = kOwn ? kGroups : 1;  // taps of consecutive table blocks
+            const int n_taps = kOwn ? (own_t0 < g.T ? (g.T - own_t0 + kGroups - 1) / kGroups : 0) : g.T;
+            const int total = n_taps * nd;
             constexpr int kEnt = NPW <= 8 ? 9 : (NPW <= 12 ? 6 : 5);  // entries in flight per thread
-            int tap = 0, dgl = tpart, ti = 0, tj = 0;  // entry e <-> (tap, dgl), tap <-> (ti, tj)
+            // entry e <-> (table block j, dgl); block j is tap own_t0 + j * kTapStep <-> (ti, tj)
+            int j = 0, tap = own_t0, dgl = tpart, ti = own_t0 / g.kw, tj = own_t0 - (own_t0 / g.kw) * g.kw;
             auto normalise = [&]() {
               while (dgl >= nd) {
                 dgl -= nd;
-                ++tap;
-                if (++tj == g.kw) { tj = 0; ++ti; }
+                ++j;
+                tap += kTapStep;
+#pragma unroll
+                for (int q = 0; q < kTapStep; ++q)
+                  if (++tj == g.kw) { tj = 0; ++ti; }
               }
             };
             normalise();
@@ -744,15 +784,16 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                 oh[k] = 0; ow[k] = 0; mm[k] = 0;
                 where[k] = -1;
                 if (e0 + k * tparts < total) {
-                  where[k] = tap | (dgl << 12) | (ti << 16) | (tj << 24);
+                  where[k] = j | (dgl << 12) | (ti << 16) | (tj << 24);
+                  const int tap_k = tap;
                   if (rvalid) {
                     if (offp) {
-                      const long long ch = ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap) * plane;
+                      const long long ch = ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap_k) * plane;
                       oh[k] = ldg_raw_ordered(offp + ch);
                       ow[k] = ldg_raw_ordered(offp + ch + plane);
                     }
                     if (mskp)
-                      mm[k] = ldg_raw_ordered(mskp + ((long long)(dg_lo + dgl) * g.T + tap) * plane);
+                      mm[k] = ldg_raw_ordered(mskp + ((long long)(dg_lo + dgl) * g.T + tap_k) * plane);
                   }
                   dgl += tparts;
                   normalise();
@@ -799,7 +840,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   wq.z = wt.z == 0.f ? 0u : __float_as_uint(wt.z);
                   wq.w = wt.w == 0.f ? 0u : __float_as_uint(wt.w);
                 }
-                const int slot = (etap * tp.ndgc + edgl) * kTabStride + trow;
+                const int slot = (tab0 + etap * tp.ndgc + edgl) * kTabStride + trow;
                 L.tab_w[slot] = wq;
                 L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * MT::kEsz);
               }
@@ -816,12 +857,14 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         const int c = vvalid ? c0 + v * MT::kCpv : c0;
         const int dgl = c / g.cpdg - dg_lo;
         const uint32_t c2 = (uint32_t)c * MT::kEsz;
+        int own_j = 0;  // this group's stages of the chunk so far
         for (int tap = 0; tap < g.T; ++tap, ++tcount) {
           if (kGroups > 1 && (int)(tcount % kGroups) != gi) continue;
           pt.lap(0);
           pt.count(5);
           uint8_t *stage = L.a + (size_t)sa * kAStageBytes + soff0;
-          const int slot0 = (tap * tp.ndgc + dgl) * kTabStride + row0;
+          const int slot0 = (tab0 + (kOwn ? own_j : tap) * tp.ndgc + dgl) * kTabStride + row0;
+          ++own_j;
           const uint4 z = make_uint4(0u, 0u, 0u, 0u);
           if constexpr (kPipe) {
             // kBatch register sets rotate over the passes: the loads of pass p + kBatch - 1 are
@@ -1193,6 +1236,7 @@ cudaError_t launch_mode(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   switch (tp.producer_cfg) {
     case 342: return launch_one<TIO, MODE, 342>(a, tp, s);
     case 1282: return launch_one<TIO, MODE, 1282>(a, tp, s);
+    case 3282: return launch_one<TIO, MODE, 3282>(a, tp, s);
     case 282: return launch_one<TIO, MODE, 282>(a, tp, s);
     default: return launch_one<TIO, MODE, 1282>(a, tp, s);
   }
