@@ -40,9 +40,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
 # committed ncu summary under profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    # 356.9 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
+    # 357.4 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
     # by the batch: traffic grows in proportion to the samples processed
-    'c5': 356.9e6 / 16,
+    'c5': 357.4e6 / 16,
 }
 
 
@@ -664,6 +664,12 @@ def main():
         hbm = peaks.get('hbm_gbs', 6650.0)
         achieved = fl_rank / (k_main * 1e-3) / 1e12 if k_main > 0 else 0.0
         roof_ms = max(fl_rank / (peak_tf * 1e12), by_rank / (hbm * 1e9)) * 1e3
+        # the channels-last restaging pass is a pure copy: 1 read + 1 write per input element
+        stage_bytes = 2.0 * n * wl['C'] * wl['H'] * wl['W'] * (2 if args.dtype == 'bf16' else 4)
+        stage_roof = (dict(bound='hbm', kernel='dcn_stage_input_cl_16bit' if args.dtype == 'bf16' else
+                           'dcn_stage_input_cl_32bit', achieved=stage_bytes / (k_stage * 1e-3) / 1e9,
+                           peak=hbm, unit='GB/s', frac=stage_bytes / (k_stage * 1e-3) / 1e9 / hbm)
+                      if k_stage > 0 else None)
         traffic = NCU_TRAFFIC_BYTES.get(args.workload) if args.dtype == 'bf16' else None
         traffic = traffic * n if traffic is not None else None
         line = dict(
@@ -685,6 +691,7 @@ def main():
                                 note='slower of FLOPs at the bf16 peak and compulsory bytes at HBM '
                                      'bandwidth, per GPU; frac uses the whole step (all launches)'),
             kernel_ms=dict(stage_input_cl=k_stage, weight_tiles=k_wt, main=k_main),
+            stage_roofline=stage_roof,
             roofline=dict(bound='tensor', achieved=achieved, peak=peak_tf, unit='TFLOP/s',
                           frac=achieved / peak_tf, traffic=traffic, peak_source=peak_src,
                           frac_of_sustained=(achieved / peaks['bf16_tflops_sustained']
