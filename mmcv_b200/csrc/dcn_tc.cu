@@ -633,7 +633,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
         for (int ks = 0; ks < tp.S; ++ks) {
           pt.lap(15);
-          ok = mbar_wait<true>(empty_b + 8 * sb, pb ^ 1u, abort_s, a.status, 7);
+          ok = mbar_wait(empty_b + 8 * sb, pb ^ 1u, abort_s, a.status, 7);
           if (!ok) break;
           pt.lap(14);
           mbar_arrive_expect_tx(full_b + 8 * sb, b_stage_bytes);

@@ -2,7 +2,8 @@
 from .deform_conv import DeformConv2d, DeformConv2dFunction, DeformConv2dPack, deform_conv2d
 from .modulated_deform_conv import (ModulatedDeformConv2d, ModulatedDeformConv2dFunction,
                                     ModulatedDeformConv2dPack, modulated_deform_conv2d)
+from .saconv import SAConv2d
 
 __all__ = ['DeformConv2d', 'DeformConv2dFunction', 'DeformConv2dPack', 'deform_conv2d',
            'ModulatedDeformConv2d', 'ModulatedDeformConv2dFunction',
-           'ModulatedDeformConv2dPack', 'modulated_deform_conv2d']
+           'ModulatedDeformConv2dPack', 'modulated_deform_conv2d', 'SAConv2d']
