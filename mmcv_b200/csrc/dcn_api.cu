@@ -153,6 +153,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     // 16-bit contraction use bf16
     tp->op_format = tf32 ? 2 : (p->dtype == DCN_DTYPE_F16 ? 0 : 1);
     tp->ch_per_stage = ch;
+    tp->io_bytes = p->dtype == DCN_DTYPE_F32 ? 4 : 2;
     tp->NT = (g.Cog + cap - 1) / cap;
     const int per = (g.Cog + tp->NT - 1) / tp->NT;
     tp->BN = (per + 31) / 32 * 32;

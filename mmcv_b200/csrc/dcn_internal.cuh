@@ -55,7 +55,8 @@ struct TcPlan {
   int tiles_per_stage;     // 1: 16-bit operands; 2: TF32x3 (high part and remainder)
   int op_format;           // tensor-core operand format: 0 fp16, 1 bf16, 2 tf32
   int ch_per_stage;        // input channels per k-stage: 64 (bf16) or 32 (TF32x3)
-  int producer_cfg;        // groups*100 + warps_per_group*10 + rows in flight per thread
+  int producer_cfg;        // [flags*1000 +] groups*100 + warps_per_group*10 + rows in flight per thread
+  int io_bytes;            // element size of the tensors (bias staging in the epilogue)
 };
 
 enum { kBM = 128 };

@@ -49,12 +49,15 @@ constexpr int kTileBytes = kBM * 128;  // one operand tile: 128 rows of 128 byte
 enum { kModeBf16 = 0, kModeTf32x3 = 1, kModeF16 = 2 };
 template <int MODE> struct ModeTraits;
 template <> struct ModeTraits<kModeBf16> {
+  using TabW = uint2;  // table entry: four 16-bit corner weights
   static constexpr int kCh = 64, kCpv = 8, kEsz = 2, kTiles = 1;
 };
 template <> struct ModeTraits<kModeF16> {
+  using TabW = uint2;
   static constexpr int kCh = 64, kCpv = 8, kEsz = 2, kTiles = 1;
 };
 template <> struct ModeTraits<kModeTf32x3> {
+  using TabW = uint4;  // table entry: four fp32 corner weights
   static constexpr int kCh = 32, kCpv = 4, kEsz = 4, kTiles = 2;
 };
 
@@ -286,6 +289,16 @@ __device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 h) {
   return *reinterpret_cast<const uint32_t *>(&h);
 }
 
+// A table entry's corner weights in the form the blends take: each 16-bit weight twice (a
+// pair), or the four fp32 weights as they are.
+template <int MODE>
+__device__ __forceinline__ uint4 table_weights(const uint2 &w) {
+  return make_uint4(__byte_perm(w.x, 0u, 0x1010), __byte_perm(w.x, 0u, 0x3232),
+                    __byte_perm(w.y, 0u, 0x1010), __byte_perm(w.y, 0u, 0x3232));
+}
+template <int MODE>
+__device__ __forceinline__ uint4 table_weights(const uint4 &w) { return w; }
+
 // Bilinear blend of four 8-channel bf16 corner vectors on packed bf16 FMAs: one multiply
 // and three fused multiply-adds per channel pair, each rounding to bf16.  `w` holds each
 // corner weight twice (a bf16 pair).
@@ -362,6 +375,8 @@ constexpr int kRowInvalid = INT_MIN;
 constexpr int kTabStride = kBM + 4;
 // (tap, deform group) blocks of the tap table: all taps, or, when every producer group keeps a
 // table of its own taps (producer_cfg thousands digit & 2), groups x ceil(taps / groups).
+// bytes of a table entry's corner weights: four 16-bit values, or four fp32 for TF32x3
+__host__ __device__ inline size_t tab_weight_bytes(const TcPlan &tp) { return tp.op_format == 2 ? 16 : 8; }
 __host__ __device__ inline int tab_blocks(const TcPlan &tp, int T) {
   const int G = (tp.producer_cfg / 100) % 10;
   const bool own = ((tp.producer_cfg / 1000) & 2) != 0;
@@ -370,13 +385,13 @@ __host__ __device__ inline int tab_blocks(const TcPlan &tp, int T) {
 
 struct SmemLayout {
   uint8_t *a, *b;
-  uint4 *tab_w;        // four corner weights per (tap, deform group, row)
+  uint8_t *tab_w;      // four corner weights per (tap, deform group, row): 8 or 16 bytes each
   uint32_t *tab_off;   // byte offset of the top-left corner from the sample's base
   int *row_h, *row_w, *row_pix;
   uint64_t *bars;
   uint32_t *tmem_slot;
   int *abort_flag;
-  float *bias_s;       // bias of the tile's output channels as fp32, one copy per epilogue warp
+  uint8_t *bias_s;     // bias of the tile's output channels in the tensors' type, two copies (tile parity)
 };
 
 __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int T) {
@@ -384,7 +399,7 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
   uint8_t *p = base;
   L.a = p; p += (size_t)tp.a_stages * tp.tiles_per_stage * kTileBytes;
   L.b = p; p += (size_t)tp.b_stages * tp.tiles_per_stage * tp.BN * 128;
-  L.tab_w = (uint4 *)p; p += (size_t)tab_blocks(tp, T) * kTabStride * sizeof(uint4);
+  L.tab_w = p; p += (size_t)tab_blocks(tp, T) * kTabStride * tab_weight_bytes(tp);
   L.tab_off = (uint32_t *)p; p += (size_t)tab_blocks(tp, T) * kTabStride * sizeof(uint32_t);
   L.row_h = (int *)p; p += kBM * sizeof(int);
   L.row_w = (int *)p; p += kBM * sizeof(int);
@@ -392,7 +407,7 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
   L.bars = (uint64_t *)p; p += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 8) * sizeof(uint64_t);
   L.tmem_slot = (uint32_t *)p; p += 8;
   L.abort_flag = (int *)p; p += 8;
-  L.bias_s = (float *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
+  L.bias_s = (uint8_t *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
   return L;
 }
 
@@ -401,10 +416,10 @@ __device__ __forceinline__ SmemLayout carve(uint8_t *base, const TcPlan &tp, int
 size_t tc_smem_bytes(const TcPlan &tp, int T) {
   size_t s = 1024;  // slack for manual 1024-byte alignment
   s += (size_t)tp.tiles_per_stage * ((size_t)tp.a_stages * kTileBytes + (size_t)tp.b_stages * tp.BN * 128);
-  s += (size_t)tab_blocks(tp, T) * kTabStride * (sizeof(uint4) + sizeof(uint32_t));
+  s += (size_t)tab_blocks(tp, T) * kTabStride * (tab_weight_bytes(tp) + sizeof(uint32_t));
   s += 3 * kBM * sizeof(int);
   s += (size_t)(2 * tp.a_stages + 2 * tp.b_stages + 8) * sizeof(uint64_t) + 16;
-  s += (size_t)kEpilogueWarps * tp.BN * sizeof(float) + 16;  // bias staging, one copy per epilogue warp
+  s += (size_t)2 * tp.BN * tp.io_bytes + 16;  // bias staging, one copy per accumulator buffer
   return s;
 }
 
@@ -506,10 +521,9 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     const int row = warp * 32 + lane;
     const int ty = row >> tp.tw_log2, tx = row & tw_mask;
     const bool act_any = g.act == DCN_ACT_SIGMOID && g.act_hi > g.act_lo;
-    float *bias_w = L.bias_s + warp * tp.BN;
     PhaseTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     long long li = 0;
-    int staged_co0 = -1;
+    int staged_co0[2] = {-1, -1};
     for (long long item = blockIdx.x; item < items; item += gridDim.x, ++li) {
       const TileId t = decode_item(item, g, tp);
       const int buf = (int)(li & 1);
@@ -519,14 +533,17 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       const int ncols = min(tp.BN, g.Cog - t.nt * tp.BN);
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
       TIO *orow = out + (long long)t.n * g.out_sn + (long long)co0 * plane + (long long)ho * g.Wo + wo;
-      if (co0 != staged_co0) {
-        // (re)stage the bias: every epilogue warp keeps a copy of its own, so that no
-        // rendezvous between warps is needed
+      // Bias copy of this accumulator buffer.  When its channels change, every epilogue warp
+      // writes the whole copy (the same values: no rendezvous between the warps is needed);
+      // a warp cannot be two tiles ahead of another, because the buffer it would then stage
+      // for is only handed over once all four warps have released it.
+      TIO *bias_w = reinterpret_cast<TIO *>(L.bias_s) + buf * tp.BN;
+      if (co0 != staged_co0[buf]) {
         __syncwarp();
         for (int i = lane; i < tp.BN; i += 32)
-          bias_w[i] = (bias && i < ncols) ? ld_as_float(bias, co0 + i) : 0.f;
+          st_from_float(bias_w, i, (bias && i < ncols) ? ld_as_float(bias, co0 + i) : 0.f);
         __syncwarp();
-        staged_co0 = co0;
+        staged_co0[buf] = co0;
       }
       const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
       pt.lap(13);
@@ -538,13 +555,14 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         uint32_t r[32];
         tmem_ld32(taddr + (uint32_t)c0, r);
         tmem_ld_wait();
-        const float4 *bs = reinterpret_cast<const float4 *>(bias_w + c0);
+        const TIO *bs = bias_w + c0;
         TIO *oc = orow + (long long)c0 * plane;
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
-          const float4 b4 = bs[j4];
-          float v[4] = {__uint_as_float(r[4 * j4]) + b4.x, __uint_as_float(r[4 * j4 + 1]) + b4.y,
-                        __uint_as_float(r[4 * j4 + 2]) + b4.z, __uint_as_float(r[4 * j4 + 3]) + b4.w};
+          float v[4] = {__uint_as_float(r[4 * j4]) + ld_as_float(bs, 4 * j4),
+                        __uint_as_float(r[4 * j4 + 1]) + ld_as_float(bs, 4 * j4 + 1),
+                        __uint_as_float(r[4 * j4 + 2]) + ld_as_float(bs, 4 * j4 + 2),
+                        __uint_as_float(r[4 * j4 + 3]) + ld_as_float(bs, 4 * j4 + 3)};
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int j = 4 * j4 + k;
@@ -665,6 +683,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     const int btid = kOwn ? ptid - gi * kWpg * 32 : ptid;
     const int trow = btid & (kBM - 1);
     const int tpart = btid >> 7, tparts = (kOwn ? kWpg * 32 : kProdThreads) >> 7;
+    typename MT::TabW *const tabw = reinterpret_cast<typename MT::TabW *>(L.tab_w);
     // first (tap, deform group) block of this group's table
     const int tab0 = kOwn ? gi * ((g.T + kGroups - 1) / kGroups) * tp.ndgc : 0;
     uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = 0, pp = 0;
@@ -812,36 +831,34 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   tap_weights(RawOf<TIO>::to_float(oh[k]), RawOf<TIO>::to_float(ow[k]),
                               mskp ? RawOf<TIO>::to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
                               wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
-                uint4 wq;
-                if constexpr (MODE == kModeBf16) {
-                  wq.x = bf162_bits(__float2bfloat162_rn(wt.x));
-                  wq.y = bf162_bits(__float2bfloat162_rn(wt.y));
-                  wq.z = bf162_bits(__float2bfloat162_rn(wt.z));
-                  wq.w = bf162_bits(__float2bfloat162_rn(wt.w));
-                  // a weight that rounds to (signed) zero is dropped: the corner is not read
-                  wq.x = (wq.x & 0x7fff7fffu) ? wq.x : 0u;
-                  wq.y = (wq.y & 0x7fff7fffu) ? wq.y : 0u;
-                  wq.z = (wq.z & 0x7fff7fffu) ? wq.z : 0u;
-                  wq.w = (wq.w & 0x7fff7fffu) ? wq.w : 0u;
-                } else if constexpr (MODE == kModeF16) {
-                  const __half2 h0 = __float2half2_rn(wt.x), h1 = __float2half2_rn(wt.y),
-                                h2 = __float2half2_rn(wt.z), h3 = __float2half2_rn(wt.w);
-                  wq.x = *reinterpret_cast<const uint32_t *>(&h0);
-                  wq.y = *reinterpret_cast<const uint32_t *>(&h1);
-                  wq.z = *reinterpret_cast<const uint32_t *>(&h2);
-                  wq.w = *reinterpret_cast<const uint32_t *>(&h3);
-                  wq.x = (wq.x & 0x7fff7fffu) ? wq.x : 0u;
-                  wq.y = (wq.y & 0x7fff7fffu) ? wq.y : 0u;
-                  wq.z = (wq.z & 0x7fff7fffu) ? wq.z : 0u;
-                  wq.w = (wq.w & 0x7fff7fffu) ? wq.w : 0u;
-                } else {
+                // a weight that is (or rounds to) zero is stored as the integer 0: such a
+                // corner is not read
+                typename MT::TabW wq;
+                if constexpr (MODE == kModeTf32x3) {
                   wq.x = wt.x == 0.f ? 0u : __float_as_uint(wt.x);
                   wq.y = wt.y == 0.f ? 0u : __float_as_uint(wt.y);
                   wq.z = wt.z == 0.f ? 0u : __float_as_uint(wt.z);
                   wq.w = wt.w == 0.f ? 0u : __float_as_uint(wt.w);
+                } else {
+                  uint32_t b0, b1, b2, b3;
+                  if constexpr (MODE == kModeBf16) {
+                    b0 = __bfloat16_as_ushort(__float2bfloat16_rn(wt.x));
+                    b1 = __bfloat16_as_ushort(__float2bfloat16_rn(wt.y));
+                    b2 = __bfloat16_as_ushort(__float2bfloat16_rn(wt.z));
+                    b3 = __bfloat16_as_ushort(__float2bfloat16_rn(wt.w));
+                  } else {
+                    b0 = __half_as_ushort(__float2half_rn(wt.x));
+                    b1 = __half_as_ushort(__float2half_rn(wt.y));
+                    b2 = __half_as_ushort(__float2half_rn(wt.z));
+                    b3 = __half_as_ushort(__float2half_rn(wt.w));
+                  }
+                  b0 = (b0 & 0x7fffu) ? b0 : 0u; b1 = (b1 & 0x7fffu) ? b1 : 0u;
+                  b2 = (b2 & 0x7fffu) ? b2 : 0u; b3 = (b3 & 0x7fffu) ? b3 : 0u;
+                  wq.x = b0 | (b1 << 16);
+                  wq.y = b2 | (b3 << 16);
                 }
                 const int slot = (tab0 + etap * tp.ndgc + edgl) * kTabStride + trow;
-                L.tab_w[slot] = wq;
+                tabw[slot] = wq;
                 L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * MT::kEsz);
               }
             }
@@ -875,7 +892,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             uint32_t tok = 0;
             auto issue = [&](int p) {
               const int sl = p % kBatch;
-              wq[sl] = vvalid ? L.tab_w[slot0 + p * kRowStep] : z;
+              wq[sl] = vvalid ? table_weights<MODE>(tabw[slot0 + p * kRowStep]) : z;
               const uint32_t o = L.tab_off[slot0 + p * kRowStep] + c2;
               q[sl][0] = ldg16_pinned(xb + o, wq[sl].x, tok);
               q[sl][1] = ldg16_pinned(xb + (uint32_t)(o + cW2), wq[sl].y, tok);
@@ -914,7 +931,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
             uint4 q[kBatch][4], wq[kBatch];
 #pragma unroll
             for (int ps = 0; ps < kBatch; ++ps) {
-              wq[ps] = vvalid ? L.tab_w[slot0 + (p0 + ps) * kRowStep] : z;
+              wq[ps] = vvalid ? table_weights<MODE>(tabw[slot0 + (p0 + ps) * kRowStep]) : z;
               const uint32_t o = L.tab_off[slot0 + (p0 + ps) * kRowStep] + c2;
               q[ps][0] = wq[ps].x ? __ldg((const uint4 *)(xb + o)) : z;
               q[ps][1] = wq[ps].y ? __ldg((const uint4 *)(xb + (uint32_t)(o + cW2))) : z;
