@@ -722,20 +722,22 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       for (long long nitem = (item == (long long)blockIdx.x ? item : item + gridDim.x);
            nitem <= item + gridDim.x && nitem < items; nitem += gridDim.x) {
         const TileId nt_ = decode_item(nitem, g, tp);
-        const int th = kBM >> tp.tw_log2;
-        const int lines_row = ((int)sizeof(TIO) << tp.tw_log2) + 127 >> 7;  // 128-byte lines per tile row
+        // 128-byte lines per tile row, rows per tile: both powers of two, so the index of a
+        // line splits into (plane, row, line) with shifts
+        const int lr_log2 = max(0, tp.tw_log2 + (sizeof(TIO) == 4 ? 2 : 1) - 7);
+        const int pp_log2 = (7 - tp.tw_log2) + lr_log2;  // lines per plane
         const int planes_off = off ? g.dg * 2 * g.T : 0;
         const int planes = planes_off + (msk ? g.dg * g.T : 0);
-        const int per_plane = th * lines_row;
-        for (int idx = ptid; idx < planes * per_plane; idx += kProdThreads) {
-          const int pl = idx / per_plane, r = idx - pl * per_plane;
-          const int ry = r / lines_row, rl = r - ry * lines_row;
+        const TIO *obase = off ? off + (long long)nt_.n * g.off_sn : nullptr;
+        const TIO *mbase = msk ? msk + (long long)nt_.n * g.msk_sn : nullptr;
+        for (int idx = ptid; idx < (planes << pp_log2); idx += kProdThreads) {
+          const int pl = idx >> pp_log2, r = idx & ((1 << pp_log2) - 1);
+          const int ry = r >> lr_log2, rl = r & ((1 << lr_log2) - 1);
           const int ho = nt_.ho0 + ry;
           if (ho >= g.Ho) continue;
           const long long pixel = (long long)ho * g.Wo + nt_.wo0;
-          const TIO *ptr = pl < planes_off
-                               ? off + (long long)nt_.n * g.off_sn + (long long)pl * plane + pixel
-                               : msk + (long long)nt_.n * g.msk_sn + (long long)(pl - planes_off) * plane + pixel;
+          const TIO *ptr = pl < planes_off ? obase + (long long)pl * plane + pixel
+                                           : mbase + (long long)(pl - planes_off) * plane + pixel;
           if (nt_.wo0 + rl * (int)(128 / sizeof(TIO)) < g.Wo)
             prefetch_l2(reinterpret_cast<const char *>(ptr) + rl * 128);
         }
