@@ -40,9 +40,9 @@ WORKLOADS = {
 # dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
 # committed ncu summary under profiles/ (None until a capture exists for the workload).
 NCU_TRAFFIC_BYTES = {
-    # 357.4 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
+    # 356.9 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
     # by the batch: traffic grows in proportion to the samples processed
-    'c5': 357.4e6 / 16,
+    'c5': 356.9e6 / 16,
 }
 
 

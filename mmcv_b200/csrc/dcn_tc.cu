@@ -1240,7 +1240,15 @@ cudaError_t launch_one(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
   }
   // leave what the kernel does not need of the SM's 256 KB to L1: the gather lives on it
   static std::atomic<int> carve_pct[64];
-  const int pct = (int)((tp.smem + 1024) * 100 / 233472) + 1;
+  // (the smallest shared-memory configuration that holds the block and its 1 KB system
+  // reserve; the percentage is rounded down so that the driver lands on that configuration)
+  int pct = 100;
+  {
+    const size_t need = tp.smem + 1024;
+    const size_t configs_kb[] = {8, 16, 32, 64, 100, 132, 164, 196, 228};
+    for (size_t kb : configs_kb)
+      if (kb * 1024 >= need) { pct = (int)(kb * 1024 * 100 / 233472); break; }
+  }
   if (carve_pct[dev & 63].load(std::memory_order_acquire) != pct) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout,
                              pct > 100 ? 100 : pct);
