@@ -97,6 +97,9 @@ typedef struct DcnPlanInfo {
   int64_t smem_bytes;     /* dynamic shared memory of the main kernel */
   int64_t Ho, Wo;
   size_t workspace_bytes;
+  int32_t operand_stages, weight_stages; /* depth of the two shared-memory rings (tcgen05 path) */
+  int32_t producer_layout; /* tcgen05 path: groups*100 + warps per group*10 + rows in flight,
+                            * +1000 rows software-pipelined, +2000 per-group tap tables */
 } DcnPlanInfo;
 
 int dcn_abi_version(void);

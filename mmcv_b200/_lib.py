@@ -56,6 +56,8 @@ class DcnPlanInfo(ctypes.Structure):
         ('grid', ctypes.c_int32), ('block', ctypes.c_int32),
         ('smem_bytes', ctypes.c_int64), ('Ho', ctypes.c_int64),
         ('Wo', ctypes.c_int64), ('workspace_bytes', ctypes.c_size_t),
+        ('operand_stages', ctypes.c_int32), ('weight_stages', ctypes.c_int32),
+        ('producer_layout', ctypes.c_int32),
     ]
 
 

@@ -339,6 +339,9 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   info->Ho = pl.g.Ho;
   info->Wo = pl.g.Wo;
   info->workspace_bytes = pl.ws.total;
+  info->operand_stages = pl.tc ? pl.tp.a_stages : 0;
+  info->weight_stages = pl.tc ? pl.tp.b_stages : 0;
+  info->producer_layout = pl.tc ? pl.tp.producer_cfg : 0;
   return DCN_OK;
 }
 

@@ -61,6 +61,12 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
+    # every 64-channel chunk has deform groups of its own: per-group tap tables, and four
+    # operand stages inside the 164 KB shared-memory configuration
+    assert info.producer_layout == 3282 and info.block == (6 + 16) * 32
+    assert (info.operand_stages, info.weight_stages) == (4, 2) and info.smem_bytes <= 167936 - 1024
+    rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
+    assert rc == 0 and info.producer_layout == 1282      # chunks share their deform group
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
