@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DCN_ABI_VERSION 2
+#define DCN_ABI_VERSION 3
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
@@ -85,6 +85,16 @@ typedef struct DcnFwdParams {
    * problem shape; dcn_fwd then skips its own re-layout of `weight`.  NULL = none. */
   const void *weight_image;
   int64_t weight_image_bytes;
+  /* Optional layout of offset and mask inside a sample: element strides between channels and
+   * between neighbouring output pixels (row-major over Ho x Wo).  All zero = the reference
+   * layout (channel stride Ho*Wo, pixel stride 1).  A channels-last tensor of Ct channels has
+   * channel stride 1 and pixel stride Ct, so the offset and mask thirds of a channels-last
+   * branch output can be passed as they lie.  Tensor-core path only (others:
+   * DCN_ERR_UNSUPPORTED). */
+  int64_t offset_channel_stride, offset_pixel_stride, mask_channel_stride, mask_pixel_stride;
+  int32_t mask_act;   /* DCN_ACT_SIGMOID: the mask tensor holds logits (what the Pack layers'
+                       * branch produces before its sigmoid).  Tensor-core path only. */
+  int32_t reserved0;
 } DcnFwdParams;
 
 /* What a call will do; filled by dcn_fwd_plan without touching the device. */

@@ -127,9 +127,12 @@ def _weight_image(lib, p, weight, dev, stream):
 
 def forward(input, offset, mask, weight, bias, output, stride, padding, dilation,
             groups, deform_groups, math_mode=None, act=_lib.ACT_NONE, act_range=(0, 0),
-            offset_batch_stride=0, mask_batch_stride=0, out_batch_stride=0):
+            offset_batch_stride=0, mask_batch_stride=0, out_batch_stride=0,
+            offset_strides=(0, 0), mask_strides=(0, 0), mask_act=_lib.ACT_NONE):
     """Launch one forward on the current stream.  offset=None means an ordinary
-    convolution, mask=None the unmodulated (v1) operator.  Returns the plan path."""
+    convolution, mask=None the unmodulated (v1) operator.  offset_strides / mask_strides are
+    (channel, pixel) element strides inside a sample, (0, 0) = dense planes; mask_act =
+    ACT_SIGMOID says the mask tensor holds logits.  Returns the workspace tensor."""
     lib = _lib.load()
     dev = _require_cuda(input=input, offset=offset, mask=mask, weight=weight, bias=bias,
                         output=output)
@@ -156,6 +159,9 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     p.offset_batch_stride = offset_batch_stride
     p.mask_batch_stride = mask_batch_stride
     p.out_batch_stride = out_batch_stride
+    p.offset_channel_stride, p.offset_pixel_stride = offset_strides
+    p.mask_channel_stride, p.mask_pixel_stride = mask_strides
+    p.mask_act = mask_act
     p.act, p.act_lo, p.act_hi = act, act_range[0], act_range[1]
     p.device = dev.index if dev.index is not None else torch.cuda.current_device()
     nbytes = ctypes.c_size_t(0)
@@ -173,6 +179,40 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
                 raise RuntimeError(f'dcn_b200: device-side wait {st.value} timed out; the '
                                    'output is not valid')
     return ws
+
+
+def forward_from_branch(input, branch, n_offset, weight, bias, output, stride, padding, dilation,
+                        groups, deform_groups):
+    """Deformable convolution whose offsets are the first n_offset channels of `branch` (the
+    raw output of a Pack layer's offset convolution, NCHW-contiguous or channels-last) and
+    whose mask logits are the remaining channels (none: the v1 operator).  The kernel reads
+    both where they lie and applies the sigmoid itself.  Returns False, having done nothing,
+    when this problem does not run on the tensor-core kernel."""
+    if branch.dim() != 4 or branch.dtype != input.dtype:
+        return False
+    N, Ct, Ho, Wo = branch.shape
+    if N == 0 or (N > 1 and branch.stride(0) != Ct * Ho * Wo):
+        return False   # (an empty batch takes the ordinary route)
+    if branch.is_contiguous():
+        strides = (Ho * Wo, 1)
+    elif branch.is_contiguous(memory_format=torch.channels_last):
+        strides = (1, Ct)
+    else:
+        return False
+    modulated = n_offset < Ct
+    offset = branch
+    # a one-element view that starts at the first mask channel (same storage, no copy)
+    mask = (branch.as_strided((1,), (1,), branch.storage_offset() + n_offset * strides[0])
+            if modulated else None)
+    try:
+        forward(input, offset, mask, weight, bias, output, stride, padding, dilation, groups,
+                deform_groups, offset_batch_stride=Ct * Ho * Wo,
+                mask_batch_stride=Ct * Ho * Wo if modulated else 0, offset_strides=strides,
+                mask_strides=strides if modulated else (0, 0),
+                mask_act=_lib.ACT_SIGMOID if modulated else _lib.ACT_NONE)
+    except _lib.Unsupported:
+        return False
+    return True
 
 
 def to_channels_last(x):

@@ -14,7 +14,7 @@ MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 2   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
+ABI_VERSION = 3   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
@@ -45,6 +45,9 @@ class DcnFwdParams(ctypes.Structure):
         ('act', ctypes.c_int32), ('act_lo', ctypes.c_int32),
         ('act_hi', ctypes.c_int32), ('device', ctypes.c_int32),
         ('weight_image', ctypes.c_void_p), ('weight_image_bytes', ctypes.c_int64),
+        ('offset_channel_stride', ctypes.c_int64), ('offset_pixel_stride', ctypes.c_int64),
+        ('mask_channel_stride', ctypes.c_int64), ('mask_pixel_stride', ctypes.c_int64),
+        ('mask_act', ctypes.c_int32), ('reserved0', ctypes.c_int32),
     ]
 
 
@@ -111,6 +114,13 @@ def last_error():
     return load().dcn_last_error().decode()
 
 
+class Unsupported(RuntimeError):
+    """DCN_ERR_UNSUPPORTED: a valid problem that this library (or the requested kernel) does
+    not take."""
+
+
 def check(rc):
+    if rc == -2:
+        raise Unsupported(f'dcn_b200: {last_error()} (code {rc})')
     if rc != 0:
         raise RuntimeError(f'dcn_b200: {last_error()} (code {rc})')

@@ -111,6 +111,13 @@ int build_geom(const DcnFwdParams *p, Geom *g) {
   g->off_sn = p->offset_batch_stride ? p->offset_batch_stride : (long long)g->dg * 2 * g->T * Ho * Wo;
   g->msk_sn = p->mask_batch_stride ? p->mask_batch_stride : (long long)g->dg * g->T * Ho * Wo;
   g->out_sn = p->out_batch_stride ? p->out_batch_stride : (long long)g->Co * Ho * Wo;
+  g->off_cs = p->offset_channel_stride ? p->offset_channel_stride : (long long)Ho * Wo;
+  g->off_ps = p->offset_pixel_stride ? p->offset_pixel_stride : 1;
+  g->msk_cs = p->mask_channel_stride ? p->mask_channel_stride : (long long)Ho * Wo;
+  g->msk_ps = p->mask_pixel_stride ? p->mask_pixel_stride : 1;
+  g->mask_act = p->mask_act;
+  if (g->mask_act != DCN_ACT_NONE && g->mask_act != DCN_ACT_SIGMOID)
+    return fail(DCN_ERR_ARG, "unknown mask activation %d", g->mask_act);
   g->act = p->act; g->act_lo = p->act_lo; g->act_hi = p->act_hi;
   if (g->act != DCN_ACT_NONE && g->act != DCN_ACT_SIGMOID)
     return fail(DCN_ERR_ARG, "unknown activation %d", g->act);
@@ -296,6 +303,14 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
     return fail(DCN_ERR_UNSUPPORTED,
                 "bf16 tensor-core contraction needs C/groups %% 8 == 0 and C/deformable_group %% 8 "
                 "== 0 (got C/groups=%d, C/deformable_group=%d)", pl->g.Cg, pl->g.cpdg);
+  if (!pl->tc) {
+    const Geom &g = pl->g;
+    const long long plane = (long long)g.Ho * g.Wo;
+    if (g.mask_act != DCN_ACT_NONE || g.off_ps != 1 || g.msk_ps != 1 || g.off_cs != plane ||
+        g.msk_cs != plane)
+      return fail(DCN_ERR_UNSUPPORTED, "strided offsets/masks and mask logits are taken by the "
+                  "tensor-core kernel only; this problem runs on another kernel");
+  }
   // 3xTF32 on a shape the tensor-core kernel does not take runs on the FFMA kernel: both
   // meet the fp32 tolerance, so the request degrades instead of failing.
   layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);

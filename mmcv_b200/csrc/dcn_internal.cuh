@@ -20,6 +20,8 @@ struct Geom {
   long long P;        // N*Ho*Wo output pixels
   long long in_sn, in_sc, in_sh, in_sw;  // input element strides
   long long off_sn, msk_sn, out_sn;      // per-sample strides of offset/mask/output
+  long long off_cs, off_ps, msk_cs, msk_ps;  // channel and pixel strides inside a sample
+  int mask_act;                          // DCN_ACT_SIGMOID: the mask holds logits
   int act, act_lo, act_hi;
 };
 

@@ -299,6 +299,11 @@ __device__ __forceinline__ uint4 table_weights(const uint2 &w) {
 template <int MODE>
 __device__ __forceinline__ uint4 table_weights(const uint4 &w) { return w; }
 
+// The modulation value of a tap: the mask element, or its sigmoid when the tensor holds logits.
+__device__ __forceinline__ float mask_value(const Geom &g, float m) {
+  return g.mask_act == DCN_ACT_SIGMOID ? 1.f / (1.f + __expf(-m)) : m;
+}
+
 // Bilinear blend of four 8-channel bf16 corner vectors on packed bf16 FMAs: one multiply
 // and three fused multiply-adds per channel pair, each rounding to bf16.  `w` holds each
 // corner weight twice (a bf16 pair).
@@ -719,8 +724,9 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       }
       // Ask L2 for the offsets and masks of the tile after this one (of this one too, the
       // first time): the tap tables are built from them and would otherwise wait on DRAM.
+      const bool dense_planes = g.off_ps == 1 && g.msk_ps == 1 && g.off_cs == plane && g.msk_cs == plane;
       for (long long nitem = (item == (long long)blockIdx.x ? item : item + gridDim.x);
-           nitem <= item + gridDim.x && nitem < items; nitem += gridDim.x) {
+           dense_planes && nitem <= item + gridDim.x && nitem < items; nitem += gridDim.x) {
         const TileId nt_ = decode_item(nitem, g, tp);
         // 128-byte lines per tile row, rows per tile: both powers of two, so the index of a
         // line splits into (plane, row, line) with shifts
@@ -778,8 +784,8 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
               hb = L.row_h[trow]; wb = L.row_w[trow]; pix = L.row_pix[trow];
               rvalid = hb != kRowInvalid;
             }
-            const TIO *offp = off ? off + (long long)t.n * g.off_sn + pix : nullptr;
-            const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + pix : nullptr;
+            const TIO *offp = off ? off + (long long)t.n * g.off_sn + (long long)pix * g.off_ps : nullptr;
+            const TIO *mskp = msk ? msk + (long long)t.n * g.msk_sn + (long long)pix * g.msk_ps : nullptr;
             constexpr int kTapStep = kOwn ? kGroups : 1;  // taps of consecutive table blocks
             const int n_taps = kOwn ? (own_t0 < g.T ? (g.T - own_t0 + kGroups - 1) / kGroups : 0) : g.T;
             const int total = n_taps * nd;
@@ -809,12 +815,12 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   const int tap_k = tap;
                   if (rvalid) {
                     if (offp) {
-                      const long long ch = ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap_k) * plane;
+                      const long long ch = ((long long)(dg_lo + dgl) * 2 * g.T + 2 * tap_k) * g.off_cs;
                       oh[k] = ldg_raw_ordered(offp + ch);
-                      ow[k] = ldg_raw_ordered(offp + ch + plane);
+                      ow[k] = ldg_raw_ordered(offp + ch + g.off_cs);
                     }
                     if (mskp)
-                      mm[k] = ldg_raw_ordered(mskp + ((long long)(dg_lo + dgl) * g.T + tap_k) * plane);
+                      mm[k] = ldg_raw_ordered(mskp + ((long long)(dg_lo + dgl) * g.T + tap_k) * g.msk_cs);
                   }
                   dgl += tparts;
                   normalise();
@@ -831,7 +837,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                 int h_low = 0, w_low = 0;
                 if (rvalid)
                   tap_weights(RawOf<TIO>::to_float(oh[k]), RawOf<TIO>::to_float(ow[k]),
-                              mskp ? RawOf<TIO>::to_float(mm[k]) : 1.f, hb + ei * g.dil_h,
+                              mskp ? mask_value(g, RawOf<TIO>::to_float(mm[k])) : 1.f, hb + ei * g.dil_h,
                               wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
                 // a weight that is (or rounds to) zero is stored as the integer 0: such a
                 // corner is not read

@@ -169,7 +169,14 @@ class DeformConv2dPack(DeformConv2d):
                     ext_module.cast_weight(self.conv_offset.bias, dtype),
                     _pair(self.stride), _pair(self.padding), _pair(self.dilation))
             else:
-                offset, _ = mdc.library_offset_branch(x, self.conv_offset, dtype)
+                offset = mdc.branch_conv(x, self.conv_offset, dtype)
+                if x.size(0) % min(self.im2col_step, x.size(0)) == 0:
+                    y = mdc.deform_from_branch(x, offset, offset.size(1), self.weight, None,
+                                               self.stride, self.padding, self.dilation,
+                                               self.groups, self.deform_groups)
+                    if y is not None:
+                        return y
+                offset = offset.contiguous()
         else:
             offset = self.conv_offset(x)
         return deform_conv2d(x, offset, self.weight, self.stride, self.padding, self.dilation,

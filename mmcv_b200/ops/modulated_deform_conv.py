@@ -99,13 +99,17 @@ modulated_deform_conv2d = ModulatedDeformConv2dFunction.apply
 OFFSET_BRANCH = os.environ.get('DCN_B200_OFFSET_BRANCH', 'library')
 
 
-def library_offset_branch(x, conv, dtype, sigmoid_from=None):
-    """conv(x) for an inference-time offset branch: x is already in the layout shared with
-    the deformable kernel.  Returns NCHW-contiguous (offset, mask) tensors; mask is None when
+def branch_conv(x, conv, dtype):
+    """conv(x) for an inference-time offset branch (library convolution, no autograd graph);
+    x is already in the layout shared with the deformable kernel."""
+    return F.conv2d(x, ext_module.cast_weight(conv.weight, dtype),
+                    ext_module.cast_weight(conv.bias, dtype), conv.stride, conv.padding,
+                    conv.dilation, conv.groups)
+
+
+def split_branch(out, sigmoid_from=None):
+    """NCHW-contiguous (offset, mask) tensors from a branch output; mask is None when
     sigmoid_from is None (the v1 layer)."""
-    out = F.conv2d(x, ext_module.cast_weight(conv.weight, dtype),
-                   ext_module.cast_weight(conv.bias, dtype), conv.stride, conv.padding,
-                   conv.dilation, conv.groups)
     if sigmoid_from is None:
         return out.contiguous(), None
     offset = out[:, :sigmoid_from].contiguous()
@@ -113,6 +117,24 @@ def library_offset_branch(x, conv, dtype, sigmoid_from=None):
                        dtype=out.dtype, device=out.device)
     torch.sigmoid(out[:, sigmoid_from:], out=mask)
     return offset, mask
+
+
+def library_offset_branch(x, conv, dtype, sigmoid_from=None):
+    """branch_conv + split_branch."""
+    return split_branch(branch_conv(x, conv, dtype), sigmoid_from)
+
+
+def deform_from_branch(x, out, n_offset, weight, bias, stride, padding, dilation, groups,
+                       deform_groups):
+    """The deformable convolution fed by the raw branch output `out` (offsets, then mask
+    logits), which the tensor-core kernel reads where it lies, sigmoid included: no split,
+    copy or sigmoid pass.  Returns None when the problem runs on another kernel."""
+    weight = ext_module.cast_weight(weight, x.dtype)
+    bias = ext_module.cast_weight(bias, x.dtype)
+    y = x.new_empty(conv_output_size(x, weight, _pair(stride), _pair(padding), _pair(dilation)))
+    done = ext_module.forward_from_branch(x, out, n_offset, weight, bias, y, _pair(stride),
+                                          _pair(padding), _pair(dilation), groups, deform_groups)
+    return y if done else None
 
 
 def fused_branch_applies(x, conv):
@@ -241,7 +263,13 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
                     self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
                 offset, mask = out[:, :two_thirds], out[:, two_thirds:]
             else:
-                offset, mask = library_offset_branch(x, self.conv_offset, dtype, two_thirds)
+                out = branch_conv(x, self.conv_offset, dtype)
+                y = deform_from_branch(x, out, two_thirds, self.weight, self.bias, self.stride,
+                                       self.padding, self.dilation, self.groups,
+                                       self.deform_groups)
+                if y is not None:
+                    return y
+                offset, mask = split_branch(out, two_thirds)
         else:
             out = self.conv_offset(x)
             offset = out[:, :two_thirds].contiguous()

@@ -291,3 +291,46 @@ def test_channels_last_copy_is_exact(dtype, shape):
     view = wide[:, 8:]
     assert torch.equal(_ext.to_channels_last(view), view)
     assert _ext.to_channels_last(got) is got
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize('channels_last', [True, False])
+def test_offsets_and_mask_logits_read_from_the_branch_output(dtype, channels_last):
+    # the kernel reads offsets and mask logits where the branch convolution left them
+    # (channels-last or NCHW, one tensor) and applies the sigmoid itself; compared with the
+    # ordinary route fed the split, sigmoided copies
+    from mmcv_b200 import _ext
+    from mmcv_b200.ops import modulated_deform_conv2d, deform_conv2d
+    torch.manual_seed(9)
+    N, C, H, W, Co, dg = 2, 64, 18, 14, 72, 2
+    x = torch.randn(N, C, H, W, device='cuda').to(dtype)
+    w = (torch.randn(Co, C, 3, 3, device='cuda') * 0.05).to(dtype)
+    b = torch.randn(Co, device='cuda').to(dtype)
+    branch = (torch.randn(N, dg * 27, H, W, device='cuda') * 1.5).to(dtype)
+    if channels_last:
+        branch = branch.contiguous(memory_format=torch.channels_last)
+    k = dg * 18
+    want = modulated_deform_conv2d(x, branch[:, :k].contiguous(),
+                                   torch.sigmoid(branch[:, k:].float()).to(dtype).contiguous(),
+                                   w, b, 1, 1, 1, 1, dg)
+    got = torch.empty_like(want)
+    assert _ext.forward_from_branch(x, branch, k, w, b, got, (1, 1), (1, 1), (1, 1), 1, dg)
+    if dtype == torch.float32:
+        ok, frac = fp32_close(got, want.cpu())
+        assert ok, frac
+    else:
+        assert rel_l2(got.float().cpu(), want.float().cpu()) <= 5e-3   # mask not rounded to bf16
+    # v1: the whole tensor is offsets
+    off = branch[:, :k]
+    off = off.contiguous(memory_format=torch.channels_last) if channels_last else off.contiguous()
+    want1 = deform_conv2d(x, off.contiguous(), w, 1, 1, 1, 1, dg)
+    got1 = torch.empty_like(want1)
+    assert _ext.forward_from_branch(x, off, k, w, None, got1, (1, 1), (1, 1), (1, 1), 1, dg)
+    assert torch.equal(got1, want1)
+    # a problem that runs on the SIMT kernels is declined, nothing is written
+    x3 = torch.randn(1, 3, 8, 8, device='cuda').to(dtype)
+    w3 = torch.randn(4, 3, 3, 3, device='cuda').to(dtype)
+    br3 = torch.randn(1, 27, 8, 8, device='cuda').to(dtype)
+    assert not _ext.forward_from_branch(x3, br3, 18, w3, None, torch.empty(1, 4, 8, 8, device='cuda',
+                                                                       dtype=dtype),
+                                        (1, 1), (1, 1), (1, 1), 1, 1)
