@@ -299,6 +299,23 @@ __device__ __forceinline__ uint4 table_weights(const uint2 &w) {
 template <int MODE>
 __device__ __forceinline__ uint4 table_weights(const uint4 &w) { return w; }
 
+// Four consecutive elements (8- or 16-byte aligned) as floats, with one load.
+__device__ __forceinline__ void load4_as_float(const float *p, float (&o)[4]) {
+  const float4 v = *reinterpret_cast<const float4 *>(p);
+  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+}
+__device__ __forceinline__ void load4_as_float(const __nv_bfloat16 *p, float (&o)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2 *>(p);
+  o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+  o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+__device__ __forceinline__ void load4_as_float(const __half *p, float (&o)[4]) {
+  const uint2 v = *reinterpret_cast<const uint2 *>(p);
+  const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
+  const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
+  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
+}
+
 // The modulation value of a tap: the mask element, or its sigmoid when the tensor holds logits.
 __device__ __forceinline__ float mask_value(const Geom &g, float m) {
   return g.mask_act == DCN_ACT_SIGMOID ? 1.f / (1.f + __expf(-m)) : m;
@@ -564,14 +581,16 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         TIO *oc = orow + (long long)c0 * plane;
 #pragma unroll
         for (int j4 = 0; j4 < 8; ++j4) {
-          float v[4] = {__uint_as_float(r[4 * j4]) + ld_as_float(bs, 4 * j4),
-                        __uint_as_float(r[4 * j4 + 1]) + ld_as_float(bs, 4 * j4 + 1),
-                        __uint_as_float(r[4 * j4 + 2]) + ld_as_float(bs, 4 * j4 + 2),
-                        __uint_as_float(r[4 * j4 + 3]) + ld_as_float(bs, 4 * j4 + 3)};
+          float b4[4];
+          load4_as_float(bs + 4 * j4, b4);
+          float v[4] = {__uint_as_float(r[4 * j4]) + b4[0], __uint_as_float(r[4 * j4 + 1]) + b4[1],
+                        __uint_as_float(r[4 * j4 + 2]) + b4[2], __uint_as_float(r[4 * j4 + 3]) + b4[3]};
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (act_tile) v[k] = apply_act(g, co0 + c0 + 4 * j4 + k, v[k]);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             const int j = 4 * j4 + k;
-            if (act_tile) v[k] = apply_act(g, co0 + c0 + j, v[k]);
             if (valid && c0 + j < ncols) st_from_float(oc, (long long)j * plane, v[k]);
           }
         }
