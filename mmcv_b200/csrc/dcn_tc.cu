@@ -555,10 +555,16 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       const int ncols = min(tp.BN, g.Cog - t.nt * tp.BN);
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
       TIO *orow = out + (long long)t.n * g.out_sn + (long long)co0 * plane + (long long)ho * g.Wo + wo;
+      const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
+      pt.lap(13);
+      if (!mbar_wait<true>(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
+      pt.lap(12);
+      tc_fence_after();
       // Bias copy of this accumulator buffer.  When its channels change, every epilogue warp
-      // writes the whole copy (the same values: no rendezvous between the warps is needed);
-      // a warp cannot be two tiles ahead of another, because the buffer it would then stage
-      // for is only handed over once all four warps have released it.
+      // writes the whole copy (the same values: no rendezvous between the warps is needed).
+      // This comes after the wait above on purpose: the accumulator buffer is only filled
+      // again once all four warps have released it, so no warp still reads the copy's
+      // previous contents.
       TIO *bias_w = reinterpret_cast<TIO *>(L.bias_s) + buf * tp.BN;
       if (co0 != staged_co0[buf]) {
         __syncwarp();
@@ -567,11 +573,6 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         __syncwarp();
         staged_co0[buf] = co0;
       }
-      const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
-      pt.lap(13);
-      if (!mbar_wait<true>(tmem_full + 8 * buf, par, abort_s, a.status, 3)) break;
-      pt.lap(12);
-      tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t)(buf * tp.BN) + ((uint32_t)(warp * 32) << 16);
       for (int c0 = 0; c0 < ncols; c0 += 32) {
         uint32_t r[32];
