@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DCN_ABI_VERSION 3
+#define DCN_ABI_VERSION 4
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
@@ -108,8 +108,15 @@ typedef struct DcnPlanInfo {
   int64_t Ho, Wo;
   size_t workspace_bytes;
   int32_t operand_stages, weight_stages; /* depth of the two shared-memory rings (tcgen05 path) */
-  int32_t producer_layout; /* tcgen05 path: groups*100 + warps per group*10 + rows in flight,
-                            * +1000 rows software-pipelined, +2000 per-group tap tables */
+  int32_t producer_layout; /* tcgen05 path, first-generation kernel: groups*100 + warps per
+                            * group*10 + rows in flight, +1000 rows software-pipelined, +2000
+                            * per-group tap tables; second generation: 2016 (2 table-builder
+                            * warps, 16 gather warps) */
+  int32_t kernel_version;  /* tcgen05 path: 1 = first-generation kernel (3xTF32), 2 = second generation, 16-bit operands */
+  int32_t window_h, window_w; /* input window kept in shared memory, pixels (0: none) */
+  int32_t table_span;      /* channel chunks served by one tap-table segment (0: one k-stage) */
+  int32_t table_slots;     /* ring depth of the tap table */
+  int32_t epilogue_tensor_stores; /* 1: output written by cp.async.bulk.tensor stores */
 } DcnPlanInfo;
 
 int dcn_abi_version(void);
@@ -199,6 +206,13 @@ int dcn_bwd_input(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *gr
                   float *grad_input, void *stream);
 int dcn_bwd_coord(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *grad_columns,
                   float *grad_offset, float *grad_mask, void *stream);
+
+/* Test aid for the bounded device-side waits.  Every wait of the tensor-core kernel gives up
+ * after a time limit, sets the status word and lets the kernel return.  wait_limit_ns
+ * shortens that limit for later calls in this process (0 = the default of two seconds);
+ * flags bit 0 makes the weight loader of the 16-bit kernel withhold its very last copy, so
+ * that the wait for it runs out.  Not for production use. */
+int dcn_debug_configure(uint64_t wait_limit_ns, int32_t flags);
 
 /* Tracing aid.  When the environment variable DCN_B200_COUNTERS=1 is set, the first
  * block of the tensor-core kernel accumulates the clock cycles its roles spend in each

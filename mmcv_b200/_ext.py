@@ -181,6 +181,35 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     return ws
 
 
+def _out_hw(input, weight, stride, padding, dilation):
+    """Output height and width, as the reference computes them
+    (mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:87-90)."""
+    kh, kw = weight.shape[2], weight.shape[3]
+    ho = (input.size(2) + 2 * padding[0] - (dilation[0] * (kh - 1) + 1)) // stride[0] + 1
+    wo = (input.size(3) + 2 * padding[1] - (dilation[1] * (kw - 1) + 1)) // stride[1] + 1
+    return ho, wo
+
+
+def _check_shapes(input, weight, offset, mask, output, stride, padding, dilation, deform_groups):
+    """The kernels index offset, mask and output from the problem geometry alone, so a tensor
+    of another shape (an offset made for another stride, a smaller batch, the wrong number of
+    deform groups) would be read or written out of bounds: reject it here."""
+    if min(stride) <= 0 or min(dilation) <= 0:
+        return   # the library reports these with the reference's messages
+    N = input.size(0)
+    T = weight.size(2) * weight.size(3)
+    ho, wo = _out_hw(input, weight, stride, padding, dilation)
+    if ho < 1 or wo < 1:
+        return   # "output size is too small": reported by the library
+    want = {'offset': (N, deform_groups * 2 * T, ho, wo), 'mask': (N, deform_groups * T, ho, wo),
+            'output': (N, weight.size(0), ho, wo)}
+    for name, t in (('offset', offset), ('mask', mask), ('output', output)):
+        if t is not None and tuple(t.shape) != want[name]:
+            raise RuntimeError(f'dcn_b200: {name} has shape {tuple(t.shape)}, expected '
+                               f'{want[name]} for this input, kernel, stride, padding, dilation '
+                               'and deformable_group')
+
+
 def forward_from_branch(input, branch, n_offset, weight, bias, output, stride, padding, dilation,
                         groups, deform_groups):
     """Deformable convolution whose offsets are the first n_offset channels of `branch` (the
@@ -191,6 +220,16 @@ def forward_from_branch(input, branch, n_offset, weight, bias, output, stride, p
     if branch.dim() != 4 or branch.dtype != input.dtype:
         return False
     N, Ct, Ho, Wo = branch.shape
+    T = weight.size(2) * weight.size(3)
+    if n_offset != deform_groups * 2 * T or Ct not in (n_offset, n_offset + deform_groups * T):
+        raise RuntimeError(f'dcn_b200: the branch has {Ct} channels with {n_offset} offset '
+                           f'channels; expected {deform_groups * 2 * T} offset channels and none '
+                           f'or {deform_groups * T} mask channels')
+    if (N, Ho, Wo) != (input.size(0),) + _out_hw(input, weight, stride, padding, dilation):
+        raise RuntimeError(f'dcn_b200: the branch is {N} x {Ho} x {Wo} (batch, height, width), '
+                           'which is not the output size of this problem')
+    _check_shapes(input, weight, None, None, output, stride, padding, dilation, deform_groups)
+    input = _input_layout(input)
     if N == 0 or (N > 1 and branch.stride(0) != Ct * Ho * Wo):
         return False   # (an empty batch takes the ordinary route)
     if branch.is_contiguous():
@@ -268,6 +307,8 @@ def modulated_deform_conv_forward(input, weight, bias, ones, offset, mask, outpu
     b = bias.contiguous() if (with_bias and bias is not None and bias.numel() > 0) else None
     if with_bias and b is None:
         raise RuntimeError('dcn_b200: with_bias is set but bias is empty')
+    _check_shapes(input, weight, offset, mask, output, (stride_h, stride_w), (pad_h, pad_w),
+                  (dilation_h, dilation_w), deformable_group)
     offset, off_bs = _per_sample(offset)
     mask, msk_bs = _per_sample(mask)
     forward(_input_layout(input), offset, mask, weight.contiguous(), b, output,
@@ -315,6 +356,8 @@ def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW
         raise RuntimeError('invalid batch size of offset')
     if im2col_step <= 0 or input.size(0) % im2col_step != 0:
         raise RuntimeError('batch size must be divisible by im2col_step')
+    _check_shapes(input, weight, offset, None, output, (dH, dW), (padH, padW),
+                  (dilationH, dilationW), deformable_group)
     forward(input, offset, None, weight, None, output, (dH, dW), (padH, padW),
             (dilationH, dilationW), group, deformable_group)
 
@@ -463,12 +506,9 @@ def deform_conv_backward_parameters(input, offset, gradOutput, gradWeight, colum
             raise RuntimeError(f'{name} must be contiguous')
     if im2col_step <= 0 or input.size(0) % im2col_step != 0:
         raise RuntimeError('batch size must be divisible by im2col_step')
-    _, _, _, gw = _backward(input, offset, None, weight_like(gradWeight), gradOutput, (dH, dW),
+    # (this entry receives no weight tensor; only its shape is needed, and gradWeight has it)
+    _, _, _, gw = _backward(input, offset, None, gradWeight, gradOutput, (dH, dW),
                             (padH, padW), (dilationH, dilationW), group, deformable_group,
                             want_input=False)
     gradWeight.add_((gw * scale).to(gradWeight.dtype))
 
-
-def weight_like(grad_weight):
-    """The parameter-gradient entry receives no weight tensor; its shape is gradWeight's."""
-    return grad_weight

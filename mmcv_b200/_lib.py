@@ -14,12 +14,12 @@ MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 3   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
+ABI_VERSION = 4   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_fwd_workspace_bytes', 'dcn_weight_image_bytes', 'dcn_prepare_weights', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
-           'dcn_read_counters', 'dcn_read_status', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
+           'dcn_read_counters', 'dcn_read_status', 'dcn_debug_configure', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
            'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
@@ -60,7 +60,10 @@ class DcnPlanInfo(ctypes.Structure):
         ('smem_bytes', ctypes.c_int64), ('Ho', ctypes.c_int64),
         ('Wo', ctypes.c_int64), ('workspace_bytes', ctypes.c_size_t),
         ('operand_stages', ctypes.c_int32), ('weight_stages', ctypes.c_int32),
-        ('producer_layout', ctypes.c_int32),
+        ('producer_layout', ctypes.c_int32), ('kernel_version', ctypes.c_int32),
+        ('window_h', ctypes.c_int32), ('window_w', ctypes.c_int32),
+        ('table_span', ctypes.c_int32), ('table_slots', ctypes.c_int32),
+        ('epilogue_tensor_stores', ctypes.c_int32),
     ]
 
 
@@ -96,6 +99,7 @@ def load():
     lib.dcn_bwd_coord.argtypes = [P(DcnFwdParams), i64, i64, vp, vp, vp, vp]
     lib.dcn_read_counters.argtypes = [vp, vp, P(ctypes.c_uint64)]
     lib.dcn_read_status.argtypes = [vp, vp, P(i32)]
+    lib.dcn_debug_configure.argtypes = [ctypes.c_uint64, i32]
     lib.dcn_modulated_deform_conv_forward.argtypes = (
         [vp] * 6 + [i32] + [i64] * 5 + [i32] * 12 + [vp, sz, vp])
     lib.dcn_deform_conv_forward.argtypes = (

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, 'csrc')
 LIB_DIR = os.path.join(PKG, 'lib')
 LIB = os.path.join(LIB_DIR, 'libdcn_b200.so')
-SOURCES = ['dcn_api.cu', 'dcn_simt.cu', 'dcn_tc.cu', 'dcn_static.cu', 'dcn_bwd.cu']
+SOURCES = ['dcn_api.cu', 'dcn_simt.cu', 'dcn_tc.cu', 'dcn_tc2.cu', 'dcn_static.cu', 'dcn_bwd.cu']
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 
 
@@ -32,21 +32,46 @@ def up_to_date():
     return all(os.path.getmtime(d) <= t for d in _deps())
 
 
+def _compile(src, obj, verbose):
+    """One translation unit -> object file (skipped when the object is newer than every
+    source and header)."""
+    if os.path.exists(obj) and all(os.path.getmtime(d) <= os.path.getmtime(obj) for d in _deps()):
+        return ''
+    cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3',
+           '-std=c++17', '-Xcompiler', '-fPIC', '-I', os.path.join(ROOT, 'include'), '-I', CSRC]
+    if verbose:
+        cmd += ['-Xptxas', '-v']
+    cmd += ['-c', src, '-o', obj]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f'nvcc failed on {src}:\n{r.stdout}{r.stderr}')
+    return r.stdout + r.stderr
+
+
 def build(force=False, verbose=False):
     if not force and up_to_date():
         return LIB
+    from concurrent.futures import ThreadPoolExecutor
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3',
-           '-std=c++17', '-shared', '-Xcompiler', '-fPIC', '-cudart', 'static',
-           '-I', os.path.join(ROOT, 'include'), '-I', CSRC]
+    obj_dir = os.path.join(LIB_DIR, 'obj')
+    os.makedirs(obj_dir, exist_ok=True)
+    objs = [os.path.join(obj_dir, s[:-3] + '.o') for s in SOURCES]
+    if force:
+        for o in objs:
+            if os.path.exists(o):
+                os.remove(o)
+    # the translation units are independent: compile them side by side, then link
+    with ThreadPoolExecutor(max_workers=len(SOURCES)) as pool:
+        logs = list(pool.map(lambda so: _compile(os.path.join(CSRC, so[0]), so[1], verbose),
+                             zip(SOURCES, objs)))
     if verbose:
-        cmd += ['-Xptxas', '-v']
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ['-o', LIB]
+        sys.stderr.write(''.join(logs))
+    cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-shared', '-Xcompiler', '-fPIC',
+           '-cudart', 'static'] + objs + ['-o', LIB]
     r = subprocess.run(cmd, capture_output=True, text=True)
-    if verbose or r.returncode != 0:
-        sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
-        raise RuntimeError('nvcc failed building libdcn_b200.so')
+        sys.stderr.write(r.stdout + r.stderr)
+        raise RuntimeError('nvcc failed linking libdcn_b200.so')
     return LIB
 
 

@@ -9,12 +9,17 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 #include "dcn_internal.cuh"
 
 namespace dcn {
 size_t tc_smem_bytes(const TcPlan &tp, int T);
+
+// Test-only knobs of the bounded waits (dcn_debug_configure).
+std::atomic<unsigned long long> g_wait_limit_ns{0};
+std::atomic<int> g_debug_flags{0};
 
 namespace {
 
@@ -50,6 +55,52 @@ int env_int(const char *name, int dflt, int lo, int hi) {
   const int x = atoi(v);
   return x < lo ? lo : (x > hi ? hi : x);
 }
+// All of them, read once per process (the first call that plans a problem).
+struct Knobs {
+  int a_stages, b_stages, producers, tile_w, simt_tiled, counters;
+  int kernel;      // 1: first-generation tensor-core kernel for every mode, 2: default routing
+  int window;      // -1: planner's choice, 0: no shared-memory input window, n: margin n
+  int epi_tma;     // -1: planner's choice, 0/1
+  int tab_slots;   // 0: planner's choice
+  int small_l1;    // 1: give the kernel the largest shared-memory configuration
+};
+const Knobs &knobs() {
+  static Knobs k;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    k.a_stages = env_int("DCN_B200_A_STAGES", 0, 0, 8);
+    k.b_stages = env_int("DCN_B200_B_STAGES", 0, 0, 8);
+    k.producers = env_int("DCN_B200_PRODUCERS", 0, 0, 9999);
+    k.tile_w = env_int("DCN_B200_TILE_W", 0, 0, 128);
+    k.simt_tiled = env_int("DCN_B200_SIMT_TILED", 1, 0, 1);
+    k.counters = env_int("DCN_B200_COUNTERS", 0, 0, 1);
+    k.kernel = env_int("DCN_B200_KERNEL", 2, 1, 2);
+    k.window = env_int("DCN_B200_WINDOW", -1, -1, 16);
+    k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
+    k.tab_slots = env_int("DCN_B200_TAB_SLOTS", 0, 0, 16);
+    k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
+  });
+  return k;
+}
+
+// Makes `device` current for the lifetime of the object and restores the caller's device
+// afterwards (the reference scopes its device switch the same way,
+// mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:68).
+struct DeviceScope {
+  int prev = -1;
+  bool switched = false;
+  cudaError_t err = cudaSuccess;
+  explicit DeviceScope(int device) {
+    err = cudaGetDevice(&prev);
+    if (err == cudaSuccess && prev != device) {
+      err = cudaSetDevice(device);
+      switched = err == cudaSuccess;
+    }
+  }
+  ~DeviceScope() {
+    if (switched) cudaSetDevice(prev);
+  }
+};
 
 int build_geom(const DcnFwdParams *p, Geom *g) {
   if (!p) return fail(DCN_ERR_ARG, "params is NULL");
@@ -138,6 +189,82 @@ int resolved_math(const DcnFwdParams *p) {
              : p->math_mode;
 }
 
+
+// Second-generation 16-bit kernel: table segments, ring depths, input window, epilogue stores.
+// Leaves the plan on the first-generation kernel when the problem does not fit.
+void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
+  const Knobs &kn = knobs();
+  // offsets into the padded copy are 31-bit byte offsets within a sample
+  if ((long long)(g.H + 3) * (g.W + 2) * g.C * 2 >= 2147483647LL) return;
+  TcPlan t = *tp;
+  t.version = 2;
+  t.producer_cfg = 2016;  // 2 table-builder warps, 16 gather warps
+  // Table segments.  Chunks whose deform groups are the same share their table entries: when
+  // every tile splits into runs of L >= 2 such chunks, one segment (all taps) serves a run and
+  // the ring holds two of them; otherwise a segment serves one k-stage.
+  int run = -1;
+  bool uniform = true;
+  for (int grp = 0; grp < g.groups && uniform; ++grp) {
+    int prev_lo = -1, prev_nd = 0, len = 0;
+    for (int cc = 0; cc <= t.KC; ++cc) {
+      int lo = -2, nd = 0;
+      if (cc < t.KC) {
+        const int c0 = grp * g.Cg + cc * 64;
+        const int c1 = c0 + 64 < (grp + 1) * g.Cg ? c0 + 64 : (grp + 1) * g.Cg;
+        lo = c0 / g.cpdg;
+        nd = (c1 - 1) / g.cpdg - lo + 1;
+      }
+      if (lo == prev_lo && nd == prev_nd) { ++len; continue; }
+      if (len > 0) {
+        if (run < 0) run = len;
+        else if (run != len) uniform = false;
+      }
+      prev_lo = lo; prev_nd = nd; len = 1;
+    }
+  }
+  const size_t entry = 12;  // bytes of a table entry
+  t.tab_span = (uniform && run >= 2 && (size_t)2 * g.T * t.ndgc * (kBM + 4) * entry <= 60 * 1024) ? run : 0;
+  t.tab_slot_blocks = t.tab_span ? g.T * t.ndgc : t.ndgc;
+  t.tab_slots = t.tab_span ? 2 : (kn.tab_slots ? kn.tab_slots : 6);
+  if ((size_t)t.tab_slots * t.tab_slot_blocks * (kBM + 4) * entry > 64 * 1024) return;
+  // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles
+  // whose 32-channel slabs never reach into another tile's channels.
+  {
+    const long long es = t.io_bytes;
+    const bool aligned = (g.Wo * es) % 16 == 0 && ((long long)g.Ho * g.Wo * es) % 16 == 0 &&
+                         (g.out_sn * es) % 16 == 0 && ((uintptr_t)p->output & 15) == 0;
+    const bool slabs_ok = g.Cog % t.BN == 0 || g.groups * t.NT == 1;
+    const int want = kn.epi_tma < 0 ? 0 : kn.epi_tma;
+    t.epi_tma = (want && aligned && slabs_ok && g.N > 0) ? 1 : 0;
+  }
+  // Input window in shared memory: the tile's undeformed footprint plus a margin of m pixels
+  // on every side, 64 channels, two buffers.  Largest margin (up to 4) that fits wins.
+  const int th = kBM >> t.tw_log2, tw = 1 << t.tw_log2;
+  const int fh = (th - 1) * g.stride_h + (g.kh - 1) * g.dil_h + 1;
+  const int fw = (tw - 1) * g.stride_w + (g.kw - 1) * g.dil_w + 1;
+  const int m_max = kn.window < 0 ? 0 : kn.window;
+  bool found = false;
+  for (int m = m_max; m >= 0 && !found; --m) {
+    t.win_h = m ? fh + 2 * m : 0;
+    t.win_w = m ? fw + 2 * m : 0;
+    t.win_my = t.win_mx = m;
+    if (m && (t.win_h > 256 || t.win_w > 256)) continue;
+    // without a window the gather lives on L1: stay inside the 164 KB shared-memory
+    // configuration if possible
+    const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
+    for (int bi = (m || kn.small_l1) ? 1 : 0; bi < 2 && !found; ++bi)
+      for (int as = 4; as >= 2 && !found; --as) {
+        if (kn.a_stages && as != kn.a_stages) continue;
+        t.a_stages = as;
+        t.b_stages = kn.b_stages ? kn.b_stages : 2;
+        t.smem = tc2_smem_bytes(t);
+        found = t.smem <= budgets[bi];
+      }
+  }
+  if (!found) return;
+  *tp = t;
+}
+
 // Decide whether the tensor-core kernel can take the problem and with what tiling.
 bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   const int math = resolved_math(p);
@@ -148,8 +275,8 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   if ((long long)g.N * g.H * g.W >= 2147483647LL) return false;
   if ((long long)g.H * g.W * g.C * (tf32 ? 4 : 2) >= 4294967295LL) return false;
   if (g.kh > 255 || g.kw > 255 || g.T > 4095) return false;
-  const int a_forced = env_int("DCN_B200_A_STAGES", 0, 0, 8);
-  const int b_forced = env_int("DCN_B200_B_STAGES", 0, 0, 8);
+  const Knobs &kn = knobs();
+  const int a_forced = kn.a_stages, b_forced = kn.b_stages;
   // Output channels per tile: as many as fit (fewest passes over the gather); TF32x3 needs
   // twice the operand memory per stage and may have to halve it.
   bool found = false;
@@ -190,7 +317,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
     // When chunks share deform groups the table is shared and lives as long as they do (1282).
     // The batched layouts (282: same warps, 342: three groups of four) stay selectable.
     const int cfg_default = chunks_share_groups ? 1282 : 3282;
-    switch (env_int("DCN_B200_PRODUCERS", cfg_default, 0, 9999)) {
+    switch (kn.producers ? kn.producers : cfg_default) {
       case 342: tp->producer_cfg = 342; break;
       case 1282: tp->producer_cfg = 1282; break;
       case 3282: tp->producer_cfg = 3282; break;
@@ -220,7 +347,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   // shapes within 3 % of the fewest, the one closest to square (smallest sampled footprint).
   int best = -1;
   {
-    const int forced = env_int("DCN_B200_TILE_W", 0, 0, 128);
+    const int forced = kn.tile_w;
     long long tiles[8] = {0}, fewest = -1;
     for (int lg = 3; lg <= 7; ++lg) {
       const int tw = 1 << lg, th = kBM >> lg;
@@ -240,6 +367,8 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   const long long mtiles = (long long)g.N * tp->tiles_x * tp->tiles_y;
   tp->items = mtiles * g.groups * tp->NT;
   tp->grid = (int)(tp->items < sms ? tp->items : sms);
+  tp->version = 1;
+  if (!tf32 && kn.kernel == 2) plan_tc2(p, g, tp);
   return true;
 }
 
@@ -251,7 +380,12 @@ void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPla
     ws->wtile_off = off;
     ws->wtile_bytes = (size_t)g.groups * tp.NT * tp.S * tp.BN * 128 * tp.tiles_per_stage;
     off = align_up(off + ws->wtile_bytes, 256);
-    if (!input_is_ready(p, g, tp.op_format)) {
+    if (tp.version == 2) {
+      // channels-last copy with a one-pixel zero border per sample and one more zero row
+      ws->xcl_off = off;
+      ws->xcl_bytes = ((size_t)g.N * (g.H + 2) + 1) * (g.W + 2) * g.C * 2;
+      off = align_up(off + ws->xcl_bytes, 256);
+    } else if (!input_is_ready(p, g, tp.op_format)) {
       ws->xcl_off = off;
       ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * (tp.tiles_per_stage == 2 ? 4 : 2);
       off = align_up(off + ws->xcl_bytes, 256);
@@ -350,6 +484,12 @@ int dcn_fwd_plan(const DcnFwdParams *p, DcnPlanInfo *info) {
   info->tile_k = pl.tc ? pl.tp.ch_per_stage : 1;
   info->grid = pl.tc ? pl.tp.grid : 0;
   info->block = pl.tc ? tc_threads(pl.tp) : 256;
+  info->kernel_version = pl.tc ? pl.tp.version : 0;
+  info->window_h = pl.tc ? pl.tp.win_h : 0;
+  info->window_w = pl.tc ? pl.tp.win_w : 0;
+  info->table_span = pl.tc ? pl.tp.tab_span : 0;
+  info->table_slots = pl.tc ? pl.tp.tab_slots : 0;
+  info->epilogue_tensor_stores = pl.tc ? pl.tp.epi_tma : 0;
   info->smem_bytes = pl.tc ? (int64_t)pl.tp.smem : 0;
   info->Ho = pl.g.Ho;
   info->Wo = pl.g.Wo;
@@ -385,7 +525,8 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
                 workspace ? workspace_bytes : (size_t)0);
   if (((uintptr_t)workspace & 255) != 0)
     return fail(DCN_ERR_WORKSPACE, "workspace must be 256-byte aligned");
-  cudaError_t e = cudaSetDevice(p->device);
+  DeviceScope scope(p->device);
+  cudaError_t e = scope.err;
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
   cudaStream_t s = (cudaStream_t)stream;
   uint8_t *ws = (uint8_t *)workspace;
@@ -401,7 +542,7 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   if (!pl.tc) {
     if (ev) { cudaEventRecord(ev[1], s); cudaEventRecord(ev[2], s); }
     // tiny problems stay on the one-thread-per-output kernel: a 64x64 tile would be mostly empty
-    const bool tiled = simt_tiled_supported(pl.g) && env_int("DCN_B200_SIMT_TILED", 1, 0, 1) &&
+    const bool tiled = simt_tiled_supported(pl.g) && knobs().simt_tiled &&
                        pl.g.P * pl.g.Co >= 4096;
     e = tiled ? launch_simt_tiled(pl.g, ptrs, p->dtype, s)
               : launch_simt_direct(pl.g, ptrs, p->dtype, s);
@@ -412,7 +553,8 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   const void *xcl = p->input;
   if (pl.stage) {
     void *dst = ws + pl.ws.xcl_off;
-    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.op_format, s);
+    e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.op_format,
+                              pl.tp.version == 2 ? 1 : 0, s);
     if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
     xcl = dst;
   }
@@ -430,8 +572,11 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
   if (ev) cudaEventRecord(ev[2], s);
   // phase counters live in the workspace header, bytes [64, 256); off unless asked for
   unsigned long long *counters =
-      env_int("DCN_B200_COUNTERS", 0, 0, 1) ? (unsigned long long *)(ws + 64) : nullptr;
-  e = launch_tc(pl.g, pl.tp, ptrs, p->dtype, xcl, wimage, status, counters, s);
+      knobs().counters ? (unsigned long long *)(ws + 64) : nullptr;
+  e = pl.tp.version == 2
+          ? launch_tc2(pl.g, pl.tp, ptrs, p->dtype, xcl, wimage, status, counters,
+                       g_wait_limit_ns.load(), g_debug_flags.load(), s)
+          : launch_tc(pl.g, pl.tp, ptrs, p->dtype, xcl, wimage, status, counters, s);
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "tensor-core kernel launch: %s", cudaGetErrorString(e));
   if (ev) cudaEventRecord(ev[3], s);
   return DCN_OK;
@@ -462,7 +607,8 @@ int dcn_prepare_weights(const DcnFwdParams *p, void *image, size_t image_bytes, 
   if (!p->weight || !image || image_bytes < pl.ws.wtile_bytes || ((uintptr_t)image & 255))
     return fail(DCN_ERR_ARG, "weight and a 256-byte aligned image of %zu bytes are required",
                 pl.ws.wtile_bytes);
-  cudaError_t e = cudaSetDevice(p->device);
+  DeviceScope scope(p->device);
+  cudaError_t e = scope.err;
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
   e = launch_weight_tiles(pl.g, pl.tp, p->weight, p->dtype, image, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
@@ -472,12 +618,16 @@ int dcn_fwd_profiled(const DcnFwdParams *p, void *workspace, size_t workspace_by
                      float ms[3]) {
   if (!ms) return fail(DCN_ERR_ARG, "ms is NULL");
   if (!p) return fail(DCN_ERR_ARG, "params is NULL");
-  cudaError_t e = cudaSetDevice(p->device);
+  DeviceScope scope(p->device);
+  cudaError_t e = scope.err;
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
   cudaEvent_t ev[4];
   for (int i = 0; i < 4; ++i) {
     e = cudaEventCreate(&ev[i]);
-    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
+    if (e != cudaSuccess) {
+      for (int j = 0; j < i; ++j) cudaEventDestroy(ev[j]);
+      return fail(DCN_ERR_CUDA, "cudaEventCreate: %s", cudaGetErrorString(e));
+    }
   }
   int rc = run_fwd(p, workspace, workspace_bytes, stream, ev);
   if (rc == DCN_OK) {
@@ -500,8 +650,6 @@ static int bwd_common(const DcnFwdParams *p, int64_t n0, int64_t n1, Geom *g) {
   DeviceInfo *dev = nullptr;
   rc = probe_device(p->device, &dev);
   if (rc) return rc;
-  cudaError_t e = cudaSetDevice(p->device);
-  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
   return DCN_OK;
 }
 
@@ -510,6 +658,8 @@ int dcn_bwd_columns(const DcnFwdParams *p, int64_t n0, int64_t n1, float *column
   int rc = bwd_common(p, n0, n1, &g);
   if (rc) return rc;
   if (!columns) return fail(DCN_ERR_ARG, "columns must be non-NULL");
+  DeviceScope scope(p->device);
+  if (scope.err != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(scope.err));
   Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
   cudaError_t e = launch_bwd_columns(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), columns, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "column kernel launch: %s", cudaGetErrorString(e));
@@ -521,6 +671,8 @@ int dcn_bwd_input(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *gr
   int rc = bwd_common(p, n0, n1, &g);
   if (rc) return rc;
   if (!grad_columns || !grad_input) return fail(DCN_ERR_ARG, "grad_columns and grad_input must be non-NULL");
+  DeviceScope scope(p->device);
+  if (scope.err != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(scope.err));
   Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
   cudaError_t e = launch_bwd_input(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), grad_columns, grad_input, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "input-gradient kernel launch: %s", cudaGetErrorString(e));
@@ -532,9 +684,17 @@ int dcn_bwd_coord(const DcnFwdParams *p, int64_t n0, int64_t n1, const float *gr
   int rc = bwd_common(p, n0, n1, &g);
   if (rc) return rc;
   if (!grad_columns || !grad_offset) return fail(DCN_ERR_ARG, "grad_columns and grad_offset must be non-NULL");
+  DeviceScope scope(p->device);
+  if (scope.err != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(scope.err));
   Ptrs ptrs{p->input, p->offset, p->mask, p->weight, p->bias, p->output};
   cudaError_t e = launch_bwd_coord(g, ptrs, p->dtype, (int)n0, (int)(n1 - n0), grad_columns, grad_offset, grad_mask, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "coordinate-gradient kernel launch: %s", cudaGetErrorString(e));
+}
+
+int dcn_debug_configure(uint64_t wait_limit_ns, int32_t flags) {
+  g_wait_limit_ns.store(wait_limit_ns);
+  g_debug_flags.store(flags);
+  return DCN_OK;
 }
 
 int dcn_read_counters(const void *workspace, void *stream, uint64_t counters[24]) {
@@ -571,14 +731,15 @@ int dcn_to_channels_last(const void *input, void *output, int32_t dtype, int64_t
   DeviceInfo *dev = nullptr;
   int rc = probe_device(device, &dev);
   if (rc) return rc;
-  cudaError_t e = cudaSetDevice(device);
+  DeviceScope scope(device);
+  cudaError_t e = scope.err;
   if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
   Geom g;
   memset(&g, 0, sizeof(g));
   g.N = (int)N; g.C = (int)C; g.H = (int)H; g.W = (int)W;
   g.in_sn = in_stride[0]; g.in_sc = in_stride[1]; g.in_sh = in_stride[2]; g.in_sw = in_stride[3];
   const int op_format = dtype == DCN_DTYPE_F32 ? 2 : (dtype == DCN_DTYPE_F16 ? 0 : 1);
-  e = launch_stage_input_cl(g, input, dtype, output, op_format, (cudaStream_t)stream);
+  e = launch_stage_input_cl(g, input, dtype, output, op_format, 0, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "layout copy launch: %s", cudaGetErrorString(e));
 }
 

@@ -59,6 +59,14 @@ struct TcPlan {
   int ch_per_stage;        // input channels per k-stage: 64 (bf16) or 32 (TF32x3)
   int producer_cfg;        // [flags*1000 +] groups*100 + warps_per_group*10 + rows in flight per thread
   int io_bytes;            // element size of the tensors (bias staging in the epilogue)
+  // --- second-generation 16-bit kernel (dcn_tc2.cu) ---
+  int version;             // 1: dcn_fwd_tc, 2: dcn_fwd_tc2
+  int tab_span;            // chunks that share one tap-table segment; 0: one segment per k-stage
+  int tab_slots;           // ring depth of the tap table
+  int tab_slot_blocks;     // (tap, deform group) blocks per ring slot
+  int win_h, win_w;        // input window held in shared memory, in pixels (0: none)
+  int win_my, win_mx;      // its margin above / left of the tile's undeformed footprint
+  int epi_tma;             // 1: the epilogue stores through the tensor-copy engine
 };
 
 enum { kBM = 128 };
@@ -119,8 +127,10 @@ cudaError_t launch_simt_tiled(const Geom &g, const Ptrs &p, int dtype, cudaStrea
 size_t simt_tiled_smem(const Geom &g);
 bool simt_tiled_supported(const Geom &g);
 
+// pad: width of the zero border around every sample of the copy (0 or 1); with a border the
+// copy ends with one more all-zero row
 cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
-                                  int op_format, cudaStream_t s);
+                                  int op_format, int pad, cudaStream_t s);
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight,
                                 int dtype, void *wtiles, cudaStream_t s);
 cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xcl,
@@ -129,6 +139,12 @@ cudaError_t launch_tc(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype,
 cudaError_t launch_clear_status(int *status, cudaStream_t s);
 
 int tc_threads(const TcPlan &tp);
+size_t tc2_smem_bytes(const TcPlan &tp);
+// Debug knobs of the second-generation kernel (tests of the bounded waits): wait limit in
+// nanoseconds (0: default) and flags (bit 0: the weight loader withholds its last copy).
+cudaError_t launch_tc2(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xpad,
+                       const void *wtiles, int *status, unsigned long long *counters,
+                       unsigned long long wait_limit_ns, int debug_flags, cudaStream_t s);
 
 cudaError_t launch_bwd_columns(const Geom &g, const Ptrs &p, int dtype, int n0, int ns, float *col,
                                cudaStream_t s);

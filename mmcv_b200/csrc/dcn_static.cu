@@ -52,8 +52,12 @@ extern "C" int dcn_fwd_static_scratch(const DcnFwdParams *p, void *stream, void 
     ptr = g_static_ptr[p->device];
     if (!ptr) {
       // Set-up, once per device and with that device current: resolve the array's address.
-      cudaError_t e = cudaSetDevice(p->device);
+      // (the caller's current device is put back afterwards)
+      int prev = -1;
+      cudaError_t e = cudaGetDevice(&prev);
+      if (e == cudaSuccess && prev != p->device) e = cudaSetDevice(p->device);
       if (e == cudaSuccess) e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+      if (prev >= 0 && prev != p->device) cudaSetDevice(prev);
       if (e != cudaSuccess || !ptr) {
         char msg[256];
         snprintf(msg, sizeof(msg), "cannot resolve the built-in scratch array on device %d: %s",

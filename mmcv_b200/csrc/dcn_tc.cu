@@ -24,20 +24,16 @@
 #include <climits>
 
 #include "dcn_internal.cuh"
+#include "dcn_ptx.cuh"
 
 namespace dcn {
 
 namespace {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
-// How long one mbarrier.try_wait may keep the thread suspended in hardware (it wakes at once
-// when the phase completes): waiting warps then take no issue slots from the producers.
-constexpr uint32_t kSuspendHintNs = 20000u;
 constexpr int kEpilogueWarps = 4;
 constexpr int kMmaWarp = 4;
 constexpr int kLoadWarp = 5;
 constexpr int kFirstProducerWarp = 6;
-constexpr int kTileBytes = kBM * 128;  // one operand tile: 128 rows of 128 bytes (16 KiB)
 
 // Arithmetic modes of the contraction.
 //  kModeBf16:   bf16 operands, one operand tile per stage, 64 channels per stage;
@@ -46,7 +42,6 @@ constexpr int kTileBytes = kBM * 128;  // one operand tile: 128 rows of 128 byte
 //               held as fp32 bit patterns; the tensor core reads their top 19 bits), two
 //               operand tiles per stage, 32 channels per stage, three MMAs per k-step:
 //               hi*hi + lo*hi + hi*lo with fp32 accumulation.
-enum { kModeBf16 = 0, kModeTf32x3 = 1, kModeF16 = 2 };
 template <int MODE> struct ModeTraits;
 template <> struct ModeTraits<kModeBf16> {
   using TabW = uint2;  // table entry: four 16-bit corner weights
@@ -71,325 +66,6 @@ struct TcArgs {
   int *status;
   unsigned long long *counters;  // optional phase timers (block 0 only), or nullptr
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void *p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity), "r"(kSuspendHintNs)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false when the block is aborting.  kBackoff: sleep between polls;
-// used by the roles that wait long and are not on the critical path (epilogue, loader), so
-// that their polling does not take issue slots from the producer warps.
-template <bool kBackoff = false>
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_s,
-                                          int *status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = globaltimer_ns();
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (kBackoff) __nanosleep(200);
-    if ((it & 31u) == 0u) {
-      if (*abort_s) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
-        *abort_s = 1;
-        atomicCAS(status, 0, code);
-        return false;
-      }
-    }
-  }
-}
-__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes,
-                                              uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-// Phase timer for the optional counters: adds the clock cycles since `t0` to slot `i` and
-// restarts `t0`.
-struct PhaseTimer {
-  unsigned long long *c;
-  long long t0;
-  __device__ __forceinline__ PhaseTimer(unsigned long long *counters, bool elected)
-      : c(elected ? counters : nullptr), t0(0) {
-    if (c) t0 = clock64();
-  }
-  __device__ __forceinline__ void lap(int i) {
-    if (c) {
-      // fire-and-forget reductions: a read-modify-write here would put a memory round
-      // trip into the phase that follows
-      const long long t1 = clock64();
-      atomicAdd(c + i, (unsigned long long)(t1 - t0));
-      t0 = t1;
-    }
-  }
-  __device__ __forceinline__ void count(int i) {
-    if (c) atomicAdd(c + i, 1ull);
-  }
-};
-
-__device__ __forceinline__ void prefetch_l2(const void *p) {
-  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
-}
-// Loads whose issue order the compiler must keep (volatile): a batch of them is issued
-// back to back so that their latencies overlap, and only then is the first one consumed.
-// The value is returned raw; converting it (raw_to_float) is a use and waits for the load.
-__device__ __forceinline__ uint32_t ldg_raw_ordered(const float *p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.b32 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t ldg_raw_ordered(const __nv_bfloat16 *p) {
-  uint32_t v;  // a 32-bit register: two 16-bit results packed into one would be a use
-  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-__device__ __forceinline__ uint32_t ldg_raw_ordered(const __half *p) {
-  uint32_t v;
-  asm volatile("ld.global.nc.u16 %0, [%1];" : "=r"(v) : "l"(p));
-  return v;
-}
-template <typename T> struct RawOf {
-  using type = uint32_t;
-  static __device__ __forceinline__ float to_float(uint32_t v) { return __uint_as_float(v); }
-};
-template <> struct RawOf<__nv_bfloat16> {
-  using type = uint32_t;
-  static __device__ __forceinline__ float to_float(uint32_t v) { return __uint_as_float(v << 16); }
-};
-template <> struct RawOf<__half> {
-  using type = uint32_t;
-  static __device__ __forceinline__ float to_float(uint32_t v) {
-    return __half2float(__ushort_as_half((unsigned short)v));
-  }
-};
-// 16-byte read-only load, zero when `take` is 0.  `tok` is passed through untouched; code that
-// must come after this load's issue takes `tok` as an input.
-__device__ __forceinline__ uint4 ldg16_pinned(const void *p, uint32_t take, uint32_t &tok) {
-  uint4 r;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.u32 p, %5, 0;\n\t"
-      "mov.u32 %0, 0;\n\tmov.u32 %1, 0;\n\tmov.u32 %2, 0;\n\tmov.u32 %3, 0;\n\t"
-      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t}"
-      : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
-      : "l"(p), "r"(take), "r"(tok));
-  asm volatile("" : "+r"(tok));
-  return r;
-}
-__device__ __forceinline__ void fence_proxy_async_smem() {
-  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t slot, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot),
-               "r"(cols)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_relinquish() {
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols)
-               : "memory");
-}
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// True in exactly one lane of the (fully converged) warp.
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
-               : "memory");
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
-        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
-        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr)
-      : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes
-// (64 elements) with the 128-byte swizzle: 8-row groups are 1024 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr) {
-  uint64_t d = (uint64_t)((saddr >> 4) & 0x3FFFu);
-  d |= (uint64_t)1 << 16;            // leading byte offset (unused with swizzle), 16 B
-  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
-  d |= (uint64_t)1 << 46;            // descriptor version of this architecture
-  d |= (uint64_t)2 << 61;            // 128-byte swizzle
-  return d;
-}
-
-__device__ __forceinline__ __nv_bfloat162 as_bf162(uint32_t u) {
-  return *reinterpret_cast<const __nv_bfloat162 *>(&u);
-}
-__device__ __forceinline__ uint32_t bf162_bits(__nv_bfloat162 h) {
-  return *reinterpret_cast<const uint32_t *>(&h);
-}
-
-// A table entry's corner weights in the form the blends take: each 16-bit weight twice (a
-// pair), or the four fp32 weights as they are.
-template <int MODE>
-__device__ __forceinline__ uint4 table_weights(const uint2 &w) {
-  return make_uint4(__byte_perm(w.x, 0u, 0x1010), __byte_perm(w.x, 0u, 0x3232),
-                    __byte_perm(w.y, 0u, 0x1010), __byte_perm(w.y, 0u, 0x3232));
-}
-template <int MODE>
-__device__ __forceinline__ uint4 table_weights(const uint4 &w) { return w; }
-
-// Four consecutive elements (8- or 16-byte aligned) as floats, with one load.
-__device__ __forceinline__ void load4_as_float(const float *p, float (&o)[4]) {
-  const float4 v = *reinterpret_cast<const float4 *>(p);
-  o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
-}
-__device__ __forceinline__ void load4_as_float(const __nv_bfloat16 *p, float (&o)[4]) {
-  const uint2 v = *reinterpret_cast<const uint2 *>(p);
-  o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
-  o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
-}
-__device__ __forceinline__ void load4_as_float(const __half *p, float (&o)[4]) {
-  const uint2 v = *reinterpret_cast<const uint2 *>(p);
-  const float2 a = __half22float2(*reinterpret_cast<const __half2 *>(&v.x));
-  const float2 b = __half22float2(*reinterpret_cast<const __half2 *>(&v.y));
-  o[0] = a.x; o[1] = a.y; o[2] = b.x; o[3] = b.y;
-}
-
-// The modulation value of a tap: the mask element, or its sigmoid when the tensor holds logits.
-__device__ __forceinline__ float mask_value(const Geom &g, float m) {
-  return g.mask_act == DCN_ACT_SIGMOID ? 1.f / (1.f + __expf(-m)) : m;
-}
-
-// Bilinear blend of four 8-channel bf16 corner vectors on packed bf16 FMAs: one multiply
-// and three fused multiply-adds per channel pair, each rounding to bf16.  `w` holds each
-// corner weight twice (a bf16 pair).
-__device__ __forceinline__ uint4 blend8_bf16(const uint4 &w, const uint4 &q0, const uint4 &q1,
-                                             const uint4 &q2, const uint4 &q3) {
-  uint4 o;
-  const __nv_bfloat162 w0 = as_bf162(w.x), w1 = as_bf162(w.y), w2 = as_bf162(w.z),
-                       w3 = as_bf162(w.w);
-  const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
-  const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
-  const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
-  const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
-  uint32_t *r = reinterpret_cast<uint32_t *>(&o);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __nv_bfloat162 t = __hmul2(w0, as_bf162(a0[i]));
-    t = __hfma2(w1, as_bf162(a1[i]), t);
-    t = __hfma2(w2, as_bf162(a2[i]), t);
-    t = __hfma2(w3, as_bf162(a3[i]), t);
-    r[i] = bf162_bits(t);
-  }
-  return o;
-}
-
-// The same blend on packed fp16 FMAs (fp16 tensors).
-__device__ __forceinline__ uint4 blend8_f16(const uint4 &w, const uint4 &q0, const uint4 &q1,
-                                            const uint4 &q2, const uint4 &q3) {
-  uint4 o;
-  const __half2 *wh = reinterpret_cast<const __half2 *>(&w);
-  const __half2 *a0 = reinterpret_cast<const __half2 *>(&q0);
-  const __half2 *a1 = reinterpret_cast<const __half2 *>(&q1);
-  const __half2 *a2 = reinterpret_cast<const __half2 *>(&q2);
-  const __half2 *a3 = reinterpret_cast<const __half2 *>(&q3);
-  __half2 *r = reinterpret_cast<__half2 *>(&o);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    __half2 t = __hmul2(wh[0], a0[i]);
-    t = __hfma2(wh[1], a1[i], t);
-    t = __hfma2(wh[2], a2[i], t);
-    t = __hfma2(wh[3], a3[i], t);
-    r[i] = t;
-  }
-  return o;
-}
-
-// Bilinear blend of four 4-channel fp32 corner vectors in fp32 (weights are fp32 bits),
-// split into the TF32 high part (low 13 mantissa bits cleared) and the exact remainder.
-__device__ __forceinline__ void blend4_tf32(const uint4 &w, const uint4 &q0, const uint4 &q1,
-                                            const uint4 &q2, const uint4 &q3, uint4 &hi,
-                                            uint4 &lo) {
-  const float w0 = __uint_as_float(w.x), w1 = __uint_as_float(w.y), w2 = __uint_as_float(w.z),
-              w3 = __uint_as_float(w.w);
-  const uint32_t *a0 = reinterpret_cast<const uint32_t *>(&q0);
-  const uint32_t *a1 = reinterpret_cast<const uint32_t *>(&q1);
-  const uint32_t *a2 = reinterpret_cast<const uint32_t *>(&q2);
-  const uint32_t *a3 = reinterpret_cast<const uint32_t *>(&q3);
-  uint32_t *h = reinterpret_cast<uint32_t *>(&hi);
-  uint32_t *l = reinterpret_cast<uint32_t *>(&lo);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float t = w0 * __uint_as_float(a0[i]);
-    t = fmaf(w1, __uint_as_float(a1[i]), t);
-    t = fmaf(w2, __uint_as_float(a2[i]), t);
-    t = fmaf(w3, __uint_as_float(a3[i]), t);
-    const uint32_t hb = __float_as_uint(t) & 0xffffe000u;
-    h[i] = hb;
-    l[i] = __float_as_uint(t - __uint_as_float(hb));
-  }
-}
 
 constexpr int kRowInvalid = INT_MIN;
 // Entries of one (tap, deform group) block of the tap table: the rows plus a skew of four, so
@@ -1025,7 +701,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
 template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, int W,
-                   long long sn, long long sc, long long sh, long long sw) {
+                   long long sn, long long sc, long long sh, long long sw, int pad) {
   __shared__ float tile[32][33];
   const int n = blockIdx.z;
   const int q0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
@@ -1047,8 +723,13 @@ dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, in
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int q = q0 + ty + 8 * k;
-      if (q < HW && c < C)
-        st_from_float(y, ((long long)n * HW + q) * C + c, tile[tx][ty + 8 * k]);
+      if (q < HW && c < C) {
+        // with a border, pixel (h, w) goes to (h + pad, w + pad) of an (H + 2 pad) x (W + 2 pad) image
+        const long long dq = pad ? (long long)n * (H + 2 * pad) * (W + 2 * pad) +
+                                       (long long)(q / W + pad) * (W + 2 * pad) + (q % W + pad)
+                                 : (long long)n * HW + q;
+        st_from_float(y, dq * C + c, tile[tx][ty + 8 * k]);
+      }
     }
   }
 }
@@ -1061,7 +742,7 @@ dcn_stage_input_cl(const T *__restrict__ x, TO *__restrict__ y, int C, int H, in
 // are XORed with (pixel & 7), which keeps both shared-memory phases free of bank conflicts.
 __global__ void __launch_bounds__(256)
 dcn_stage_input_cl_16bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, int C,
-                         long long HW, long long sn, long long sc) {
+                         long long HW, long long sn, long long sc, int W, int pad) {
   __shared__ __align__(16) uint32_t tile[64][32];
   const int n = blockIdx.z;
   const long long q0 = (long long)blockIdx.x * 64;
@@ -1090,8 +771,59 @@ dcn_stage_input_cl_16bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y,
     const int vec = threadIdx.x + k * 256;
     const int p = vec >> 3, o = vec & 7;
     const uint4 d = *reinterpret_cast<const uint4 *>(&tile[p][(o ^ (p & 7)) << 2]);
-    if (q0 + p < HW && c0 + o * 8 < C)
-      *reinterpret_cast<uint4 *>(y + (((long long)n * HW + q0 + p) * C + c0 + o * 8) * 2) = d;
+    if (q0 + p < HW && c0 + o * 8 < C) {
+      const long long q = q0 + p;
+      const int H = (int)(HW / W);
+      const long long dq = pad ? (long long)n * (H + 2 * pad) * (W + 2 * pad) +
+                                     (q / W + pad) * (W + 2 * pad) + (q % W + pad)
+                               : (long long)n * HW + q;
+      *reinterpret_cast<uint4 *>(y + (dq * C + c0 + o * 8) * 2) = d;
+    }
+  }
+}
+
+// Zeroes the border of a padded channels-last copy [N][H+2][W+2][C] and the extra row that
+// follows the last sample; 16 bytes per thread and step (C * esize is a multiple of 16).
+__global__ void __launch_bounds__(256)
+dcn_zero_border(uint8_t *__restrict__ y, int N, int H, int W, int vec_per_px) {
+  const int Wp = W + 2, Hp = H + 2;
+  const long long per_sample = 2LL * Wp + 2LL * H;  // border pixels of one sample
+  const long long total = ((long long)N * per_sample + Wp) * vec_per_px;
+  const uint4 z = make_uint4(0u, 0u, 0u, 0u);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long bp = i / vec_per_px;
+    const int vv = (int)(i - bp * vec_per_px);
+    long long pix;  // pixel index in the padded buffer
+    if (bp >= (long long)N * per_sample) {
+      pix = (long long)N * Hp * Wp + (bp - (long long)N * per_sample);
+    } else {
+      const long long n = bp / per_sample;
+      const long long r = bp - n * per_sample;
+      long long hh, ww;
+      if (r < Wp) { hh = 0; ww = r; }
+      else if (r < 2LL * Wp) { hh = Hp - 1; ww = r - Wp; }
+      else { const long long k = r - 2LL * Wp; hh = 1 + (k >> 1); ww = (k & 1) ? Wp - 1 : 0; }
+      pix = (n * Hp + hh) * Wp + ww;
+    }
+    *reinterpret_cast<uint4 *>(y + (pix * vec_per_px + vv) * 16) = z;
+  }
+}
+
+// Channels-last input (dense, the copy's own 16-bit type) -> the same with a zero border.
+__global__ void __launch_bounds__(256)
+dcn_pad_cl_copy(const uint8_t *__restrict__ x, uint8_t *__restrict__ y, long long n_px, int H, int W,
+                int vec_per_px) {
+  const long long total = n_px * vec_per_px;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long px = i / vec_per_px;
+    const int vv = (int)(i - px * vec_per_px);
+    const long long n = px / ((long long)H * W);
+    const long long q = px - n * (long long)H * W;
+    const long long dq = (n * (H + 2) + q / W + 1) * (W + 2) + q % W + 1;
+    *reinterpret_cast<uint4 *>(y + (dq * vec_per_px + vv) * 16) =
+        __ldg(reinterpret_cast<const uint4 *>(x + i * 16));
   }
 }
 
@@ -1132,22 +864,44 @@ dcn_stage_input_cl_32bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y,
 
 namespace {
 template <typename T, typename TO>
-void stage_launch(const Geom &g, const void *input, void *xcl, dim3 grid, cudaStream_t s) {
+void stage_launch(const Geom &g, const void *input, void *xcl, dim3 grid, int pad, cudaStream_t s) {
   dcn_stage_input_cl<T, TO><<<grid, 256, 0, s>>>((const T *)input, (TO *)xcl, g.C, g.H, g.W,
-                                                  g.in_sn, g.in_sc, g.in_sh, g.in_sw);
+                                                  g.in_sn, g.in_sc, g.in_sh, g.in_sw, pad);
 }
 template <typename TO>
-void stage_from(const Geom &g, const void *input, int dtype, void *xcl, dim3 grid, cudaStream_t s) {
-  if (dtype == DCN_DTYPE_F32) stage_launch<float, TO>(g, input, xcl, grid, s);
-  else if (dtype == DCN_DTYPE_F16) stage_launch<__half, TO>(g, input, xcl, grid, s);
-  else stage_launch<__nv_bfloat16, TO>(g, input, xcl, grid, s);
+void stage_from(const Geom &g, const void *input, int dtype, void *xcl, dim3 grid, int pad,
+                cudaStream_t s) {
+  if (dtype == DCN_DTYPE_F32) stage_launch<float, TO>(g, input, xcl, grid, pad, s);
+  else if (dtype == DCN_DTYPE_F16) stage_launch<__half, TO>(g, input, xcl, grid, pad, s);
+  else stage_launch<__nv_bfloat16, TO>(g, input, xcl, grid, pad, s);
 }
 }  // namespace
 
 // op_format: element type of the channels-last copy (0 fp16, 1 bf16, 2 fp32 for TF32x3)
 cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, void *xcl,
-                                  int op_format, cudaStream_t s) {
+                                  int op_format, int pad, cudaStream_t s) {
   if (g.N == 0) return cudaSuccess;
+  if (pad) {
+    // the border (and the all-zero row after the last sample) first; the copies below fill
+    // the interior
+    const int vpp = g.C * (op_format == 2 ? 4 : 2) / 16;
+    const long long total = ((long long)g.N * (2LL * (g.W + 2) + 2LL * g.H) + g.W + 2) * vpp;
+    const unsigned blocks = (unsigned)((total + 255) / 256 < 4096 ? (total + 255) / 256 : 4096);
+    dcn_zero_border<<<blocks, 256, 0, s>>>((uint8_t *)xcl, g.N, g.H, g.W, vpp);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    // dense channels-last input in the copy's type: a plain vector copy
+    const bool same16 = dtype != DCN_DTYPE_F32 && op_format != 2 &&
+                        (op_format == 0) == (dtype == DCN_DTYPE_F16);
+    if (same16 && g.in_sc == 1 && g.in_sw == g.C && g.in_sh == (long long)g.W * g.C &&
+        g.in_sn == (long long)g.H * g.W * g.C && ((uintptr_t)input & 15) == 0) {
+      const long long n_px = (long long)g.N * g.H * g.W;
+      const long long tv = n_px * vpp;
+      const unsigned cb = (unsigned)((tv + 255) / 256 < 148 * 64 ? (tv + 255) / 256 : 148 * 64);
+      dcn_pad_cl_copy<<<cb, 256, 0, s>>>((const uint8_t *)input, (uint8_t *)xcl, n_px, g.H, g.W, vpp);
+      return cudaGetLastError();
+    }
+  }
   {
     // 16-bit in, the same 16-bit type out, contiguous planes
     const bool same16 = dtype != DCN_DTYPE_F32 && op_format != 2 &&
@@ -1158,11 +912,11 @@ cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, v
         (g.C + 63) / 64 <= 65535) {
       dim3 grid((unsigned)((HW + 63) / 64), (unsigned)((g.C + 63) / 64), (unsigned)g.N);
       dcn_stage_input_cl_16bit<<<grid, 256, 0, s>>>((const uint8_t *)input, (uint8_t *)xcl, g.C, HW,
-                                                    g.in_sn, g.in_sc);
+                                                    g.in_sn, g.in_sc, g.W, pad);
       return cudaGetLastError();
     }
     // fp32 in, fp32 out
-    if (dtype == DCN_DTYPE_F32 && op_format == 2 && g.in_sw == 1 && g.in_sh == g.W && HW % 4 == 0 &&
+    if (!pad && dtype == DCN_DTYPE_F32 && op_format == 2 && g.in_sw == 1 && g.in_sh == g.W && HW % 4 == 0 &&
         g.C % 4 == 0 && g.in_sn % 4 == 0 && g.in_sc % 4 == 0 && ((uintptr_t)input & 15) == 0 &&
         g.N <= 65535 && (g.C + 31) / 32 <= 65535) {
       dim3 grid((unsigned)((HW + 63) / 64), (unsigned)((g.C + 31) / 32), (unsigned)g.N);
@@ -1172,9 +926,9 @@ cudaError_t launch_stage_input_cl(const Geom &g, const void *input, int dtype, v
     }
   }
   dim3 grid((g.H * g.W + 31) / 32, (g.C + 31) / 32, g.N);
-  if (op_format == 2) stage_from<float>(g, input, dtype, xcl, grid, s);
-  else if (op_format == 0) stage_from<__half>(g, input, dtype, xcl, grid, s);
-  else stage_from<__nv_bfloat16>(g, input, dtype, xcl, grid, s);
+  if (op_format == 2) stage_from<float>(g, input, dtype, xcl, grid, pad, s);
+  else if (op_format == 0) stage_from<__half>(g, input, dtype, xcl, grid, pad, s);
+  else stage_from<__nv_bfloat16>(g, input, dtype, xcl, grid, pad, s);
   return cudaGetLastError();
 }
 
@@ -1303,6 +1057,7 @@ cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 }  // namespace
 
 int tc_threads(const TcPlan &tp) {
+  if (tp.version == 2) return 768;  // dcn_fwd_tc2: 4 epilogue, MMA, loader, 2 builder and 16 gather warps
   return (kFirstProducerWarp + ((tp.producer_cfg / 100) % 10) * ((tp.producer_cfg / 10) % 10)) * 32;
 }
 

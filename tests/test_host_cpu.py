@@ -50,6 +50,7 @@ def test_plan_routes_and_sizes():
     assert info.workspace_bytes >= 2 * 64 * 16 * 16 * 2 + 64 * 64 * 9 * 2
     rc, info = plan(params(dtype=_lib.DTYPE_F32))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32   # 3xTF32
+    assert info.kernel_version == 1
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_FFMA))
     assert rc == 0 and info.path == _lib.PATH_SIMT_TILED
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_FFMA, N=1, C=4, Co=4, H=5, W=5))
@@ -61,12 +62,17 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
-    # every 64-channel chunk has deform groups of its own: per-group tap tables, and four
-    # operand stages inside the 164 KB shared-memory configuration
-    assert info.producer_layout == 3282 and info.block == (6 + 16) * 32
-    assert (info.operand_stages, info.weight_stages) == (4, 2) and info.smem_bytes <= 167936 - 1024
+    # 16-bit tensors run on the second-generation kernel: 4 epilogue + MMA + loader + 2 table
+    # builder + 16 gather warps.  Every 64-channel chunk has deform groups of its own here, so
+    # a table segment serves one k-stage.
+    assert info.kernel_version == 2 and info.producer_layout == 2016 and info.block == 24 * 32
+    assert info.table_span == 0 and info.table_slots >= 4
+    assert info.operand_stages >= 2 and info.weight_stages == 2
     rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
-    assert rc == 0 and info.producer_layout == 1282      # chunks share their deform group
+    # the four chunks of a tile share their deform group: one table segment per tile, two slots
+    assert rc == 0 and info.kernel_version == 2 and (info.table_span, info.table_slots) == (4, 2)
+    rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
+    assert rc == 0 and (info.table_span, info.table_slots) == (2, 2)   # 128 channels per deform group
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
@@ -108,6 +114,44 @@ def test_forward_on_cpu_tensors_fails_loudly():
         _ext.deform_conv_forward(x, w, torch.zeros(1, 18, 5, 5), out, e, e, kW=3, kH=3, dW=1,
                                  dH=1, padW=1, padH=1, dilationW=1, dilationH=1, group=1,
                                  deformable_group=1, im2col_step=1)
+
+
+def test_offset_mask_output_shapes_are_checked_before_any_launch():
+    """The kernels take every size from the problem geometry, so a tensor of another shape must
+    be rejected on the host (no launch happens here: the tensors are CPU tensors and the shape
+    error comes first)."""
+    x = torch.randn(2, 4, 6, 6)
+    w = torch.randn(4, 4, 3, 3)
+    e = x.new_empty(0)
+
+    def call(offset, mask, out, dg=1, stride=1):
+        _ext.modulated_deform_conv_forward(
+            x, w, e, e, offset, mask, out, e, kernel_h=3, kernel_w=3, stride_h=stride,
+            stride_w=stride, pad_h=1, pad_w=1, dilation_h=1, dilation_w=1, group=1,
+            deformable_group=dg, with_bias=False)
+
+    good_off, good_msk, good_out = torch.zeros(2, 18, 6, 6), torch.ones(2, 9, 6, 6), torch.empty(2, 4, 6, 6)
+    for off, msk, out, kw, what in [
+            (torch.zeros(2, 18, 3, 3), good_msk, good_out, {}, 'offset'),       # made for stride 2
+            (torch.zeros(1, 18, 6, 6), good_msk, good_out, {}, 'offset'),       # smaller batch
+            (good_off, torch.ones(2, 18, 6, 6), good_out, {}, 'mask'),          # two deform groups' worth
+            (good_off, good_msk, torch.empty(2, 4, 5, 6), {}, 'output'),
+            (good_off, good_msk, good_out, dict(dg=2), 'offset'),               # wrong deformable_group
+            (good_off, good_msk, good_out, dict(stride=2), 'offset')]:
+        with pytest.raises(RuntimeError, match=f'{what} has shape'):
+            call(off, msk, out, **kw)
+    with pytest.raises(RuntimeError, match='CUDA tensor'):     # all shapes right: next check
+        call(good_off, good_msk, good_out)
+    # the branch form: channel count and spatial size of the branch output
+    with pytest.raises(RuntimeError, match='offset channels'):
+        _ext.forward_from_branch(x, torch.zeros(2, 20, 6, 6), 18, w, None, good_out, (1, 1), (1, 1),
+                                 (1, 1), 1, 1)
+    with pytest.raises(RuntimeError, match='not the output size'):
+        _ext.forward_from_branch(x, torch.zeros(2, 27, 3, 3), 18, w, None, good_out, (1, 1), (1, 1),
+                                 (1, 1), 1, 1)
+    with pytest.raises(RuntimeError, match='output has shape'):
+        _ext.forward_from_branch(x, torch.zeros(2, 27, 6, 6), 18, w, None, torch.empty(2, 4, 3, 3),
+                                 (1, 1), (1, 1), (1, 1), 1, 1)
 
 
 def test_kernel_shape_mismatch_is_runtime_error():
