@@ -190,31 +190,38 @@ int resolved_math(const DcnFwdParams *p) {
 }
 
 
-// Second-generation 16-bit kernel: table segments, ring depths, input window, epilogue stores.
-// Leaves the plan on the first-generation kernel when the problem does not fit.
+// Second-generation 16-bit kernel: K units, table segments, ring depths, input window,
+// epilogue stores.  Leaves the plan on the first-generation kernel when the problem does not fit.
 void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   const Knobs &kn = knobs();
   // offsets into the padded copy are 31-bit byte offsets within a sample
   if ((long long)(g.H + 3) * (g.W + 2) * g.C * 2 >= 2147483647LL) return;
+  if (tp->items >= 2147483647LL) return;
   TcPlan t = *tp;
   t.version = 2;
   t.producer_cfg = 2016;  // 2 table-builder warps, 16 gather warps
-  // Table segments.  Chunks whose deform groups are the same share their table entries: when
-  // every tile splits into runs of L >= 2 such chunks, one segment (all taps) serves a run and
-  // the ring holds two of them; otherwise a segment serves one k-stage.
-  int run = -1;
+  // K units: (32-channel half-chunk, tap), half-chunk-major; two per k-stage
+  t.KH = (g.Cg + 31) / 32;
+  t.U = t.KH * g.T;
+  t.S = (t.U + 1) / 2;
+  // Table segments.  Half-chunks with the same single deform group share their table entries:
+  // when every tile splits into runs of L >= 2 such half-chunks, one segment (a block per tap)
+  // serves a run and the ring holds two of them; otherwise a segment serves one k-stage (two
+  // units, a block per unit and deform group).
+  int run = -1, ndu = 1;
   bool uniform = true;
-  for (int grp = 0; grp < g.groups && uniform; ++grp) {
+  for (int grp = 0; grp < g.groups; ++grp) {
     int prev_lo = -1, prev_nd = 0, len = 0;
-    for (int cc = 0; cc <= t.KC; ++cc) {
+    for (int hc = 0; hc <= t.KH; ++hc) {
       int lo = -2, nd = 0;
-      if (cc < t.KC) {
-        const int c0 = grp * g.Cg + cc * 64;
-        const int c1 = c0 + 64 < (grp + 1) * g.Cg ? c0 + 64 : (grp + 1) * g.Cg;
+      if (hc < t.KH) {
+        const int c0 = grp * g.Cg + hc * 32;
+        const int c1 = c0 + 32 < (grp + 1) * g.Cg ? c0 + 32 : (grp + 1) * g.Cg;
         lo = c0 / g.cpdg;
         nd = (c1 - 1) / g.cpdg - lo + 1;
+        if (nd > ndu) ndu = nd;
       }
-      if (lo == prev_lo && nd == prev_nd) { ++len; continue; }
+      if (lo == prev_lo && nd == prev_nd && nd == 1) { ++len; continue; }
       if (len > 0) {
         if (run < 0) run = len;
         else if (run != len) uniform = false;
@@ -222,9 +229,12 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
       prev_lo = lo; prev_nd = nd; len = 1;
     }
   }
+  if (ndu > 8) return;
+  t.ndu = ndu;
   const size_t entry = 12;  // bytes of a table entry
-  t.tab_span = (uniform && run >= 2 && (size_t)2 * g.T * t.ndgc * (kBM + 4) * entry <= 60 * 1024) ? run : 0;
-  t.tab_slot_blocks = t.tab_span ? g.T * t.ndgc : t.ndgc;
+  t.tab_span = (uniform && run >= 2 && ndu == 1 && t.KH % run == 0 &&
+                (size_t)2 * g.T * (kBM + 4) * entry <= 60 * 1024) ? run : 0;
+  t.tab_slot_blocks = t.tab_span ? g.T : 2 * ndu;
   t.tab_slots = t.tab_span ? 2 : (kn.tab_slots ? kn.tab_slots : 6);
   if ((size_t)t.tab_slots * t.tab_slot_blocks * (kBM + 4) * entry > 64 * 1024) return;
   // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles
@@ -238,22 +248,23 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     t.epi_tma = (want && aligned && slabs_ok && g.N > 0) ? 1 : 0;
   }
   // Input window in shared memory: the tile's undeformed footprint plus a margin of m pixels
-  // on every side, 64 channels, two buffers.  Largest margin (up to 4) that fits wins.
+  // on every side, 32 channels, two buffers.  Largest margin (up to 6) that fits wins; the
+  // width is rounded up to an even number of pixels (bank rule of the paired reads).
   const int th = kBM >> t.tw_log2, tw = 1 << t.tw_log2;
-  const int fh = (th - 1) * g.stride_h + (g.kh - 1) * g.dil_h + 1;
-  const int fw = (tw - 1) * g.stride_w + (g.kw - 1) * g.dil_w + 1;
+  const int fh = (th - 1) * g.stride_h + (g.kh - 1) * g.dil_h + 2;  // + the lower/right corner
+  const int fw = (tw - 1) * g.stride_w + (g.kw - 1) * g.dil_w + 2;
   const int m_max = kn.window < 0 ? 0 : kn.window;
   bool found = false;
   for (int m = m_max; m >= 0 && !found; --m) {
     t.win_h = m ? fh + 2 * m : 0;
-    t.win_w = m ? fw + 2 * m : 0;
+    t.win_w = m ? (fw + 2 * m + 1) / 2 * 2 : 0;
     t.win_my = t.win_mx = m;
     if (m && (t.win_h > 256 || t.win_w > 256)) continue;
     // without a window the gather lives on L1: stay inside the 164 KB shared-memory
     // configuration if possible
     const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
     for (int bi = (m || kn.small_l1) ? 1 : 0; bi < 2 && !found; ++bi)
-      for (int as = 4; as >= 2 && !found; --as) {
+      for (int as = m ? 3 : 4; as >= 2 && !found; --as) {
         if (kn.a_stages && as != kn.a_stages) continue;
         t.a_stages = as;
         t.b_stages = kn.b_stages ? kn.b_stages : 2;

@@ -61,7 +61,10 @@ struct TcPlan {
   int io_bytes;            // element size of the tensors (bias staging in the epilogue)
   // --- second-generation 16-bit kernel (dcn_tc2.cu) ---
   int version;             // 1: dcn_fwd_tc, 2: dcn_fwd_tc2
-  int tab_span;            // chunks that share one tap-table segment; 0: one segment per k-stage
+  int KH;                  // 32-channel half-chunks per conv group
+  int U;                   // (half-chunk, tap) units per tile = KH*T; a k-stage holds two
+  int ndu;                 // max deform groups touched by one half-chunk
+  int tab_span;            // half-chunks that share one tap-table segment; 0: one segment per k-stage
   int tab_slots;           // ring depth of the tap table
   int tab_slot_blocks;     // (tap, deform group) blocks per ring slot
   int win_h, win_w;        // input window held in shared memory, in pixels (0: none)

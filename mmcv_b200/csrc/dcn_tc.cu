@@ -976,9 +976,55 @@ dcn_weight_tiles(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int
   }
 }
 
+// The same for the second-generation kernel, whose k-stage holds two (32-channel half-chunk,
+// tap) units, half-chunk-major: unit u = hc*T + tap, stage s = units 2s and 2s+1, 64 bytes
+// each of a row.  A unit beyond the last one, and channels beyond the group, are zero.
+template <typename T>
+__global__ void __launch_bounds__(256)
+dcn_weight_tiles2(const T *__restrict__ w, uint8_t *__restrict__ dst, int Cg, int Cog, int Tt,
+                  int BN, int NT, int S, int U, int op_format) {
+  const int blk = blockIdx.x;  // (grp*NT + nt)*S + ks
+  const int ks = blk % S;
+  const int gn = blk / S;
+  const int nt = gn % NT, grp = gn / NT;
+  uint8_t *out = dst + (size_t)blk * BN * 128;
+  const int e_end = min(BN, ((int)blockIdx.y + 1) * 16) * 64;
+#pragma unroll 4
+  for (int e = (int)blockIdx.y * 16 * 64 + threadIdx.x; e < e_end; e += blockDim.x) {
+    const int r = e >> 6, j = e & 63;
+    const int col = nt * BN + r;
+    const int unit = 2 * ks + (j >> 5);
+    const int hc = unit / Tt, tap = unit - hc * Tt;
+    const int ch = hc * 32 + (j & 31);
+    float val = 0.f;
+    if (col < Cog && unit < U && ch < Cg) {
+      const long long co = (long long)grp * Cog + col;
+      val = ld_as_float(w, (co * Cg + ch) * Tt + tap);
+    }
+    const int byte = r * 128 + (((j >> 3) ^ (r & 7)) << 4) + (j & 7) * 2;
+    if (op_format == 0)
+      *reinterpret_cast<__half *>(out + byte) = __float2half_rn(val);
+    else
+      *reinterpret_cast<__nv_bfloat16 *>(out + byte) = __float2bfloat16_rn(val);
+  }
+}
+
 cudaError_t launch_weight_tiles(const Geom &g, const TcPlan &tp, const void *weight, int dtype,
                                 void *wtiles, cudaStream_t s) {
   const dim3 blocks((unsigned)(g.groups * tp.NT * tp.S), (unsigned)((tp.BN + 15) / 16));
+  if (tp.version == 2) {
+    if (dtype == DCN_DTYPE_F32)
+      dcn_weight_tiles2<float><<<blocks, 256, 0, s>>>((const float *)weight, (uint8_t *)wtiles, g.Cg,
+                                                      g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.U, tp.op_format);
+    else if (dtype == DCN_DTYPE_F16)
+      dcn_weight_tiles2<__half><<<blocks, 256, 0, s>>>((const __half *)weight, (uint8_t *)wtiles, g.Cg,
+                                                       g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.U, tp.op_format);
+    else
+      dcn_weight_tiles2<__nv_bfloat16><<<blocks, 256, 0, s>>>(
+          (const __nv_bfloat16 *)weight, (uint8_t *)wtiles, g.Cg, g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.U,
+          tp.op_format);
+    return cudaGetLastError();
+  }
   if (dtype == DCN_DTYPE_F32)
     dcn_weight_tiles<float><<<blocks, 256, 0, s>>>((const float *)weight, (uint8_t *)wtiles, g.Cg,
                                                    g.Cog, g.T, tp.BN, tp.NT, tp.S, tp.op_format);

@@ -21,11 +21,14 @@
 //     the image is always read (0 * Inf = NaN as in the reference,
 //     modulated_deform_conv_cuda_kernel.cuh:100-107).  Two rows per thread are in flight and
 //     the rotation runs across k-stage boundaries.
-//   * optionally the 64-channel slice of the tile's input neighbourhood is brought into shared
-//     memory by one tensor-map copy (cp.async.bulk.tensor, zero fill outside the tensor) per
-//     channel chunk, double-buffered; entries whose 2x2 neighbourhood lies inside that window
-//     are read from shared memory, the others from global memory, through the same generic
-//     loads.
+//   * K is walked in units of (32-channel half-chunk, tap); a k-stage is two consecutive units.
+//     The 32-channel slice of the tile's input neighbourhood (its undeformed footprint plus a
+//     margin) is brought into shared memory by one tensor-map copy (cp.async.bulk.tensor, zero
+//     fill outside the tensor) per half-chunk, double-buffered; entries whose 2x2 neighbourhood
+//     lies inside that window are read from shared memory (64 bytes per pixel; the two units of
+//     a row read their left/right corners in opposite order when needed, so that the eight
+//     lanes of a row never meet in a bank), the others from global memory, through the same
+//     generic loads.
 //
 // MMA issue, weight loader (cp.async.bulk + mbarrier complete_tx) and the accumulator
 // double-buffering in tensor memory are as in dcn_fwd_tc.  Every mbarrier wait is bounded.
@@ -83,21 +86,35 @@ __device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// 16-byte load through a generic address (shared window or global memory).  `tok` is passed
-// through untouched; code that must come after this load's issue takes `tok` as an input.
-__device__ __forceinline__ uint4 ld16_generic(const void *p, uint32_t &tok) {
-  uint4 r;
-  asm volatile("ld.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-               : "l"(p), "r"(tok));
-  asm volatile("" : "+r"(tok));
-  return r;
-}
+// 16-byte loads.  `tok` is passed through untouched; code that must come after a load's issue
+// takes `tok` as an input.
 __device__ __forceinline__ uint4 ld16_global(const void *p, uint32_t &tok) {
   uint4 r;
   asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p), "r"(tok));
+  asm volatile("" : "+r"(tok));
+  return r;
+}
+__device__ __forceinline__ uint4 lds16(uint32_t addr, uint32_t &tok) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "r"(addr), "r"(tok));
+  asm volatile("" : "+r"(tok));
+  return r;
+}
+// One lane reads global memory, another the shared-memory window: the same 16-byte load, in
+// the lane's own state space.
+__device__ __forceinline__ uint4 ld16_either(bool from_global, const void *gp, uint32_t sp, uint32_t &tok) {
+  uint4 r;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %6, 0;\n\t"
+      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t"
+      "@!p ld.shared.v4.u32 {%0, %1, %2, %3}, [%5];\n\t}"
+      : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
+      : "l"(gp), "r"(sp), "r"((uint32_t)from_global), "r"(tok));
   asm volatile("" : "+r"(tok));
   return r;
 }
@@ -122,7 +139,7 @@ struct Smem2 {
   uint8_t *bias_s;
 };
 
-__host__ __device__ inline size_t win_bytes(const TcPlan &tp) { return (size_t)tp.win_h * tp.win_w * 128; }
+__host__ __device__ inline size_t win_bytes(const TcPlan &tp) { return (size_t)tp.win_h * tp.win_w * 64; }  // 32 channels per pixel
 __host__ __device__ inline size_t epi_bytes(const TcPlan &tp) {
   return tp.epi_tma ? (size_t)kEpiWarps * 2 * 32 * 32 * tp.io_bytes : 0;  // per warp: two slabs of 32 channels x 32 pixels
 }
@@ -260,7 +277,7 @@ size_t tc2_smem_bytes(const TcPlan &tp) {
   return s;
 }
 
-template <typename TIO, int MODE, bool kWin>
+template <typename TIO, int MODE, bool kWin, bool kSegStage>
 __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constant__ Tc2Args a) {
   uint8_t *smem = smem_aligned();
   const Geom &g = a.g;
@@ -314,9 +331,11 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
   const long long plane = (long long)g.Ho * g.Wo;
   const int tw_mask = (1 << tp.tw_log2) - 1;
   const int T = g.T;
-  // table segments: one per k-stage (tab_span == 0), or one per run of tab_span chunks (whose
-  // chunks then touch a single deform group)
-  const bool seg_per_stage = tp.tab_span == 0;
+  // K is walked in units of (32-channel half-chunk, tap), half-chunk-major; a k-stage holds two
+  // consecutive units (64 bytes each of the operand row).
+  // table segments: one per k-stage (tab_span == 0: two units, ndu deform groups each), or one
+  // per run of tab_span half-chunks that share their single deform group (one block per tap)
+  constexpr bool seg_per_stage = kSegStage;
   const uint32_t slot_entries = (uint32_t)tp.tab_slot_blocks * kTabStride2;
   const uint32_t Wp = (uint32_t)g.W + 2u;
   const uint32_t Cb = (uint32_t)g.C * 2u;       // bytes of one padded pixel
@@ -487,7 +506,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const uint32_t per_mt = (uint32_t)(g.groups * tp.NT);
       uint32_t sb = 0, pb = 0;
       bool ok = true;
-      // window copies: one per (tile, chunk), issued as soon as its buffer is free; `wq` counts
+      // window copies: one per (tile, 32-channel half-chunk), issued as soon as its buffer is free; `wq` counts
       // them; the loop below polls for the next one between weight copies
       uint32_t w_item = blockIdx.x, wq = 0;
       int w_cc = 0;
@@ -499,10 +518,10 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           const uint32_t wb = wq & 1u;
           mbar_arrive_expect_tx(win_full + 8 * wb, wbytes);
           // coordinates in the padded tensor: (channel, column + 1, row + 1, sample)
-          tma_load_4d(smem_u32(L.win) + wb * wbytes, &a.win_map, t.grp * g.Cg + w_cc * 64,
+          tma_load_4d(smem_u32(L.win) + wb * wbytes, &a.win_map, t.grp * g.Cg + w_cc * 32,
                       win_x0(g, tp, t.wo0) + 1, win_y0(g, tp, t.ho0) + 1, t.n, win_full + 8 * wb);
           ++wq;
-          if (++w_cc == tp.KC) { w_cc = 0; w_item += gridDim.x; }
+          if (++w_cc == tp.KH) { w_cc = 0; w_item += gridDim.x; }
         }
       };
       PhaseTimer pt(a.counters, blockIdx.x == 0);
@@ -562,18 +581,19 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     __syncwarp();
   } else if (warp < kFirstGatherWarp) {
     // ------------------------------ table builders ------------------------------
-    // The (tap, deform group) blocks of all segments form one stream; builder warp b computes
-    // blocks b, b + 2, ...: four rows per thread, the twelve loads of a block in flight together.
+    // The (unit, deform group) blocks of all segments form one stream; builder warp b computes
+    // blocks b, b + 2, ...: four rows per thread.  The twelve loads of a block are in flight
+    // together, and a block is computed only after the loads of the warp's next block have
+    // been issued.
     const int bw = warp - kFirstBuildWarp;
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
     const uint32_t dead_off = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;  // an all-zero 2x2 neighbourhood
     const bool dense_planes = g.off_ps == 1 && g.msk_ps == 1 && g.off_cs == plane && g.msk_cs == plane;
     const int wh = tp.win_h, ww = tp.win_w;
-    const uint32_t tabw_addr = smem_u32(L.tab_w), tabo_addr = smem_u32(L.tab_off);
-    const int span_step = seg_per_stage ? 1 : tp.tab_span;
-    const int seg_taps = seg_per_stage ? 1 : T;
-    uint32_t q = 0, blk_ctr = 0;
+    const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)lane * 8u;
+    const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)lane * 4u;
+    uint32_t q = 0, turn = 0;
     bool ok = true;
     PhaseTimer pt(a.counters, blockIdx.x == 0 && bw == 0 && lane == 0);
 
@@ -599,124 +619,219 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           prefetch_l2(reinterpret_cast<const char *>(ptr) + rl * 128);
       }
     };
+
+    // the block whose loads are in flight (always one of the current tile)
+    uint32_t roh[4], row_[4], rmm[4];
+    bool pend = false, pend_first = false, pend_last = false;
+    uint32_t pend_e = 0, pend_slot = 0, pend_par = 0;
+    int pend_ti = 0, pend_tj = 0;
+    int ho0 = 0, wo0 = 0, wy0 = 0, wx0 = 0;   // current tile
+    // entries of the pending block, then its segment's hand-over if it was this warp's last
+    // block there
+    auto flush = [&]() -> bool {
+      if (!pend) return true;
+      pend = false;
+      if (pend_first) {
+        pt.lap(1);
+        const bool r = mbar_wait2(tab_empty + 8 * pend_slot, pend_par, 9);
+        pt.lap(6);
+        if (!r) return false;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
+        uint32_t eo = dead_off;
+        // this thread's rows: lane, lane + 32, lane + 64, lane + 96
+        const int r = lane + 32 * j;
+        const int ho = ho0 + (r >> tp.tw_log2), wo = wo0 + (r & tw_mask);
+        const float h_im = (float)(ho * g.stride_h - g.pad_h + pend_ti * g.dil_h) + RawOf<TIO>::to_float(roh[j]);
+        const float w_im = (float)(wo * g.stride_w - g.pad_w + pend_tj * g.dil_w) + RawOf<TIO>::to_float(row_[j]);
+        if (ho < g.Ho && wo < g.Wo && h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
+          const float m = msk ? mask_value(g, RawOf<TIO>::to_float(rmm[j])) : 1.f;
+          const float hf = floorf(h_im), wf = floorf(w_im);
+          const float lh = h_im - hf, lw = w_im - wf;
+          const float hh = 1.f - lh, hw = 1.f - lw;
+          wt.x = hh * hw * m; wt.y = hh * lw * m; wt.z = lh * hw * m; wt.w = lh * lw * m;
+          const int hl = (int)hf, wl = (int)wf;
+          // inside the shared-memory window: offset within the window (64 bytes per pixel);
+          // else (flagged) the offset within the padded sample
+          const int wy = hl - wy0, wx = wl - wx0;
+          if (kWin && wy >= 0 && wx >= 0 && wy + 1 < wh && wx + 1 < ww)
+            eo = (uint32_t)(wy * ww + wx) * 64u;
+          else
+            eo = (((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb) | kWinFlag;
+        }
+        const uint32_t e = pend_e + 32u * (uint32_t)j;
+        sts8(tabw_addr + e * 8u, pack_weights2<MODE>(wt.x, wt.y), pack_weights2<MODE>(wt.z, wt.w));
+        sts4(tabo_addr + e * 4u, eo);
+      }
+      if (pend_last) {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tab_full + 8 * pend_slot);
+      }
+      return true;
+    };
+
     prefetch_tile(blockIdx.x);
     for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+      ok = flush();   // (a pending block belongs to the previous tile)
+      if (!ok) break;
       const TileId2 t = decode_item2(item, g, tp);
       prefetch_tile(item + gridDim.x);
-      // this thread's rows: lane, lane + 32, lane + 64, lane + 96
-      int pix[4], hb[4], wb[4];
+      ho0 = t.ho0; wo0 = t.wo0;
+      wy0 = win_y0(g, tp, t.ho0); wx0 = win_x0(g, tp, t.wo0);
+      // pixel of each of this thread's rows (a row beyond the image reads pixel 0; its entry
+      // fails the test above)
+      int pix[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int r = lane + 32 * j;
         const int ho = t.ho0 + (r >> tp.tw_log2), wo = t.wo0 + (r & tw_mask);
-        pix[j] = (ho < g.Ho && wo < g.Wo) ? ho * g.Wo + wo : -1;
-        hb[j] = ho * g.stride_h - g.pad_h;
-        wb[j] = wo * g.stride_w - g.pad_w;
+        pix[j] = (ho < g.Ho && wo < g.Wo) ? ho * g.Wo + wo : 0;
       }
-      const int wy0 = win_y0(g, tp, t.ho0), wx0 = win_x0(g, tp, t.wo0);
       const TIO *offn = off ? off + (long long)t.n * g.off_sn : nullptr;
       const TIO *mskn = msk ? msk + (long long)t.n * g.msk_sn : nullptr;
-      for (int cc = 0; cc < tp.KC && ok; cc += span_step) {
-        const int c0 = t.grp * g.Cg + cc * 64;
-        const int dg_lo = c0 / g.cpdg;
-        const int nd = (min(c0 + 64, (t.grp + 1) * g.Cg) - 1) / g.cpdg - dg_lo + 1;
-        int ti = 0, tj = 0;
-        for (int tap0 = 0; tap0 < T && ok; tap0 += seg_taps, ++q) {
-          const uint32_t slot = q % (uint32_t)RS;
-          // every builder warp waits for the slot, with or without blocks of its own in this
-          // segment: its arrival below must not be counted for the slot's previous use
-          pt.lap(1);
-          ok = mbar_wait2(tab_empty + 8 * slot, ((q / (uint32_t)RS) & 1u) ^ 1u, 9);
-          pt.lap(6);
-          if (!ok) break;
-          for (int tap = tap0; tap < tap0 + seg_taps; ++tap) {
-            for (int d = 0; d < nd; ++d) {
-              const bool mine = (int)blk_ctr == bw;
-              if (++blk_ctr == (uint32_t)kBuildWarps) blk_ctr = 0;
-              if (!mine) continue;
-              const int dgi = dg_lo + d;
-              uint32_t oh[4], ow[4], mm[4];
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                oh[j] = 0; ow[j] = 0; mm[j] = 0;
-                if (pix[j] >= 0) {
-                  if (offn) {
-                    const TIO *p = offn + (long long)pix[j] * g.off_ps + ((long long)dgi * 2 * T + 2 * tap) * g.off_cs;
-                    oh[j] = ldg_raw_ordered(p);
-                    ow[j] = ldg_raw_ordered(p + g.off_cs);
-                  }
-                  if (mskn)
-                    mm[j] = ldg_raw_ordered(mskn + (long long)pix[j] * g.msk_ps + ((long long)dgi * T + tap) * g.msk_cs);
-                }
-              }
-              const uint32_t blk = seg_per_stage ? (uint32_t)d : (uint32_t)tap;
-              const uint32_t e0 = slot * slot_entries + blk * kTabStride2 + (uint32_t)lane;
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
-                uint32_t eo = dead_off;
-                if (pix[j] >= 0) {
-                  const float h_im = (float)(hb[j] + ti * g.dil_h) + RawOf<TIO>::to_float(oh[j]);
-                  const float w_im = (float)(wb[j] + tj * g.dil_w) + RawOf<TIO>::to_float(ow[j]);
-                  if (h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
-                    const float m = mskn ? mask_value(g, RawOf<TIO>::to_float(mm[j])) : 1.f;
-                    const float hf = floorf(h_im), wf = floorf(w_im);
-                    const float lh = h_im - hf, lw = w_im - wf;
-                    const float hh = 1.f - lh, hw = 1.f - lw;
-                    wt.x = hh * hw * m; wt.y = hh * lw * m; wt.z = lh * hw * m; wt.w = lh * lw * m;
-                    const int hl = (int)hf, wl = (int)wf;
-                    // inside the shared-memory window: offset within the window; else (flagged)
-                    // the offset within the padded sample
-                    const int wy = hl - wy0, wx = wl - wx0;
-                    if (kWin && wy >= 0 && wx >= 0 && wy + 1 < wh && wx + 1 < ww)
-                      eo = (uint32_t)(wy * ww + wx) * 128u;
-                    else
-                      eo = (((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb) | kWinFlag;
-                  }
-                }
-                const uint32_t e = e0 + 32u * (uint32_t)j;
-                sts8(tabw_addr + e * 8u, pack_weights2<MODE>(wt.x, wt.y), pack_weights2<MODE>(wt.z, wt.w));
-                sts4(tabo_addr + e * 4u, eo);
-              }
-            }
-            if (++tj == g.kw) { tj = 0; ++ti; }
+      const int nseg = seg_per_stage ? tp.S : tp.KH / tp.tab_span;
+      // running unit (stage segments): half-chunk, tap and the tap's row / column
+      int u_hc = 0, u_tap = 0, u_ti = 0, u_tj = 0;
+      int c_hc = -1, dg_lo = 0, nd = 1;   // deform groups of half-chunk c_hc
+      for (int sg = 0; sg < nseg && ok; ++sg, ++q) {
+        const uint32_t slot = q % (uint32_t)RS;
+        const uint32_t spar = ((q / (uint32_t)RS) & 1u) ^ 1u;
+        // the segment's units: two consecutive (half-chunk, tap) units, or the taps of one run
+        const int n_u = seg_per_stage ? min(2, tp.U - 2 * sg) : T;
+        if (!seg_per_stage) { u_hc = sg * tp.tab_span; u_tap = 0; u_ti = 0; u_tj = 0; }
+        bool first_mine = true;
+        for (int ui = 0; ui < n_u && ok; ++ui) {
+          const int hc = u_hc, tap = u_tap, ti = u_ti, tj = u_tj;
+          // next unit
+          if (++u_tj == g.kw) { u_tj = 0; ++u_ti; }
+          if (++u_tap == T) { u_tap = 0; u_ti = 0; u_tj = 0; ++u_hc; }
+          if (hc != c_hc) {
+            c_hc = hc;
+            const int c0 = t.grp * g.Cg + hc * 32;
+            dg_lo = c0 / g.cpdg;
+            nd = seg_per_stage ? (min(c0 + 32, (t.grp + 1) * g.Cg) - 1) / g.cpdg - dg_lo + 1 : 1;
           }
+          for (int d = 0; d < nd && ok; ++d) {
+            const bool mine = (int)turn == bw;
+            if (++turn == (uint32_t)kBuildWarps) turn = 0;
+            if (!mine) continue;
+            // loads of this block, issued before the pending block is computed
+            uint32_t noh[4], now_[4], nmm[4];
+            const TIO *ob = off ? offn + ((long long)(dg_lo + d) * 2 * T + 2 * tap) * g.off_cs : nullptr;
+            const TIO *mb = msk ? mskn + ((long long)(dg_lo + d) * T + tap) * g.msk_cs : nullptr;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              noh[j] = 0; now_[j] = 0; nmm[j] = 0;
+              if (off) {
+                const TIO *pp = ob + (long long)pix[j] * g.off_ps;
+                noh[j] = ldg_raw_ordered(pp);
+                now_[j] = ldg_raw_ordered(pp + g.off_cs);
+              }
+              if (msk) nmm[j] = ldg_raw_ordered(mb + (long long)pix[j] * g.msk_ps);
+            }
+            ok = flush();
+            if (!ok) break;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { roh[j] = noh[j]; row_[j] = now_[j]; rmm[j] = nmm[j]; }
+            pend = true;
+            pend_first = first_mine;
+            pend_last = false;
+            first_mine = false;
+            pend_slot = slot;
+            pend_par = spar;
+            pend_ti = ti;
+            pend_tj = tj;
+            pend_e = slot * slot_entries +
+                     (seg_per_stage ? (uint32_t)(ui * tp.ndu + d) : (uint32_t)tap) * kTabStride2;
+          }
+        }
+        if (!ok) break;
+        if (first_mine) {
+          // none of the segment's blocks was this warp's: it still waits for the slot and
+          // arrives, so that no arrival is counted for the slot's previous use
+          ok = mbar_wait2(tab_empty + 8 * slot, spar, 9);
+          if (!ok) break;
           __syncwarp();
           if (lane == 0) mbar_arrive(tab_full + 8 * slot);
+        } else {
+          pend_last = true;  // the pending block is this warp's last one of the segment
         }
       }
     }
+    if (ok) ok = flush();
     if (!ok) *abort_s = 1;
   } else {
     // ------------------------------ gather ------------------------------
     const int gw = warp - kFirstGatherWarp;
     const int sub = lane >> 3;  // row within the warp's group of four
-    const int v = lane & 7;     // 16-byte vector (8 channels) of the 128-byte row
+    const int v = lane & 7;     // 16-byte vector of the 128-byte row
+    const int usel = v >> 2;    // which of the stage's two units this lane gathers
+    const int cv = v & 3;       // 8-channel vector within the unit
     const int row0 = gw * 4 + sub;
     const uint32_t a_base = smem_u32(L.a) + (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
     const char *xpad = reinterpret_cast<const char *>(a.xpad);
     const uint32_t wbytes = (uint32_t)win_bytes(tp);
-    const uint32_t win_rb = (uint32_t)tp.win_w * 128u;
-    const char *win_gen = reinterpret_cast<const char *>(L.win) + v * 16;  // generic address
+    const uint32_t win_rb = (uint32_t)tp.win_w * 64u;
+    const uint32_t win_s = smem_u32(L.win) + (uint32_t)cv * 16u;
     const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)row0 * 8u;
     const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)row0 * 4u;
+    const int KH = tp.KH;
+    const int nseg = seg_per_stage ? tp.S : KH / tp.tab_span;   // table segments per tile
 
-    // position: the k-stage (item, cc, tap) whose loads are issued next
+    const uint32_t span = seg_per_stage ? 1u : (uint32_t)tp.tab_span;
+    // position: the k-stage (item, s) whose loads are issued next; its unit A = 2 s is
+    // (half-chunk hcA, tap tapA); in run mode hcA is half-chunk inrunA of run runA
     uint32_t item = blockIdx.x;
-    int cc = 0, tap = 0;
-    uint32_t q = 0, wq = 0, sa = 0, pa = 0;
-    // per chunk
-    const char *gbase = nullptr;   // sample + channel bytes of this thread's vector
-    uint32_t eblk = 0;             // table block of this thread's deform group (stage segments)
+    int s = 0, hcA = 0, tapA = 0;
+    uint32_t runA = 0, inrunA = 0;
+    uint32_t sa = 0, pa = 0;
+    // running counts over the tiles of this block: window of (tile, half-chunk 0), table
+    // segment of (tile, run 0); table ring position of the current stage (stage segments)
+    uint32_t win_base = 0, seg_base = 0, slotS = 0, phS = 0;
+    // windows / run segments: next one to wait for, next one to hand back
+    uint32_t win_acq = 0, win_rel = 0, seg_acq = 0, seg_rel = 0;
+    // this lane's unit of the stage; the values below change with its half-chunk only
+    int my_hc = -2;
+    const char *gbase = nullptr;   // sample + channel bytes of this lane's vector (global)
+    uint32_t wbase = 0;            // window buffer of the half-chunk + this lane's 16 bytes (shared address)
+    uint32_t e_fixed = 0;          // table entry of row0 without the stage's (or tap's) part
+    uint32_t e0 = 0;               // table entry of pass 0
     bool zero_vec = false;
-    auto enter_chunk = [&]() {
+    int grp = 0;
+    const char *sbase = nullptr;
+    auto enter_item = [&]() {
       const TileId2 t = decode_item2(item, g, tp);
-      const int c0 = t.grp * g.Cg + cc * 64;
-      // the last chunk of a group may be partly beyond its channels: those vectors are zero
-      zero_vec = cc * 64 + v * 8 >= g.Cg;
-      const int c = zero_vec ? c0 : c0 + v * 8;
-      eblk = seg_per_stage ? (uint32_t)(c / g.cpdg - c0 / g.cpdg) * kTabStride2 : 0u;
-      gbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb) + (unsigned long long)c * 2ull;
+      grp = t.grp;
+      sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
+      my_hc = -2;
+    };
+    // Per-lane values of the stage at the current position.
+    auto enter_stage = [&]() {
+      int hc = hcA, tap = tapA;
+      uint32_t run = runA;
+      if (usel) {
+        if (++tap == T) {
+          tap = 0; ++hc;
+          if (inrunA + 1u == span) ++run;
+        }
+      }
+      const int key = 2 * s + usel < tp.U ? hc : -1;
+      if (key != my_hc) {
+        my_hc = key;
+        const int cg = hc * 32 + cv * 8;           // channel within the conv group
+        zero_vec = key < 0 || cg >= g.Cg;
+        const int c0 = grp * g.Cg + hc * 32;
+        const int c = zero_vec ? grp * g.Cg : c0 + cv * 8;
+        gbase = sbase + (unsigned long long)c * 2ull;
+        wbase = win_s + ((win_base + (uint32_t)hc) & 1u) * wbytes;
+        if (seg_per_stage)
+          e_fixed = ((uint32_t)(usel * tp.ndu) + (zero_vec ? 0u : (uint32_t)(c / g.cpdg - c0 / g.cpdg))) * kTabStride2;
+        else
+          e_fixed = ((seg_base + run) & 1u) * slot_entries;
+      }
+      e0 = seg_per_stage ? slotS * slot_entries + e_fixed : e_fixed + (uint32_t)tap * kTabStride2;
     };
 
     uint4 qd[2][4];
@@ -726,98 +841,150 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
     // loads of pass p of the k-stage at the current position into register set p
     auto issue = [&](int p) {
-      const uint32_t e = (q % (uint32_t)RS) * slot_entries + eblk +
-                         (seg_per_stage ? 0u : (uint32_t)tap * kTabStride2) + (uint32_t)(p * kRowsPerPass);
-      wq2[p] = lds8(tabw_addr + e * 8u);
-      const uint32_t o = lds4(tabo_addr + e * 4u);
+      uint2 w = make_uint2(0u, 0u);
+      uint32_t o = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;   // an all-zero neighbourhood
+      if (!zero_vec) {
+        const uint32_t e = e0 + (uint32_t)(p * kRowsPerPass);
+        w = lds8(tabw_addr + e * 8u);
+        o = lds4(tabo_addr + e * 4u);
+      }
+      const uint32_t ob = o & ~kWinFlag;
       if constexpr (kWin) {
+        // The two units of a row read 64-byte slots; the lanes of unit 0 start with the
+        // even slot of their left/right pair and those of unit 1 with the odd one, so the
+        // eight lanes of a row always cover all 32 banks.  (The window's row pitch is an even
+        // number of slots: the bottom corners repeat the top ones' parity.)
         const bool from_global = (o & kWinFlag) != 0u;
-        const char *base = (from_global ? gbase : win_gen + (wq & 1u) * wbytes) + (o & ~kWinFlag);
-        const uint32_t dp = from_global ? Cb : 128u, dr = from_global ? Rb : win_rb;
-        qd[p][0] = ld16_generic(base, tok);
-        qd[p][1] = ld16_generic(base + dp, tok);
-        qd[p][2] = ld16_generic(base + dr, tok);
-        qd[p][3] = ld16_generic(base + dr + dp, tok);
+        const bool swap = (((ob >> 6) & 1u) != (uint32_t)usel) && !from_global;
+        if (swap) w = make_uint2(__byte_perm(w.x, 0u, 0x1032), __byte_perm(w.y, 0u, 0x1032));
+        const uint32_t sp = wbase + ob;
+        const uint32_t s1 = swap ? sp + 64u : sp, s2 = swap ? sp : sp + 64u;
+        if (!__any_sync(0xffffffffu, from_global)) {
+          // the usual case: every lane of the warp reads the window
+          qd[p][0] = lds16(s1, tok);
+          qd[p][1] = lds16(s2, tok);
+          qd[p][2] = lds16(s1 + win_rb, tok);
+          qd[p][3] = lds16(s2 + win_rb, tok);
+        } else {
+          const char *base = gbase + ob;
+          qd[p][0] = ld16_either(from_global, base, s1, tok);
+          qd[p][1] = ld16_either(from_global, base + Cb, s2, tok);
+          qd[p][2] = ld16_either(from_global, base + Rb, s1 + win_rb, tok);
+          qd[p][3] = ld16_either(from_global, base + Rb + Cb, s2 + win_rb, tok);
+        }
       } else {
-        const char *base = gbase + (o & ~kWinFlag);
+        const char *base = gbase + ob;
         qd[p][0] = ld16_global(base, tok);
         qd[p][1] = ld16_global(base + Cb, tok);
         qd[p][2] = ld16_global(base + Rb, tok);
         qd[p][3] = ld16_global(base + Rb + Cb, tok);
       }
+      wq2[p] = w;
     };
-    auto blend_store = [&](uint32_t stage_addr, bool zv, int p) {
+    auto blend_store = [&](uint32_t stage_addr, int p) {
       uint4 w = table_weights<MODE>(wq2[p]);
       w.x |= tok;  // tok is 0: pins the blend behind the loads issued before it
       uint4 r;
       if constexpr (MODE == kModeBf16) r = blend8_bf16(w, qd[p][0], qd[p][1], qd[p][2], qd[p][3]);
       else r = blend8_f16(w, qd[p][0], qd[p][1], qd[p][2], qd[p][3]);
-      if (zv) r = make_uint4(0u, 0u, 0u, 0u);
       sts16(stage_addr + (uint32_t)(p * kRowsPerPass * 128), r);
     };
-    // what the first loads of the k-stage at the current position need: its table segment
-    // and, with a new chunk, the chunk's window
+    // What the loads of the k-stage at the current position need: its table segment(s) and
+    // the windows of both its units (unit B's are the later ones).
     auto acquire = [&]() -> bool {
-      bool r = true;
-      if (tap == 0) {
-        enter_chunk();
-        if (kWin) r = mbar_wait2(win_full + 8 * (wq & 1u), (wq >> 1) & 1u, 13);
+      uint32_t hcB = (uint32_t)hcA, runB = runA;
+      if (tapA + 1 == T && 2 * s + 1 < tp.U) {
+        ++hcB;
+        if (inrunA + 1u == span) ++runB;
       }
-      const bool seg_first = seg_per_stage || (tap == 0 && cc % tp.tab_span == 0);
-      if (r && seg_first) r = mbar_wait2(tab_full + 8 * (q % (uint32_t)RS), (q / (uint32_t)RS) & 1u, 12);
-      return r;
+      if (seg_per_stage) {
+        if (!mbar_wait2(tab_full + 8 * slotS, phS, 12)) return false;
+      } else {
+        while (seg_acq <= seg_base + runB) {
+          if (!mbar_wait2(tab_full + 8 * (seg_acq & 1u), (seg_acq >> 1) & 1u, 12)) return false;
+          ++seg_acq;
+        }
+      }
+      if (kWin) {
+        while (win_acq <= win_base + hcB) {
+          if (!mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13)) return false;
+          ++win_acq;
+        }
+      }
+      return true;
     };
 
     bool valid = item < items;
     if (valid) {
+      enter_item();
       ok = acquire();
       pt.lap(2);
-      if (ok) issue(0);
+      if (ok) { enter_stage(); issue(0); }
     }
     while (valid && ok) {
 #pragma unroll
       for (int p = 1; p < kPasses2; ++p) issue(p);
-      // every read of the stage's table entries has been issued: hand the slot back with the
-      // segment's last stage
-      const bool chunk_last = tap == T - 1;
-      const bool seg_last = seg_per_stage || (chunk_last && (cc % tp.tab_span == tp.tab_span - 1));
-      if (seg_last) {
+      // Every read of the finishing stage's table entries has been issued.
+      const uint32_t cur_sa = sa | (pa << 8);   // ring slot and phase of the finishing stage
+      if (seg_per_stage) {
+        // its segment goes back to the builders
         __syncwarp();
-        if (lane == 0) mbar_arrive(tab_empty + 8 * (q % (uint32_t)RS));
+        if (lane == 0) mbar_arrive(tab_empty + 8 * slotS);
+        if (++slotS == (uint32_t)RS) { slotS = 0; phS ^= 1u; }
       }
-      // remember the finishing stage, move the position to the next one
-      const uint32_t cur_addr = a_base + sa * (uint32_t)kTileBytes;
-      const uint32_t cur_full = full_a + 8 * sa, cur_empty = empty_a + 8 * sa, cur_par = pa ^ 1u;
-      const uint32_t cur_wbuf = wq & 1u;
-      const bool cur_zero = zero_vec;
+      // move the position to the next stage
       if (++sa == (uint32_t)A) { sa = 0; pa ^= 1u; }
-      if (seg_last) ++q;
-      if (++tap == T) {
-        tap = 0;
-        ++wq;
-        if (++cc == tp.KC) { cc = 0; item += gridDim.x; }
+      tapA += 2;
+      while (tapA >= T) {
+        tapA -= T; ++hcA;
+        if (++inrunA == span) { inrunA = 0; ++runA; }
       }
-      valid = item < items;
+      if (++s == tp.S) {
+        s = 0; hcA = 0; tapA = 0; runA = 0; inrunA = 0;
+        win_base += (uint32_t)KH;
+        seg_base += (uint32_t)nseg;
+        item += gridDim.x;
+        valid = item < items;
+        if (valid) enter_item();
+      }
+      if (!seg_per_stage) {
+        // run segments before the next stage's first unit go back to the builders
+        const uint32_t seg_keep = valid ? seg_base + runA : seg_acq;
+        if (seg_rel < seg_keep) {
+          __syncwarp();
+          if (lane == 0)
+            for (uint32_t i = seg_rel; i < seg_keep; ++i) mbar_arrive(tab_empty + 8 * (i & 1u));
+          seg_rel = seg_keep;
+        }
+      }
       pt.lap(4);
-      ok = mbar_wait2(cur_empty, cur_par, 8);
+      ok = mbar_wait2(empty_a + 8 * (cur_sa & 0xffu), (cur_sa >> 8) ^ 1u, 8);
       pt.lap(3);
       if (!ok) break;
-      blend_store(cur_addr, cur_zero, 0);
+      const uint32_t cur_addr = a_base + (cur_sa & 0xffu) * (uint32_t)kTileBytes;
+      blend_store(cur_addr, 0);
       if (valid) {
         pt.lap(4);
         ok = acquire();
         pt.lap(2);
         if (!ok) break;
+        enter_stage();
         issue(0);
       }
 #pragma unroll
-      for (int p = 1; p < kPasses2; ++p) blend_store(cur_addr, cur_zero, p);
+      for (int p = 1; p < kPasses2; ++p) blend_store(cur_addr, p);
       fence_proxy_async_smem();
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(cur_full);
-        // all loads from the finished chunk's window have returned (their values were consumed)
-        if (kWin && chunk_last) mbar_arrive(win_empty + 8 * cur_wbuf);
+      if (lane == 0) mbar_arrive(full_a + 8 * (cur_sa & 0xffu));
+      if (kWin) {
+        // all loads from the windows before the next stage's first unit have returned (their
+        // values were consumed above): those windows go back to the loader
+        const uint32_t win_keep = valid ? win_base + (uint32_t)hcA : win_acq;
+        if (win_rel < win_keep) {
+          if (lane == 0)
+            for (uint32_t i = win_rel; i < win_keep; ++i) mbar_arrive(win_empty + 8 * (i & 1u));
+          win_rel = win_keep;
+        }
       }
     }
     if (!ok) *abort_s = 1;
@@ -861,9 +1028,9 @@ EncodeTiledFn encode_fn() {
   return f;
 }
 
-template <typename TIO, int MODE, bool kWin>
+template <typename TIO, int MODE, bool kWin, bool kSegStage>
 cudaError_t launch_one2(const Tc2Args &a, const TcPlan &tp, cudaStream_t s) {
-  auto kern = dcn_fwd_tc2<TIO, MODE, kWin>;
+  auto kern = dcn_fwd_tc2<TIO, MODE, kWin, kSegStage>;
   static std::atomic<unsigned long long> done_mask{0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -921,7 +1088,7 @@ cudaError_t launch_tc2(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype
     const cuuint64_t dims[4] = {(cuuint64_t)g.C, (cuuint64_t)g.W + 2, (cuuint64_t)g.H + 2, (cuuint64_t)g.N};
     const cuuint64_t strides[3] = {(cuuint64_t)g.C * 2, (cuuint64_t)(g.W + 2) * g.C * 2,
                                    (cuuint64_t)(g.H + 2) * (g.W + 2) * g.C * 2};
-    const cuuint32_t box[4] = {64, (cuuint32_t)tp.win_w, (cuuint32_t)tp.win_h, 1};
+    const cuuint32_t box[4] = {32, (cuuint32_t)tp.win_w, (cuuint32_t)tp.win_h, 1};
     const cuuint32_t estr[4] = {1, 1, 1, 1};
     if (enc(&a.win_map, in_type, 4, const_cast<void *>(xpad), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -947,13 +1114,16 @@ cudaError_t launch_tc2(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
-  const bool win = tp.win_h > 0;
-  if (dtype == DCN_DTYPE_F32)
-    return win ? launch_one2<float, kModeBf16, true>(a, tp, s) : launch_one2<float, kModeBf16, false>(a, tp, s);
-  if (dtype == DCN_DTYPE_F16)
-    return win ? launch_one2<__half, kModeF16, true>(a, tp, s) : launch_one2<__half, kModeF16, false>(a, tp, s);
-  return win ? launch_one2<__nv_bfloat16, kModeBf16, true>(a, tp, s)
-             : launch_one2<__nv_bfloat16, kModeBf16, false>(a, tp, s);
+  const bool win = tp.win_h > 0, seg_stage = tp.tab_span == 0;
+#define DCN_TC2_LAUNCH(TIO, MODE)                                                              \
+  (win ? (seg_stage ? launch_one2<TIO, MODE, true, true>(a, tp, s)                             \
+                    : launch_one2<TIO, MODE, true, false>(a, tp, s))                           \
+       : (seg_stage ? launch_one2<TIO, MODE, false, true>(a, tp, s)                            \
+                    : launch_one2<TIO, MODE, false, false>(a, tp, s)))
+  if (dtype == DCN_DTYPE_F32) return DCN_TC2_LAUNCH(float, kModeBf16);
+  if (dtype == DCN_DTYPE_F16) return DCN_TC2_LAUNCH(__half, kModeF16);
+  return DCN_TC2_LAUNCH(__nv_bfloat16, kModeBf16);
+#undef DCN_TC2_LAUNCH
 }
 
 }  // namespace dcn

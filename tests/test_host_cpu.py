@@ -69,10 +69,11 @@ def test_plan_routes_and_sizes():
     assert info.table_span == 0 and info.table_slots >= 4
     assert info.operand_stages >= 2 and info.weight_stages == 2
     rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
-    # the four chunks of a tile share their deform group: one table segment per tile, two slots
-    assert rc == 0 and info.kernel_version == 2 and (info.table_span, info.table_slots) == (4, 2)
+    # the eight 32-channel half-chunks of a tile share their deform group: one table segment
+    # per tile, two slots
+    assert rc == 0 and info.kernel_version == 2 and (info.table_span, info.table_slots) == (8, 2)
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
-    assert rc == 0 and (info.table_span, info.table_slots) == (2, 2)   # 128 channels per deform group
+    assert rc == 0 and (info.table_span, info.table_slots) == (4, 2)   # 128 channels per deform group
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
