@@ -26,6 +26,9 @@ import torch  # noqa: E402
 
 WORKLOADS = {
     # name: N, C, H, W, Co, k, stride, pad, dil, groups, dg, offset sigma, mask, bias, int_frac, mask sigma
+    'c1': dict(N=2, C=64, H=56, W=56, Co=64, k=3, s=1, p=1, d=1, g=1, dg=1, sigma=2.0,
+               mask=True, bias=True, int_frac=0.0, msigma=1.0,
+               desc='DCNv2 N=2 C=64 56x56 3x3 s1 p1 dg=1 bias'),
     'c5': dict(N=256, C=256, H=128, W=128, Co=256, k=3, s=1, p=1, d=1, g=1, dg=8, sigma=2.0,
                mask=True, bias=True, int_frac=0.0, msigma=1.0,
                desc='DCNv2 N=256 C=256 128x128 3x3 s1 p1 dg=8 bias'),
@@ -186,6 +189,102 @@ def cpu_reference_sample(wl, seconds_budget=20.0, max_reps=3):
                 seconds_per_call=best, pixels_per_s=n * Ho * Wo / best)
 
 
+
+def abi_params(_lib, wl, n, x, off, msk, w, b, out, dtype_name, fp32_math, device_index):
+    """DcnFwdParams of one layer call (the struct the public API fills)."""
+    p = _lib.DcnFwdParams()
+    p.input, p.offset = x.data_ptr(), off.data_ptr()
+    p.mask = msk.data_ptr() if msk is not None else None
+    p.weight, p.bias = w.data_ptr(), (b.data_ptr() if b is not None else None)
+    p.output = out.data_ptr()
+    if dtype_name == 'bf16':
+        p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
+    else:
+        p.dtype = _lib.DTYPE_F32
+        p.math_mode = _lib.MATH_TF32X3 if fp32_math == 'tf32x3' else _lib.MATH_FFMA
+    p.N, p.C, p.H, p.W, p.Co = n, wl['C'], wl['H'], wl['W'], wl['Co']
+    p.kh = p.kw = wl['k']
+    p.stride_h = p.stride_w = wl['s']
+    p.pad_h = p.pad_w = wl['p']
+    p.dil_h = p.dil_w = wl['d']
+    p.groups, p.deform_groups = wl['g'], wl['dg']
+    for i, s in enumerate(x.stride()):
+        p.in_stride[i] = s
+    p.device = device_index
+    return p
+
+
+def main_kernel_name(info):
+    if info.path == 1:
+        return 'dcn_fwd_tc2' if info.kernel_version == 2 else 'dcn_fwd_tc'
+    return 'dcn_fwd_simt_tiled' if info.path == 2 else 'dcn_fwd_simt_direct'
+
+
+def oracle_check(wl, x, off, msk, w, b, y, samples, dtype_name):
+    """Compares samples `samples` of the device result y with the CPU checker (the compiled
+    reference when present, else the C restatement) on the same inputs; bf16 results are
+    checked against fp32 arithmetic on the bf16-rounded inputs.  Bounds: fp32
+    max|d| <= 1e-4 max|ref| + 1e-5, bf16 relative L2 <= 2e-2."""
+    import oracle
+    idx = torch.tensor(sorted(set(samples)), device=x.device)
+    f = lambda t: None if t is None else t.index_select(0, idx).float().cpu()
+    ref = oracle.best_forward(f(x), f(off), f(msk), w.float().cpu(), None if b is None else b.float().cpu(),
+                              wl['s'], wl['p'], wl['d'], wl['g'], wl['dg'])
+    got = y.index_select(0, idx).float().cpu()
+    if dtype_name == 'bf16':
+        err = ((got - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+        return err <= 2e-2, err
+    err = (got - ref).abs().max().item()
+    return err <= 1e-4 * ref.abs().max().item() + 1e-5, err
+
+
+def measure_config(_lib, lib, name, dtype_name, fp32_math, dev, peaks, tf32_peak, reps=10):
+    """One single-layer configuration at full size on one GPU: device time of the whole call
+    and of its main kernel (median of `reps` calls after 3 warm-ups), roofline fraction of the
+    layer, and a checker comparison of two samples."""
+    wl = WORKLOADS[name]
+    dtype = torch.bfloat16 if dtype_name == 'bf16' else torch.float32
+    esize = 2 if dtype_name == 'bf16' else 4
+    n = wl['N']
+    x, off, msk, w, b = make_inputs(wl, 0, n, dev, dtype)
+    fl, by, Ho, Wo = flops_and_bytes(wl, n, esize)
+    out = torch.empty(n, wl['Co'], Ho, Wo, device=dev, dtype=dtype)
+    p = abi_params(_lib, wl, n, x, off, msk, w, b, out, dtype_name, fp32_math, dev.index or 0)
+    info = _lib.DcnPlanInfo()
+    _lib.check(lib.dcn_fwd_plan(ctypes.byref(p), ctypes.byref(info)))
+    ws = torch.empty(max(info.workspace_bytes, 256), dtype=torch.uint8, device=dev)
+    sptr = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    buf = (ctypes.c_float * 3)()
+    steps, mains = [], []
+    for i in range(3 + reps):
+        _lib.check(lib.dcn_fwd_profiled(ctypes.byref(p), ctypes.c_void_p(ws.data_ptr()), ws.numel(), sptr, buf))
+        if i >= 3:
+            steps.append(buf[0] + buf[1] + buf[2])
+            mains.append(buf[2])
+    stat = ctypes.c_int32(-1)
+    _lib.check(lib.dcn_read_status(ctypes.c_void_p(ws.data_ptr()), sptr, ctypes.byref(stat)))
+    steps.sort(); mains.sort()
+    ms, main_ms = steps[len(steps) // 2], mains[len(mains) // 2]
+    hbm = peaks.get('hbm_gbs', 6650.0)
+    if dtype_name == 'bf16':
+        peak, peak_name = peaks.get('bf16_tflops', 1590.0), 'bf16 tensor peak (MEASURED_PEAKS.json, burst)'
+    elif info.path == 1:
+        peak, peak_name = tf32_peak / 3.0, f'TF32 matmul measured in this run ({tf32_peak:.0f} TFLOP/s) / 3 products'
+    else:
+        peak, peak_name = 148 * 128 * 2 * 1.965e9 / 1e12, 'nominal FFMA rate (148 SMs x 128 lanes x 2 x 1.965 GHz)'
+    roof_ms = max(fl / (peak * 1e12), by / (hbm * 1e9)) * 1e3
+    ok, err = oracle_check(wl, x, off, msk, w, b, out, [0, n - 1], dtype_name)
+    return dict(workload=name + ': ' + wl['desc'], dtype=dtype_name,
+                math=('bf16' if dtype_name == 'bf16' else fp32_math), kernel=main_kernel_name(info),
+                ms_per_step=ms, main_kernel_ms=main_ms, tflops=fl / (ms * 1e-3) / 1e12,
+                output_pixels_per_s=n * Ho * Wo / (ms * 1e-3),
+                roofline=dict(bound='tensor' if fl / (peak * 1e12) >= by / (hbm * 1e9) else 'hbm',
+                              layer_ms=roof_ms, frac=roof_ms / ms, frac_main_kernel=roof_ms / main_ms,
+                              peak=peak, peak_name=peak_name, hbm_gbs=hbm),
+                parity_ok=bool(ok and stat.value == 0), parity_err=err,
+                parity_samples=[0, n - 1], launches_per_step=info.launches)
+
+
 C4_LAYERS = [  # (count, C, H, W): the 13 deformable 3x3 convs of ResNet-50-DCNv2 stages 3-5
     (4, 128, 168, 100), (6, 256, 84, 50), (3, 512, 42, 25)]
 C4_BATCH = 16
@@ -203,14 +302,16 @@ def c4_work(n):
     return fl, by
 
 
-def run_c4(args, rank, world, local):
-    """13-layer stack through ModulatedDeformConv2dPack, bf16, N=16 (batch-sharded)."""
+def run_c4(args, rank, world, local, dist_ready=False, emit=True):
+    """13-layer stack through ModulatedDeformConv2dPack, bf16, N=16 (batch-sharded).  Returns the
+    result line on rank 0 (and prints it when `emit`)."""
     import torch.distributed as dist
     from mmcv_b200.ops import ModulatedDeformConv2dPack
+    from mmcv_b200.ops import modulated_deform_conv as mdc
     from mmcv_b200.shard import batch_shard
     torch.cuda.set_device(local)
     dev = torch.device('cuda', local)
-    if world > 1:
+    if world > 1 and not dist_ready:
         os.environ.setdefault('MASTER_ADDR', '127.0.0.1')
         dist.init_process_group('nccl', device_id=dev)
     n_total = args.batch or C4_BATCH
@@ -263,6 +364,26 @@ def run_c4(args, rank, world, local):
         torch.cuda.synchronize(dev)
         per_kind[f'C{C}_{H}x{W}'] = a.elapsed_time(b) / 5
         idx += cnt
+    # parity, one layer of each kind, sample 0: (i) the offset branch against a plain fp32
+    # convolution on the same bf16 inputs and weights; (ii) the layer's output against the CPU
+    # checker fed the branch's own (bf16) offsets and mask, which isolates the deformable kernel
+    parity, idx = {}, 0
+    import oracle
+    import torch.nn.functional as F
+    for cnt, C, H, W in C4_LAYERS:
+        m, x1 = layers[idx], inputs[idx][:1]
+        with torch.no_grad():
+            y1 = m(x1)
+            br = mdc.branch_conv(mdc.shared_layout(x1), m.conv_offset, torch.bfloat16).float()
+            br_ref = F.conv2d(x1.float(), m.conv_offset.weight.float(), m.conv_offset.bias.float(), padding=1)
+            e_br = ((br - br_ref).norm() / br_ref.norm().clamp_min(1e-30)).item()
+            br16 = br.to(torch.bfloat16).float()
+            off1, msk1 = br16[:, :18].cpu(), torch.sigmoid(br16[:, 18:]).to(torch.bfloat16).float().cpu()
+            ref = oracle.best_forward(x1.float().cpu(), off1, msk1, m.weight.float().cpu(),
+                                      m.bias.float().cpu(), 1, 1, 1, 1, 1)
+            e_y = ((y1.float().cpu() - ref).norm() / ref.norm().clamp_min(1e-30)).item()
+        parity[f'C{C}_{H}x{W}'] = dict(branch_rel_l2=e_br, layer_rel_l2=e_y, ok=bool(e_br <= 2e-2 and e_y <= 2e-2))
+        idx += cnt
     # end to end: host inputs in, last layer's output out, every step
     hin = [x.cpu().pin_memory() for x in inputs]
     hout = torch.empty(inputs[-1].shape, dtype=torch.bfloat16).pin_memory()
@@ -274,8 +395,6 @@ def run_c4(args, rank, world, local):
                 y = m(hx.to(dev, non_blocking=True))
             hout.copy_(y, non_blocking=True)
 
-    if args.dtype == 'fp32':
-        _ext.set_fp32_math(args.fp32_math)
     e2e_step()
     barrier()
     f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -308,14 +427,14 @@ def run_c4(args, rank, world, local):
             steps=args.steps, warmup=args.warmup, ms_per_step=ms, higher_is_better=True,
             scaling='strong', vs_baseline=None, dtype='bf16', data='synthetic',
             config=dict(workload='c4: 13 ModulatedDeformConv2dPack layers (ResNet-50-DCNv2 stages '
-                                 '3-5), N=16, bf16, offset branch = library convolution on the shared channels-last input',
+                                 '3-5), N=16, bf16, offset branch = ' + mdc.OFFSET_BRANCH + ' convolution on the shared channels-last input',
                         global_batch=n_total, parallelism=f'batch-shard x{world}, no collective',
                         l2='layer inputs 53-107 MB each, 13 distinct tensors per step (> L2)',
                         frozen_weights=bool(args.frozen_weights)),
             layer_roofline=dict(ms=roof * 1e3, frac=roof * 1e3 / ms if world == 1 else None,
                                 flops=fl_r, note='sum over the 26 launches of max(FLOPs at bf16 '
                                                  'peak, compulsory bytes at HBM bandwidth)'),
-            per_layer_ms=per_kind,
+            per_layer_ms=per_kind, parity=parity, parity_ok=all(v['ok'] for v in parity.values()),
             roofline=dict(bound='tensor', achieved=fl_r / (ms * 1e-3) / 1e12, peak=peak_tf,
                           unit='TFLOP/s', frac=fl_r / (ms * 1e-3) / 1e12 / peak_tf, traffic=None,
                           kernel='dcn_fwd_tc_bf16 (whole stack incl. layout copies, the offset-branch convolutions and weight tiling)'),
@@ -323,11 +442,15 @@ def run_c4(args, rank, world, local):
                      h2d_bytes_per_step=sum(h.numel() * 2 for h in hin),
                      d2h_bytes_per_step=hout.numel() * 2, ms_per_step=e2e_ms,
                      api='mmcv_b200.ops.ModulatedDeformConv2dPack'),
-            gpu_launches=args.steps * 13 * (2 if args.frozen_weights else 3), clocks=clocks)
-        print(json.dumps(line), flush=True)
-    if world > 1:
+            gpu_launches=args.steps * 13 * (3 if args.frozen_weights else 4), clocks=clocks)
+        if emit:
+            print(json.dumps(line), flush=True)
+    else:
+        line = None
+    if world > 1 and not dist_ready:
         dist.barrier()
         dist.destroy_process_group()
+    return line
 
 
 def run_backward(args, wl):
@@ -445,6 +568,10 @@ def main():
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--no-per-config', action='store_true',
+                    help='skip the per-configuration table (c1-c4) that the default c5 run appends')
+    ap.add_argument('--no-shard-check', action='store_true',
+                    help='skip the checker comparison and the NCCL-gathered checksums of the shards')
     ap.add_argument('--backward', action='store_true',
                     help='time forward + backward through autograd instead of the forward')
     ap.add_argument('--frozen-weights', action='store_true',
@@ -511,29 +638,7 @@ def main():
     st, pd, dl = (wl['s'],) * 2, (wl['p'],) * 2, (wl['d'],) * 2
 
     # C-ABI parameters for the device-resident measurement (same call the public API makes)
-    def params():
-        p = _lib.DcnFwdParams()
-        p.input, p.offset = x.data_ptr(), off.data_ptr()
-        p.mask = msk.data_ptr() if msk is not None else None
-        p.weight, p.bias = w.data_ptr(), (b.data_ptr() if b is not None else None)
-        p.output = out.data_ptr()
-        if args.dtype == 'bf16':
-            p.dtype, p.math_mode = _lib.DTYPE_BF16, _lib.MATH_AUTO
-        else:
-            p.dtype = _lib.DTYPE_F32
-            p.math_mode = _lib.MATH_TF32X3 if args.fp32_math == 'tf32x3' else _lib.MATH_FFMA
-        p.N, p.C, p.H, p.W, p.Co = n, wl['C'], wl['H'], wl['W'], wl['Co']
-        p.kh = p.kw = wl['k']
-        p.stride_h = p.stride_w = wl['s']
-        p.pad_h = p.pad_w = wl['p']
-        p.dil_h = p.dil_w = wl['d']
-        p.groups, p.deform_groups = wl['g'], wl['dg']
-        for i, s in enumerate(x.stride()):
-            p.in_stride[i] = s
-        p.device = local
-        return p
-
-    p = params()
+    p = abi_params(_lib, wl, n, x, off, msk, w, b, out, args.dtype, args.fp32_math, local)
     info = _lib.DcnPlanInfo()
     _lib.check(lib.dcn_fwd_plan(ctypes.byref(p), ctypes.byref(info)))
     ws = torch.empty(max(info.workspace_bytes, 256), dtype=torch.uint8, device=dev)
@@ -641,6 +746,51 @@ def main():
     del keep
     e2e_ms = f0.elapsed_time(f1) / e2e_steps
 
+
+    # Correctness of the sharded outputs, outside the timed region: every rank compares the
+    # first and the last sample of its shard with the CPU checker, and the per-sample fp64
+    # checksums of all shards are gathered over NCCL; rank 0 then recomputes the other ranks'
+    # shards itself (same seeds, same kernel: the checksums must agree bit for bit).
+    shard_check = None
+    if not args.no_shard_check:
+        step()
+        torch.cuda.synchronize(dev)
+        ok_o, err_o = oracle_check(wl, x, off, msk, w, b, out, [0, n - 1], args.dtype)
+        sums = out.double().sum(dim=(1, 2, 3))
+        flag = torch.tensor([1.0 if ok_o else 0.0, err_o], device=dev, dtype=torch.float64)
+        if world > 1:
+            per_rank = [torch.zeros(per, device=dev, dtype=torch.float64) for _ in range(world)]
+            mine = torch.zeros(per, device=dev, dtype=torch.float64)
+            mine[:n] = sums
+            dist.all_gather(per_rank, mine)
+            flags = [torch.zeros(2, device=dev, dtype=torch.float64) for _ in range(world)]
+            dist.all_gather(flags, flag)
+        else:
+            per_rank, flags = [sums], [flag]
+        if rank == 0:
+            match = True
+            for r in range(1, world):
+                r0, r1 = batch_shard(wl['N'], r, world)
+                xr, offr, mskr, _, _ = make_inputs(wl, r0, r1, dev, dtype)
+                outr = torch.empty(r1 - r0, wl['Co'], Ho, Wo, device=dev, dtype=dtype)
+                pr = abi_params(_lib, wl, r1 - r0, xr, offr, mskr, w, b, outr, args.dtype, args.fp32_math, local)
+                _lib.check(lib.dcn_fwd(ctypes.byref(pr), ctypes.c_void_p(ws.data_ptr()), ws.numel(), sptr))
+                torch.cuda.synchronize(dev)
+                match = match and bool(torch.equal(outr.double().sum(dim=(1, 2, 3)), per_rank[r][:r1 - r0]))
+                del xr, offr, mskr, outr
+            allsums = torch.cat([per_rank[r][:batch_shard(wl['N'], r, world)[1] - batch_shard(wl['N'], r, world)[0]]
+                                 for r in range(world)])
+            shard_check = dict(
+                ok=bool(match and all(f[0].item() == 1.0 for f in flags)),
+                samples_checked=[[batch_shard(wl['N'], r, world)[0], batch_shard(wl['N'], r, world)[1] - 1]
+                                 for r in range(world)],
+                checker_err_max=max(f[1].item() for f in flags),
+                checksums_gathered=int(allsums.numel()), checksums_match_single_gpu=bool(match),
+                checksum_of_checksums=float(allsums.sum().item()),
+                note='first and last sample of every shard against the CPU checker (bf16: relative '
+                     'L2 <= 2e-2; fp32: max|d| <= 1e-4 max|ref| + 1e-5); per-sample fp64 checksums '
+                     'gathered over NCCL and compared with rank 0 recomputing every other shard')
+
     t = torch.tensor([ms_total, e2e_ms, kms[0], kms[1], kms[2]], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -696,7 +846,7 @@ def main():
                           frac=achieved / peak_tf, traffic=traffic, peak_source=peak_src,
                           frac_of_sustained=(achieved / peaks['bf16_tflops_sustained']
                                              if 'bf16_tflops_sustained' in peaks else None),
-                          kernel='dcn_fwd_tc' if info.path == 1 else 'dcn_fwd_simt_direct'),
+                          kernel=main_kernel_name(info)),
             e2e=dict(value=fl_total / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
                      h2d_bytes_per_step=h2d, d2h_bytes_per_step=d2h, ms_per_step=e2e_ms,
                      steps=e2e_steps, chunks=(n + chunk - 1) // chunk,
@@ -709,6 +859,29 @@ def main():
             line['phase_counters_cycles_block0_last_launch'] = counters
         if not args.no_cpu_baseline:
             line['cpu_baseline'] = cpu_reference_sample(wl)
+        if shard_check is not None:
+            line['shard_check'] = shard_check
+        if world == 1 and args.workload == 'c5' and not args.batch and not args.no_per_config:
+            # every other configuration of the metric, at full size, on this GPU
+            del x, off, msk, out, hx, hoff, hmsk, hout
+            torch.cuda.empty_cache()
+            tf32 = measure_tf32_peak(dev)
+            per_config = {}
+            for key, (nm, dt, fm) in {'c1_fp32_tf32x3': ('c1', 'fp32', 'tf32x3'), 'c1_fp32_ffma': ('c1', 'fp32', 'ffma'),
+                                      'c2_bf16': ('c2', 'bf16', ''), 'c2_fp32_tf32x3': ('c2', 'fp32', 'tf32x3'),
+                                      'c3_bf16': ('c3', 'bf16', ''), 'c3_fp32_tf32x3': ('c3', 'fp32', 'tf32x3')}.items():
+                per_config[key] = measure_config(_lib, lib, nm, dt, fm, dev, peaks, tf32)
+            c4args = argparse.Namespace(**vars(args))
+            c4args.batch, c4args.steps, c4args.e2e_steps = 0, 5, 1
+            c4 = run_c4(c4args, 0, 1, local, dist_ready=True, emit=False)
+            per_config['c4_bf16_stack'] = dict(
+                workload=c4['config']['workload'], dtype='bf16', ms_per_step=c4['ms_per_step'],
+                tflops=c4['value'], per_layer_ms=c4['per_layer_ms'],
+                roofline=dict(layer_ms=c4['layer_roofline']['ms'], frac=c4['layer_roofline']['frac'],
+                              peak=peak_tf, peak_name='sum over the 26 launches of max(FLOPs at the bf16 '
+                              'tensor peak, compulsory bytes at HBM bandwidth)'),
+                parity=c4['parity'], parity_ok=c4['parity_ok'], e2e_tflops=c4['e2e']['value'])
+            line['per_config'] = per_config
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()

@@ -79,6 +79,7 @@ const Knobs &knobs() {
     k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
     k.tab_slots = env_int("DCN_B200_TAB_SLOTS", 0, 0, 16);
     k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
+    g_debug_flags.store(env_int("DCN_B200_DEBUG_FLAGS", 0, 0, 255));
   });
   return k;
 }
@@ -199,7 +200,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   if (tp->items >= 2147483647LL) return;
   TcPlan t = *tp;
   t.version = 2;
-  t.producer_cfg = 2016;  // 2 table-builder warps, 16 gather warps
+  t.producer_cfg = 4016;  // 4 table-builder warps, 16 gather warps
   // K units: (32-channel half-chunk, tap), half-chunk-major; two per k-stage
   t.KH = (g.Cg + 31) / 32;
   t.U = t.KH * g.T;
@@ -235,7 +236,9 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   t.tab_span = (uniform && run >= 2 && ndu == 1 && t.KH % run == 0 &&
                 (size_t)2 * g.T * (kBM + 4) * entry <= 60 * 1024) ? run : 0;
   t.tab_slot_blocks = t.tab_span ? g.T : 2 * ndu;
-  t.tab_slots = t.tab_span ? 2 : (kn.tab_slots ? kn.tab_slots : 6);
+  // (stage segments: an even ring of at least six slots, so that a slot always serves the same
+  // gather group and no builder warp meets a slot two uses after its last visit)
+  t.tab_slots = t.tab_span ? 2 : (kn.tab_slots >= 6 ? kn.tab_slots / 2 * 2 : 6);
   if ((size_t)t.tab_slots * t.tab_slot_blocks * (kBM + 4) * entry > 64 * 1024) return;
   // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles
   // whose 32-channel slabs never reach into another tile's channels.

@@ -7,28 +7,28 @@
 // mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:108-137), with the producer side split into
 // two decoupled roles:
 //
-//   * table builders (2 warps; a warp takes every other (tap, deform group) block of 128
-//     entries, four rows per thread, all loads of a block in flight together) turn offsets and
+//   * table builders (4 warps; a warp owns every fourth table segment and fills its blocks of
+//     128 entries, four rows per thread) turn offsets and
 //     masks into tap-table entries -- four 16-bit corner weights with the modulation folded
 //     in, and the byte offset of the top-left corner -- and publish them through a ring of
 //     table segments in shared memory.  They run ahead of the gather, which therefore never
 //     waits for an offset or a mask.
-//   * gather warps (16) read an entry, fetch the four corners, blend them on packed 16-bit
-//     FMAs and write the 128-byte-swizzled operand tile tcgen05.mma reads.  The input is a
+//   * gather warps (16, in two groups that fill alternate k-stages) read an entry, fetch the
+//     four corners, blend them on packed 16-bit FMAs and write the 128-byte-swizzled operand
+//     tile tcgen05.mma reads; a thread blends 16 channels of one (row, unit).  The input is a
 //     channels-last copy with a one-pixel zero border around every sample: a corner outside
 //     the image reads zeros, a sample outside the sampling gate points at an all-zero
 //     neighbourhood with zero weights, so the loads carry no predicates and a corner inside
 //     the image is always read (0 * Inf = NaN as in the reference,
-//     modulated_deform_conv_cuda_kernel.cuh:100-107).  Two rows per thread are in flight and
-//     the rotation runs across k-stage boundaries.
+//     modulated_deform_conv_cuda_kernel.cuh:100-107).
 //   * K is walked in units of (32-channel half-chunk, tap); a k-stage is two consecutive units.
 //     The 32-channel slice of the tile's input neighbourhood (its undeformed footprint plus a
 //     margin) is brought into shared memory by one tensor-map copy (cp.async.bulk.tensor, zero
 //     fill outside the tensor) per half-chunk, double-buffered; entries whose 2x2 neighbourhood
-//     lies inside that window are read from shared memory (64 bytes per pixel; the two units of
-//     a row read their left/right corners in opposite order when needed, so that the eight
-//     lanes of a row never meet in a bank), the others from global memory, through the same
-//     generic loads.
+//     lies inside that window are read from shared memory (64 bytes per pixel; which of the
+//     left/right corners and which of its two 16-byte vectors a lane reads first depends on
+//     the slot's and the row's parity, so that the eight lanes of a quarter warp never meet in
+//     a bank), the others from global memory.
 //
 // MMA issue, weight loader (cp.async.bulk + mbarrier complete_tx) and the accumulator
 // double-buffering in tensor memory are as in dcn_fwd_tc.  Every mbarrier wait is bounded.
@@ -48,15 +48,31 @@ namespace {
 constexpr int kEpiWarps = 4;
 constexpr int kMmaWarp2 = 4;
 constexpr int kLoadWarp2 = 5;
-constexpr int kFirstBuildWarp = 6;
-constexpr int kBuildWarps = 2;
+constexpr int kWinWarp = 6;   // (warp 7 idles: the builders are a warpgroup of their own)
+constexpr int kFirstBuildWarp = 8;
+constexpr int kBuildWarps = 4;
 constexpr int kFirstGatherWarp = kFirstBuildWarp + kBuildWarps;
 constexpr int kGatherWarps = 16;
-constexpr int kThreads2 = (kFirstGatherWarp + kGatherWarps) * 32;  // 768: six warps per scheduler, 80 registers per thread
-constexpr int kPasses2 = (kBM * 8) / (kGatherWarps * 32);          // rows of a stage per gather thread
-constexpr int kRowsPerPass = kGatherWarps * 4;
-constexpr int kTabStride2 = kBM + 4;  // entries of one (tap, deform group) block, skewed
+constexpr int kThreads2 = (kFirstGatherWarp + kGatherWarps) * 32;  // 896 = 7 warpgroups: epilogue | MMA, weight loader, window loader, - | 4 builders | 4 x gather
+constexpr int kGroups2 = 2;                              // gather groups; group i fills k-stages i, i + 2, ...
+constexpr int kWarpsPerGroup = kGatherWarps / kGroups2;  // 8 warps: 64 rows per pass, two passes per stage
+constexpr int kTabStride2 = kBM + 8;  // entries of one (unit / tap, deform group) block; the skew puts the
+                                      // blocks of a stage's two units into different bank halves
 constexpr uint32_t kWinFlag = 0x80000000u;  // table entry: the neighbourhood is read from global memory
+
+// Register budget per role (setmaxnreg works on warpgroups of four consecutive warps; the
+// block starts with 72 registers per thread): the two warpgroups that hold the epilogue and the
+// MMA / loader warps give registers back, the four gather warpgroups take them, the builders
+// keep theirs.
+constexpr int kRegsLight = 56, kRegsGather = 80;
+template <int N>
+__device__ __forceinline__ void reg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void reg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
 
 struct alignas(64) Tc2Args {
   CUtensorMap win_map;       // padded channels-last input as a 4-D tensor (window copies)
@@ -72,19 +88,6 @@ struct alignas(64) Tc2Args {
   unsigned long long wait_limit_ns;
   int debug_flags;
 };
-
-// Non-blocking test of a barrier phase (mbar_try_wait may suspend the thread for a while).
-__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
 
 // 16-byte loads.  `tok` is passed through untouched; code that must come after a load's issue
 // takes `tok` as an input.
@@ -163,16 +166,16 @@ __device__ __forceinline__ Smem2 carve2(uint8_t *base, const TcPlan &tp) {
   return L;
 }
 
-// Out-of-line continuation of a wait: polls until the phase completes, the block aborts or the
+// Continuation of a wait (kept out of the fast path): polls until the phase completes, the block aborts or the
 // time limit passes (then it raises the abort flag and records `code` in the status word).
-__device__ __noinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, int code, int backoff) {
+__device__ __forceinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, int code, int backoff) {
   uint8_t *ctrl = smem_aligned();
   volatile int *abort_s = (volatile int *)(ctrl + kCtrlAbort);
   const unsigned long long limit = *(const unsigned long long *)(ctrl + kCtrlLimit);
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (backoff) __nanosleep(200);
+    if (backoff) __nanosleep((unsigned)backoff);
     if ((it & 15u) == 0u) {
       if (*abort_s) return false;
       if (globaltimer_ns() - t0 > limit) {
@@ -184,7 +187,7 @@ __device__ __noinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, int 
   }
 }
 // Bounded wait.  Returns false when the block is aborting.
-__device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int code, int backoff = 0) {
+__device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int code, int backoff = 100) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow2(bar, parity, code, backoff);
 }
@@ -204,6 +207,17 @@ __device__ __forceinline__ void sts8(uint32_t addr, uint32_t x, uint32_t y) {
 }
 __device__ __forceinline__ void sts4(uint32_t addr, uint32_t x) {
   asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(x) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+        "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
 }
 
 struct TileId2 {
@@ -296,7 +310,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < A; ++i) {
-      mbar_init(full_a + 8 * i, kGatherWarps);
+      mbar_init(full_a + 8 * i, kWarpsPerGroup);
       mbar_init(empty_a + 8 * i, 1);
     }
     for (int i = 0; i < B; ++i) {
@@ -310,8 +324,8 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       mbar_init(win_empty + 8 * i, kGatherWarps);
     }
     for (int i = 0; i < RS; ++i) {
-      mbar_init(tab_full + 8 * i, kBuildWarps);
-      mbar_init(tab_empty + 8 * i, kGatherWarps);
+      mbar_init(tab_full + 8 * i, kSegStage ? 1 : kBuildWarps);   // the segment's owner, or all builders
+      mbar_init(tab_empty + 8 * i, kSegStage ? kWarpsPerGroup : kGatherWarps);
     }
     *abort_s = 0;
     *(unsigned long long *)(smem + kCtrlLimit) = a.wait_limit_ns;
@@ -341,6 +355,8 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
   const uint32_t Cb = (uint32_t)g.C * 2u;       // bytes of one padded pixel
   const uint32_t Rb = Wp * Cb;                  // bytes of one padded row
 
+  if (warp < kFirstBuildWarp) {
+  reg_dec<kRegsLight>();
   if (warp < kEpiWarps) {
     // ------------------------------ epilogue ------------------------------
     // Thread = one pixel (accumulator row); per 32 output channels one tcgen05.ld, then bias,
@@ -367,7 +383,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
       const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
       pt.lap(13);
-      bool ok = mbar_wait2(tmem_full + 8 * buf, par, 3, 1);
+      bool ok = mbar_wait2(tmem_full + 8 * buf, par, 3, 200);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05 instructions below need the whole warp
       if (!ok) break;
       pt.lap(12);
@@ -385,30 +401,34 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const uint32_t taddr = tmem_base + (uint32_t)(buf * tp.BN) + ((uint32_t)(warp * 32) << 16);
       if (tp.epi_tma) {
         for (int c0 = 0; c0 < ncols; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + (uint32_t)c0, r);
-          tmem_ld_wait();
-          const TIO *bs = bias_w + c0;
           // the slab about to be overwritten must have been read by the store issued from it
           bulk_wait_read<1>();
           __syncwarp();
           const uint32_t sbase = epi_base + slab * kSlabBytes + (uint32_t)lane * (uint32_t)sizeof(TIO);
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[16];
+            tmem_ld16(taddr + (uint32_t)(c0 + 16 * h), r);
+            tmem_ld_wait();
+            const TIO *bs = bias_w + c0 + 16 * h;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
-            float b4[4];
-            load4_as_float(bs + 4 * j4, b4);
+            for (int j4 = 0; j4 < 4; ++j4) {
+              float b4[4];
+              load4_as_float(bs + 4 * j4, b4);
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              const int j = 4 * j4 + k;
-              float v = __uint_as_float(r[j]) + b4[k];
-              if (act_tile) v = apply_act(g, co0 + c0 + j, v);
-              if constexpr (sizeof(TIO) == 2) {
-                TIO o;
-                st_from_float(&o, 0, v);
-                const unsigned short bits = *reinterpret_cast<const unsigned short *>(&o);
-                asm volatile("st.shared.u16 [%0], %1;" ::"r"(sbase + (uint32_t)j * 64u), "h"(bits) : "memory");
-              } else {
-                asm volatile("st.shared.f32 [%0], %1;" ::"r"(sbase + (uint32_t)j * 128u), "f"(v) : "memory");
+              for (int k = 0; k < 4; ++k) {
+                const int j = 4 * j4 + k;
+                float v = __uint_as_float(r[j]) + b4[k];
+                if (act_tile) v = apply_act(g, co0 + c0 + 16 * h + j, v);
+                const uint32_t sa_ = sbase + (uint32_t)(16 * h + j) * 32u * (uint32_t)sizeof(TIO);
+                if constexpr (sizeof(TIO) == 2) {
+                  TIO o;
+                  st_from_float(&o, 0, v);
+                  const unsigned short bits = *reinterpret_cast<const unsigned short *>(&o);
+                  asm volatile("st.shared.u16 [%0], %1;" ::"r"(sa_), "h"(bits) : "memory");
+                } else {
+                  asm volatile("st.shared.f32 [%0], %1;" ::"r"(sa_), "f"(v) : "memory");
+                }
               }
             }
           }
@@ -427,14 +447,15 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         const int ho = t.ho0 + ty, wo = t.wo0 + tx;
         const bool valid = ho < g.Ho && wo < g.Wo;
         TIO *orow = out + (long long)t.n * g.out_sn + (long long)co0 * plane + (long long)ho * g.Wo + wo;
-        for (int c0 = 0; c0 < ncols; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld32(taddr + (uint32_t)c0, r);
+#pragma unroll 1
+        for (int c0 = 0; c0 < ncols; c0 += 16) {
+          uint32_t r[16];
+          tmem_ld16(taddr + (uint32_t)c0, r);
           tmem_ld_wait();
           const TIO *bs = bias_w + c0;
           TIO *oc = orow + (long long)c0 * plane;
 #pragma unroll
-          for (int j4 = 0; j4 < 8; ++j4) {
+          for (int j4 = 0; j4 < 4; ++j4) {
             float b4[4];
             load4_as_float(bs + 4 * j4, b4);
             float v[4] = {__uint_as_float(r[4 * j4]) + b4[0], __uint_as_float(r[4 * j4 + 1]) + b4[1],
@@ -469,16 +490,16 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const int buf = (int)(li & 1);
       const uint32_t par = (li >> 1) & 1u;
       pt.lap(11);
-      ok = __all_sync(0xffffffffu, mbar_wait2(tmem_empty + 8 * buf, par ^ 1u, 4));
+      ok = __all_sync(0xffffffffu, mbar_wait2(tmem_empty + 8 * buf, par ^ 1u, 4, 0));
       if (!ok) break;
       pt.lap(10);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)(buf * tp.BN);
       for (int ks = 0; ks < tp.S; ++ks) {
-        ok = __all_sync(0xffffffffu, mbar_wait2(full_b + 8 * sb, pb, 5));
+        ok = __all_sync(0xffffffffu, mbar_wait2(full_b + 8 * sb, pb, 5, 0));
         if (!ok) break;
         pt.lap(8);
-        ok = __all_sync(0xffffffffu, mbar_wait2(full_a + 8 * sa, pa, 6));
+        ok = __all_sync(0xffffffffu, mbar_wait2(full_a + 8 * sa, pa, 6, 0));
         if (!ok) break;
         pt.lap(9);
         tc_fence_after();
@@ -501,55 +522,18 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     }
     __syncwarp();
   } else if (warp == kLoadWarp2) {
-    // ------------------ weight loader (+ input windows) ------------------
+    // ------------------------------ weight loader ------------------------------
     if (lane == 0) {
       const uint32_t per_mt = (uint32_t)(g.groups * tp.NT);
       uint32_t sb = 0, pb = 0;
       bool ok = true;
-      // window copies: one per (tile, 32-channel half-chunk), issued as soon as its buffer is free; `wq` counts
-      // them; the loop below polls for the next one between weight copies
-      uint32_t w_item = blockIdx.x, wq = 0;
-      int w_cc = 0;
-      const uint32_t wbytes = (uint32_t)win_bytes(tp);
-      auto try_window = [&]() {
-        // buffer wq & 1 was last used by window wq - 2
-        if (kWin && w_item < items && mbar_test(win_empty + 8 * (wq & 1u), ((wq >> 1) & 1u) ^ 1u)) {
-          const TileId2 t = decode_item2(w_item, g, tp);
-          const uint32_t wb = wq & 1u;
-          mbar_arrive_expect_tx(win_full + 8 * wb, wbytes);
-          // coordinates in the padded tensor: (channel, column + 1, row + 1, sample)
-          tma_load_4d(smem_u32(L.win) + wb * wbytes, &a.win_map, t.grp * g.Cg + w_cc * 32,
-                      win_x0(g, tp, t.wo0) + 1, win_y0(g, tp, t.ho0) + 1, t.n, win_full + 8 * wb);
-          ++wq;
-          if (++w_cc == tp.KH) { w_cc = 0; w_item += gridDim.x; }
-        }
-      };
       PhaseTimer pt(a.counters, blockIdx.x == 0);
       for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const uint32_t rem = item % per_mt;
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
         for (int ks = 0; ks < tp.S; ++ks) {
           pt.lap(15);
-          if (kWin) {
-            // while waiting for a free weight stage keep serving the windows
-            const unsigned long long t0 = globaltimer_ns();
-            uint32_t it = 0;
-            try_window();
-            while (!mbar_test(empty_b + 8 * sb, pb ^ 1u)) {
-              try_window();
-              if ((++it & 63u) == 0u) {
-                if (*abort_s) { ok = false; break; }
-                if (globaltimer_ns() - t0 > a.wait_limit_ns) {
-                  *abort_s = 1;
-                  atomicCAS(a.status, 0, 7);
-                  ok = false;
-                  break;
-                }
-              }
-            }
-          } else {
-            ok = mbar_wait2(empty_b + 8 * sb, pb ^ 1u, 7);
-          }
+          ok = mbar_wait2(empty_b + 8 * sb, pb ^ 1u, 7);
           if (!ok) break;
           pt.lap(14);
           const bool withhold = (a.debug_flags & 1) && item + gridDim.x >= items && ks == tp.S - 1;
@@ -561,30 +545,35 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           if (++sb == (uint32_t)B) { sb = 0; pb ^= 1u; }
         }
       }
-      if (kWin) {
-        // windows still owed (the gather of the last tile waits for them)
-        const unsigned long long t0 = globaltimer_ns();
-        uint32_t it = 0;
-        while (ok && w_item < items) {
-          try_window();
-          if ((++it & 63u) == 0u) {
-            if (*abort_s) break;
-            if (globaltimer_ns() - t0 > a.wait_limit_ns) {
-              *abort_s = 1;
-              atomicCAS(a.status, 0, 11);
-              break;
-            }
-          }
+    }
+    __syncwarp();
+  } else if (warp == kWinWarp) {
+    // ------------------------------ window loader ------------------------------
+    // One tensor-map copy per (tile, 32-channel half-chunk), in the order the gather uses
+    // them, into the two window buffers in turn.
+    if (kWin && lane == 0) {
+      const uint32_t wbytes = (uint32_t)win_bytes(tp);
+      uint32_t wq = 0;
+      bool ok = true;
+      for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        const TileId2 t = decode_item2(item, g, tp);
+        for (int hc = 0; hc < tp.KH; ++hc, ++wq) {
+          const uint32_t wb = wq & 1u;
+          // buffer wb was last used by window wq - 2
+          ok = mbar_wait2(win_empty + 8 * wb, ((wq >> 1) & 1u) ^ 1u, 11);
+          if (!ok) break;
+          mbar_arrive_expect_tx(win_full + 8 * wb, wbytes);
+          // coordinates in the padded tensor: (channel, column + 1, row + 1, sample)
+          tma_load_4d(smem_u32(L.win) + wb * wbytes, &a.win_map, t.grp * g.Cg + hc * 32,
+                      win_x0(g, tp, t.wo0) + 1, win_y0(g, tp, t.ho0) + 1, t.n, win_full + 8 * wb);
         }
       }
     }
     __syncwarp();
+  }
   } else if (warp < kFirstGatherWarp) {
     // ------------------------------ table builders ------------------------------
-    // The (unit, deform group) blocks of all segments form one stream; builder warp b computes
-    // blocks b, b + 2, ...: four rows per thread.  The twelve loads of a block are in flight
-    // together, and a block is computed only after the loads of the warp's next block have
-    // been issued.
+    // A block = the 128 entries of one (unit or tap, deform group): four rows per thread.
     const int bw = warp - kFirstBuildWarp;
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
@@ -593,11 +582,12 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     const int wh = tp.win_h, ww = tp.win_w;
     const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)lane * 8u;
     const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)lane * 4u;
-    uint32_t q = 0, turn = 0;
     bool ok = true;
     PhaseTimer pt(a.counters, blockIdx.x == 0 && bw == 0 && lane == 0);
+    const uint32_t nseg = seg_per_stage ? (uint32_t)tp.S : (uint32_t)(tp.KH / tp.tab_span);  // segments per tile
 
-    // Ask L2 for the offset and mask planes of tile `nitem` (dense planes only).
+    // Ask L2 for a quarter (this warp's) of the offset and mask planes of tile `nitem` (dense
+    // planes only).
     auto prefetch_tile = [&](uint32_t nitem) {
       if (!dense_planes || nitem >= items) return;
       const TileId2 nt_ = decode_item2(nitem, g, tp);
@@ -620,195 +610,232 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       }
     };
 
-    // the block whose loads are in flight (always one of the current tile)
-    uint32_t roh[4], row_[4], rmm[4];
-    bool pend = false, pend_first = false, pend_last = false;
-    uint32_t pend_e = 0, pend_slot = 0, pend_par = 0;
-    int pend_ti = 0, pend_tj = 0;
-    int ho0 = 0, wo0 = 0, wy0 = 0, wx0 = 0;   // current tile
-    // entries of the pending block, then its segment's hand-over if it was this warp's last
-    // block there
-    auto flush = [&]() -> bool {
-      if (!pend) return true;
-      pend = false;
-      if (pend_first) {
-        pt.lap(1);
-        const bool r = mbar_wait2(tab_empty + 8 * pend_slot, pend_par, 9);
-        pt.lap(6);
-        if (!r) return false;
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
-        uint32_t eo = dead_off;
-        // this thread's rows: lane, lane + 32, lane + 64, lane + 96
-        const int r = lane + 32 * j;
-        const int ho = ho0 + (r >> tp.tw_log2), wo = wo0 + (r & tw_mask);
-        const float h_im = (float)(ho * g.stride_h - g.pad_h + pend_ti * g.dil_h) + RawOf<TIO>::to_float(roh[j]);
-        const float w_im = (float)(wo * g.stride_w - g.pad_w + pend_tj * g.dil_w) + RawOf<TIO>::to_float(row_[j]);
-        if (ho < g.Ho && wo < g.Wo && h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
-          const float m = msk ? mask_value(g, RawOf<TIO>::to_float(rmm[j])) : 1.f;
-          const float hf = floorf(h_im), wf = floorf(w_im);
-          const float lh = h_im - hf, lw = w_im - wf;
-          const float hh = 1.f - lh, hw = 1.f - lw;
-          wt.x = hh * hw * m; wt.y = hh * lw * m; wt.z = lh * hw * m; wt.w = lh * lw * m;
-          const int hl = (int)hf, wl = (int)wf;
-          // inside the shared-memory window: offset within the window (64 bytes per pixel);
-          // else (flagged) the offset within the padded sample
-          const int wy = hl - wy0, wx = wl - wx0;
-          if (kWin && wy >= 0 && wx >= 0 && wy + 1 < wh && wx + 1 < ww)
-            eo = (uint32_t)(wy * ww + wx) * 64u;
-          else
-            eo = (((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb) | kWinFlag;
-        }
-        const uint32_t e = pend_e + 32u * (uint32_t)j;
-        sts8(tabw_addr + e * 8u, pack_weights2<MODE>(wt.x, wt.y), pack_weights2<MODE>(wt.z, wt.w));
-        sts4(tabo_addr + e * 4u, eo);
-      }
-      if (pend_last) {
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tab_full + 8 * pend_slot);
-      }
-      return true;
-    };
-
-    prefetch_tile(blockIdx.x);
-    for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
-      ok = flush();   // (a pending block belongs to the previous tile)
-      if (!ok) break;
-      const TileId2 t = decode_item2(item, g, tp);
+    uint32_t cur_item = 0xffffffffu;
+    TileId2 t = {0, 0, 0, 0, 0};
+    int wy0 = 0, wx0 = 0;
+    const TIO *offn = nullptr, *mskn = nullptr;
+    auto enter_tile = [&](uint32_t item) {
+      if (item == cur_item) return;
+      cur_item = item;
+      t = decode_item2(item, g, tp);
       prefetch_tile(item + gridDim.x);
-      ho0 = t.ho0; wo0 = t.wo0;
       wy0 = win_y0(g, tp, t.ho0); wx0 = win_x0(g, tp, t.wo0);
-      // pixel of each of this thread's rows (a row beyond the image reads pixel 0; its entry
-      // fails the test above)
-      int pix[4];
+      offn = off ? off + (long long)t.n * g.off_sn : nullptr;
+      mskn = msk ? msk + (long long)t.n * g.msk_sn : nullptr;
+    };
+    // The 128 entries of table block `blk` of slot `slot`: tap (ti, tj) = `tap`, deform group dgi.
+    auto do_block = [&](uint32_t slot, uint32_t blk, int tap, int ti, int tj, int dgi) {
+      const float tif = (float)(ti * g.dil_h), tjf = (float)(tj * g.dil_w);
+      const TIO *ob = off ? offn + ((long long)dgi * 2 * T + 2 * tap) * g.off_cs : nullptr;
+      const TIO *mb = msk ? mskn + ((long long)dgi * T + tap) * g.msk_cs : nullptr;
+      const uint32_t e0 = slot * slot_entries + blk * kTabStride2;
+      // this thread's rows: lane, lane + 32, lane + 64, lane + 96, two at a time (the six loads
+      // of a pair in flight together)
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int r = lane + 32 * j;
-        const int ho = t.ho0 + (r >> tp.tw_log2), wo = t.wo0 + (r & tw_mask);
-        pix[j] = (ho < g.Ho && wo < g.Wo) ? ho * g.Wo + wo : 0;
-      }
-      const TIO *offn = off ? off + (long long)t.n * g.off_sn : nullptr;
-      const TIO *mskn = msk ? msk + (long long)t.n * g.msk_sn : nullptr;
-      const int nseg = seg_per_stage ? tp.S : tp.KH / tp.tab_span;
-      // running unit (stage segments): half-chunk, tap and the tap's row / column
-      int u_hc = 0, u_tap = 0, u_ti = 0, u_tj = 0;
-      int c_hc = -1, dg_lo = 0, nd = 1;   // deform groups of half-chunk c_hc
-      for (int sg = 0; sg < nseg && ok; ++sg, ++q) {
-        const uint32_t slot = q % (uint32_t)RS;
-        const uint32_t spar = ((q / (uint32_t)RS) & 1u) ^ 1u;
-        // the segment's units: two consecutive (half-chunk, tap) units, or the taps of one run
-        const int n_u = seg_per_stage ? min(2, tp.U - 2 * sg) : T;
-        if (!seg_per_stage) { u_hc = sg * tp.tab_span; u_tap = 0; u_ti = 0; u_tj = 0; }
-        bool first_mine = true;
-        for (int ui = 0; ui < n_u && ok; ++ui) {
-          const int hc = u_hc, tap = u_tap, ti = u_ti, tj = u_tj;
-          // next unit
-          if (++u_tj == g.kw) { u_tj = 0; ++u_ti; }
-          if (++u_tap == T) { u_tap = 0; u_ti = 0; u_tj = 0; ++u_hc; }
-          if (hc != c_hc) {
-            c_hc = hc;
-            const int c0 = t.grp * g.Cg + hc * 32;
-            dg_lo = c0 / g.cpdg;
-            nd = seg_per_stage ? (min(c0 + 32, (t.grp + 1) * g.Cg) - 1) / g.cpdg - dg_lo + 1 : 1;
+      for (int half = 0; half < 2; ++half) {
+        uint32_t roh[2], row_[2], rmm[2];
+        float hbf[2], wbf[2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int r = lane + 64 * half + 32 * j;
+          const int ho = t.ho0 + (r >> tp.tw_log2), wo = t.wo0 + (r & tw_mask);
+          const bool rv = ho < g.Ho && wo < g.Wo;
+          // a row beyond the image reads pixel 0 and gets a position that fails the gate
+          const long long pix = rv ? (long long)ho * g.Wo + wo : 0;
+          hbf[j] = rv ? (float)(ho * g.stride_h - g.pad_h) + tif : -1.0e9f;
+          wbf[j] = (float)(wo * g.stride_w - g.pad_w) + tjf;
+          roh[j] = 0; row_[j] = 0; rmm[j] = 0;
+          if (off) {
+            const TIO *pp = ob + pix * g.off_ps;
+            roh[j] = ldg_raw_ordered(pp);
+            row_[j] = ldg_raw_ordered(pp + g.off_cs);
           }
-          for (int d = 0; d < nd && ok; ++d) {
-            const bool mine = (int)turn == bw;
-            if (++turn == (uint32_t)kBuildWarps) turn = 0;
-            if (!mine) continue;
-            // loads of this block, issued before the pending block is computed
-            uint32_t noh[4], now_[4], nmm[4];
-            const TIO *ob = off ? offn + ((long long)(dg_lo + d) * 2 * T + 2 * tap) * g.off_cs : nullptr;
-            const TIO *mb = msk ? mskn + ((long long)(dg_lo + d) * T + tap) * g.msk_cs : nullptr;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              noh[j] = 0; now_[j] = 0; nmm[j] = 0;
-              if (off) {
-                const TIO *pp = ob + (long long)pix[j] * g.off_ps;
-                noh[j] = ldg_raw_ordered(pp);
-                now_[j] = ldg_raw_ordered(pp + g.off_cs);
-              }
-              if (msk) nmm[j] = ldg_raw_ordered(mb + (long long)pix[j] * g.msk_ps);
-            }
-            ok = flush();
-            if (!ok) break;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { roh[j] = noh[j]; row_[j] = now_[j]; rmm[j] = nmm[j]; }
-            pend = true;
-            pend_first = first_mine;
-            pend_last = false;
-            first_mine = false;
-            pend_slot = slot;
-            pend_par = spar;
-            pend_ti = ti;
-            pend_tj = tj;
-            pend_e = slot * slot_entries +
-                     (seg_per_stage ? (uint32_t)(ui * tp.ndu + d) : (uint32_t)tap) * kTabStride2;
-          }
+          if (msk) rmm[j] = ldg_raw_ordered(mb + pix * g.msk_ps);
         }
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
+          uint32_t eo = dead_off;
+          const float h_im = hbf[j] + RawOf<TIO>::to_float(roh[j]);
+          const float w_im = wbf[j] + RawOf<TIO>::to_float(row_[j]);
+          if (h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
+            const float m = msk ? mask_value(g, RawOf<TIO>::to_float(rmm[j])) : 1.f;
+            const float hf = floorf(h_im), wf = floorf(w_im);
+            const float lh = h_im - hf, lw = w_im - wf;
+            const float hh = 1.f - lh, hw = 1.f - lw;
+            wt.x = hh * hw * m; wt.y = hh * lw * m; wt.z = lh * hw * m; wt.w = lh * lw * m;
+            const int hl = (int)hf, wl = (int)wf;
+            // inside the shared-memory window: offset within the window (64 bytes per pixel);
+            // else (flagged) the offset within the padded sample
+            const uint32_t wy = (uint32_t)(hl - wy0), wx = (uint32_t)(wl - wx0);
+            if (kWin && wy < (uint32_t)(wh - 1) && wx < (uint32_t)(ww - 1))
+              eo = (wy * (uint32_t)ww + wx) * 64u;
+            else
+              eo = (((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb) | kWinFlag;
+          }
+          const uint32_t e = e0 + 64u * (uint32_t)half + 32u * (uint32_t)j;
+          sts8(tabw_addr + e * 8u, pack_weights2<MODE>(wt.x, wt.y), pack_weights2<MODE>(wt.z, wt.w));
+          sts4(tabo_addr + e * 4u, eo);
+        }
+      }
+    };
+    prefetch_tile(blockIdx.x);
+    if constexpr (kSegStage) {
+      // Stage segments: builder warp b owns the segments b, b + 4, ... (counted over all tiles
+      // of this block): it alone fills them and hands them over.  (The ring is deeper than the
+      // builders are many, so a warp never meets a slot two uses ahead of its last visit.)
+      uint32_t item = blockIdx.x, sg = (uint32_t)bw, q = (uint32_t)bw;
+      for (;; sg += (uint32_t)kBuildWarps, q += (uint32_t)kBuildWarps) {
+        while (item < items && sg >= nseg) { sg -= nseg; item += gridDim.x; }
+        if (item >= items || !ok) break;
+        enter_tile(item);
+        const uint32_t slot = q % (uint32_t)RS;
+        pt.lap(1);
+        ok = mbar_wait2(tab_empty + 8 * slot, ((q / (uint32_t)RS) & 1u) ^ 1u, 9);
+        pt.lap(6);
         if (!ok) break;
-        if (first_mine) {
-          // none of the segment's blocks was this warp's: it still waits for the slot and
-          // arrives, so that no arrival is counted for the slot's previous use
-          ok = mbar_wait2(tab_empty + 8 * slot, spar, 9);
+        // the segment's two consecutive (half-chunk, tap) units
+        const int n_u = min(2, tp.U - 2 * (int)sg);
+        int u_hc = (2 * (int)sg) / T, u_tap = 2 * (int)sg - u_hc * T;
+        for (int ui = 0; ui < n_u; ++ui) {
+          const int c0 = t.grp * g.Cg + u_hc * 32;
+          const int dg_lo = c0 / g.cpdg;
+          const int nd = (min(c0 + 32, (t.grp + 1) * g.Cg) - 1) / g.cpdg - dg_lo + 1;
+          const int ti = u_tap / g.kw;
+          for (int d = 0; d < nd; ++d)
+            do_block(slot, (uint32_t)(ui * tp.ndu + d), u_tap, ti, u_tap - ti * g.kw, dg_lo + d);
+          if (++u_tap == T) { u_tap = 0; ++u_hc; }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tab_full + 8 * slot);
+      }
+    } else {
+      // Run segments (one block per tap, two slots): every builder warp visits every segment
+      // and fills every fourth block of it; all of them hand it over.
+      uint32_t q = 0;
+      for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
+        enter_tile(item);
+        for (uint32_t sg = 0; sg < nseg && ok; ++sg, ++q) {
+          const uint32_t slot = q & 1u;
+          pt.lap(1);
+          ok = mbar_wait2(tab_empty + 8 * slot, ((q >> 1) & 1u) ^ 1u, 9);
+          pt.lap(6);
           if (!ok) break;
+          const int c0 = t.grp * g.Cg + (int)sg * tp.tab_span * 32;
+          const int dgi = c0 / g.cpdg;
+          for (int tap = bw; tap < T; tap += kBuildWarps) {
+            const int ti = tap / g.kw;
+            do_block(slot, (uint32_t)tap, tap, ti, tap - ti * g.kw, dgi);
+          }
           __syncwarp();
           if (lane == 0) mbar_arrive(tab_full + 8 * slot);
-        } else {
-          pend_last = true;  // the pending block is this warp's last one of the segment
         }
       }
     }
-    if (ok) ok = flush();
     if (!ok) *abort_s = 1;
   } else {
     // ------------------------------ gather ------------------------------
+    reg_inc<kRegsGather>();
+    // Group gi fills the k-stages gi, gi + 2, ... (counted over all tiles of this block).  A
+    // stage is two passes of 64 rows; in a pass a warp covers eight rows and a lane blends the
+    // 16 channels {q1, q2} x 8 of one (row, unit): lane = 4 * row + 2 * unit + p.
     const int gw = warp - kFirstGatherWarp;
-    const int sub = lane >> 3;  // row within the warp's group of four
-    const int v = lane & 7;     // 16-byte vector of the 128-byte row
-    const int usel = v >> 2;    // which of the stage's two units this lane gathers
-    const int cv = v & 3;       // 8-channel vector within the unit
-    const int row0 = gw * 4 + sub;
-    const uint32_t a_base = smem_u32(L.a) + (uint32_t)(row0 * 128 + ((v ^ (row0 & 7)) << 4));
+    const int gi = gw / kWarpsPerGroup, gwl = gw % kWarpsPerGroup;
+    const int rr = lane >> 2;          // row within the warp's eight
+    const int usel = (lane >> 1) & 1;  // which of the stage's two units
+    const int row0 = gwl * 8 + rr;     // pass p: row0 + 64 p
+    // Odd rows take their second vector first: the rows of a quarter warp then read (and
+    // write) different bank quarters.
+    const uint32_t q1 = (uint32_t)(lane & 1) ^ (uint32_t)((rr & 1) << 1), q2 = q1 ^ 2u;
+    // operand tile: 16-byte chunk (4 * unit + q) of row r lives at chunk index ^ (r & 7)
+    const uint32_t a_row = smem_u32(L.a) + (uint32_t)row0 * 128u;
+    const uint32_t a_c1 = ((uint32_t)(4 * usel) + q1) ^ (uint32_t)(row0 & 7);
+    const uint32_t a_c2 = ((uint32_t)(4 * usel) + q2) ^ (uint32_t)(row0 & 7);
     const char *xpad = reinterpret_cast<const char *>(a.xpad);
     const uint32_t wbytes = (uint32_t)win_bytes(tp);
     const uint32_t win_rb = (uint32_t)tp.win_w * 64u;
-    const uint32_t win_s = smem_u32(L.win) + (uint32_t)cv * 16u;
+    const uint32_t win_s = smem_u32(L.win);
     const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)row0 * 8u;
     const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)row0 * 4u;
     const int KH = tp.KH;
-    const int nseg = seg_per_stage ? tp.S : KH / tp.tab_span;   // table segments per tile
-
     const uint32_t span = seg_per_stage ? 1u : (uint32_t)tp.tab_span;
-    // position: the k-stage (item, s) whose loads are issued next; its unit A = 2 s is
-    // (half-chunk hcA, tap tapA); in run mode hcA is half-chunk inrunA of run runA
+    const uint32_t nseg = seg_per_stage ? (uint32_t)tp.S : (uint32_t)KH / span;   // table segments per tile
+    const uint32_t dead_o = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;   // an all-zero neighbourhood
+
+    // position: the k-stage (item, s) this group fills next; its unit A = 2 s is (half-chunk
+    // hcA, tap tapA); with run segments hcA is half-chunk inrunA of run runA
     uint32_t item = blockIdx.x;
-    int s = 0, hcA = 0, tapA = 0;
+    int s = gi, hcA = 0, tapA = 0;
     uint32_t runA = 0, inrunA = 0;
-    uint32_t sa = 0, pa = 0;
+    uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = ((uint32_t)gi / (uint32_t)A) & 1u;
     // running counts over the tiles of this block: window of (tile, half-chunk 0), table
     // segment of (tile, run 0); table ring position of the current stage (stage segments)
-    uint32_t win_base = 0, seg_base = 0, slotS = 0, phS = 0;
+    uint32_t win_base = 0, seg_base = 0;
+    uint32_t slotS = (uint32_t)gi % (uint32_t)RS, phS = ((uint32_t)gi / (uint32_t)RS) & 1u;
     // windows / run segments: next one to wait for, next one to hand back
     uint32_t win_acq = 0, win_rel = 0, seg_acq = 0, seg_rel = 0;
-    // this lane's unit of the stage; the values below change with its half-chunk only
-    int my_hc = -2;
-    const char *gbase = nullptr;   // sample + channel bytes of this lane's vector (global)
-    uint32_t wbase = 0;            // window buffer of the half-chunk + this lane's 16 bytes (shared address)
-    uint32_t e_fixed = 0;          // table entry of row0 without the stage's (or tap's) part
-    uint32_t e0 = 0;               // table entry of pass 0
-    bool zero_vec = false;
-    int grp = 0;
-    const char *sbase = nullptr;
-    auto enter_item = [&]() {
-      const TileId2 t = decode_item2(item, g, tp);
-      grp = t.grp;
-      sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
-      my_hc = -2;
+    bool ok = true;
+    PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
+
+    // unit A of stage s of a tile: (hcA, tapA) = divmod(2 s, T), and its run
+    auto locate = [&]() {
+      hcA = 0; tapA = 2 * s; runA = 0; inrunA = 0;
+      while (tapA >= T) {
+        tapA -= T; ++hcA;
+        if (++inrunA == span) { inrunA = 0; ++runA; }
+      }
     };
-    // Per-lane values of the stage at the current position.
-    auto enter_stage = [&]() {
+    // tiles are skipped while the stage index runs past their end
+    auto normalise = [&]() {
+      while (item < items && s >= tp.S) {
+        s -= tp.S;
+        item += gridDim.x;
+        win_base += (uint32_t)KH;
+        seg_base += nseg;
+      }
+      locate();
+    };
+    normalise();
+    int my_hc = -2;
+    uint32_t my_item = 0xffffffffu;
+    const char *gbase = nullptr;   // sample + channel bytes of this lane's unit (global)
+    uint32_t wbase = 0;            // window buffer of the unit's half-chunk (shared address)
+    uint32_t e_fixed = 0;          // table entry of row0 without the stage's (or tap's) part
+    bool zero_vec = false;
+    const char *sbase = nullptr;
+    int grp = 0;
+
+    while (item < items && ok) {
+      // ---- what the stage needs: table segment(s), the windows of both its units
+      uint32_t hcB = (uint32_t)hcA, runB = runA;
+      if (tapA + 1 == T && 2 * s + 1 < tp.U) {
+        ++hcB;
+        if (inrunA + 1u == span) ++runB;
+      }
+      if (seg_per_stage) {
+        ok = mbar_wait2(tab_full + 8 * slotS, phS, 12);
+      } else {
+        while (ok && seg_acq <= seg_base + runB) {
+          ok = mbar_wait2(tab_full + 8 * (seg_acq & 1u), (seg_acq >> 1) & 1u, 12);
+          ++seg_acq;
+        }
+      }
+      if (kWin) {
+        while (ok && win_acq <= win_base + hcB) {
+          ok = mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13);
+          ++win_acq;
+        }
+      }
+      pt.lap(2);
+      if (!ok) break;
+      // ---- this lane's unit
+      if (item != my_item) {
+        my_item = item;
+        my_hc = -2;
+        const TileId2 t = decode_item2(item, g, tp);
+        grp = t.grp;
+        sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
+      }
       int hc = hcA, tap = tapA;
       uint32_t run = runA;
       if (usel) {
@@ -820,166 +847,117 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const int key = 2 * s + usel < tp.U ? hc : -1;
       if (key != my_hc) {
         my_hc = key;
-        const int cg = hc * 32 + cv * 8;           // channel within the conv group
-        zero_vec = key < 0 || cg >= g.Cg;
+        // a unit beyond the tile's last one, or channels beyond the group: zero vectors
         const int c0 = grp * g.Cg + hc * 32;
-        const int c = zero_vec ? grp * g.Cg : c0 + cv * 8;
-        gbase = sbase + (unsigned long long)c * 2ull;
+        zero_vec = key < 0 || hc * 32 + 16 * (int)(lane & 1) >= g.Cg;   // (Cg is a multiple of 8; see issue)
+        gbase = sbase + (unsigned long long)(key < 0 ? grp * g.Cg : c0) * 2ull;
         wbase = win_s + ((win_base + (uint32_t)hc) & 1u) * wbytes;
-        if (seg_per_stage)
-          e_fixed = ((uint32_t)(usel * tp.ndu) + (zero_vec ? 0u : (uint32_t)(c / g.cpdg - c0 / g.cpdg))) * kTabStride2;
-        else
-          e_fixed = ((seg_base + run) & 1u) * slot_entries;
+        if (seg_per_stage) e_fixed = (uint32_t)(usel * tp.ndu) * kTabStride2;
+        else e_fixed = ((seg_base + run) & 1u) * slot_entries;
       }
-      e0 = seg_per_stage ? slotS * slot_entries + e_fixed : e_fixed + (uint32_t)tap * kTabStride2;
-    };
-
-    uint4 qd[2][4];
-    uint2 wq2[2];
-    uint32_t tok = 0;
-    bool ok = true;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
-    // loads of pass p of the k-stage at the current position into register set p
-    auto issue = [&](int p) {
-      uint2 w = make_uint2(0u, 0u);
-      uint32_t o = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;   // an all-zero neighbourhood
-      if (!zero_vec) {
-        const uint32_t e = e0 + (uint32_t)(p * kRowsPerPass);
-        w = lds8(tabw_addr + e * 8u);
-        o = lds4(tabo_addr + e * 4u);
+      const uint32_t e0 = seg_per_stage ? slotS * slot_entries + e_fixed : e_fixed + (uint32_t)tap * kTabStride2;
+      // deform group of each of the two vectors within the unit's set (stage segments; a unit
+      // spans several deform groups only when a deform group has fewer than 32 channels)
+      uint32_t eq1 = 0, eq2 = 0;
+      if (seg_per_stage && tp.ndu > 1 && key >= 0) {
+        const int c0 = grp * g.Cg + hc * 32;
+        eq1 = (uint32_t)((c0 + 8 * (int)q1) / g.cpdg - c0 / g.cpdg) * kTabStride2;
+        eq2 = (uint32_t)((c0 + 8 * (int)q2) / g.cpdg - c0 / g.cpdg) * kTabStride2;
       }
-      const uint32_t ob = o & ~kWinFlag;
-      if constexpr (kWin) {
-        // The two units of a row read 64-byte slots; the lanes of unit 0 start with the
-        // even slot of their left/right pair and those of unit 1 with the odd one, so the
-        // eight lanes of a row always cover all 32 banks.  (The window's row pitch is an even
-        // number of slots: the bottom corners repeat the top ones' parity.)
-        const bool from_global = (o & kWinFlag) != 0u;
-        const bool swap = (((ob >> 6) & 1u) != (uint32_t)usel) && !from_global;
-        if (swap) w = make_uint2(__byte_perm(w.x, 0u, 0x1032), __byte_perm(w.y, 0u, 0x1032));
-        const uint32_t sp = wbase + ob;
-        const uint32_t s1 = swap ? sp + 64u : sp, s2 = swap ? sp : sp + 64u;
-        if (!__any_sync(0xffffffffu, from_global)) {
-          // the usual case: every lane of the warp reads the window
-          qd[p][0] = lds16(s1, tok);
-          qd[p][1] = lds16(s2, tok);
-          qd[p][2] = lds16(s1 + win_rb, tok);
-          qd[p][3] = lds16(s2 + win_rb, tok);
-        } else {
-          const char *base = gbase + ob;
-          qd[p][0] = ld16_either(from_global, base, s1, tok);
-          qd[p][1] = ld16_either(from_global, base + Cb, s2, tok);
-          qd[p][2] = ld16_either(from_global, base + Rb, s1 + win_rb, tok);
-          qd[p][3] = ld16_either(from_global, base + Rb + Cb, s2 + win_rb, tok);
-        }
-      } else {
-        const char *base = gbase + ob;
-        qd[p][0] = ld16_global(base, tok);
-        qd[p][1] = ld16_global(base + Cb, tok);
-        qd[p][2] = ld16_global(base + Rb, tok);
-        qd[p][3] = ld16_global(base + Rb + Cb, tok);
-      }
-      wq2[p] = w;
-    };
-    auto blend_store = [&](uint32_t stage_addr, int p) {
-      uint4 w = table_weights<MODE>(wq2[p]);
-      w.x |= tok;  // tok is 0: pins the blend behind the loads issued before it
-      uint4 r;
-      if constexpr (MODE == kModeBf16) r = blend8_bf16(w, qd[p][0], qd[p][1], qd[p][2], qd[p][3]);
-      else r = blend8_f16(w, qd[p][0], qd[p][1], qd[p][2], qd[p][3]);
-      sts16(stage_addr + (uint32_t)(p * kRowsPerPass * 128), r);
-    };
-    // What the loads of the k-stage at the current position need: its table segment(s) and
-    // the windows of both its units (unit B's are the later ones).
-    auto acquire = [&]() -> bool {
-      uint32_t hcB = (uint32_t)hcA, runB = runA;
-      if (tapA + 1 == T && 2 * s + 1 < tp.U) {
-        ++hcB;
-        if (inrunA + 1u == span) ++runB;
-      }
-      if (seg_per_stage) {
-        if (!mbar_wait2(tab_full + 8 * slotS, phS, 12)) return false;
-      } else {
-        while (seg_acq <= seg_base + runB) {
-          if (!mbar_wait2(tab_full + 8 * (seg_acq & 1u), (seg_acq >> 1) & 1u, 12)) return false;
-          ++seg_acq;
-        }
-      }
-      if (kWin) {
-        while (win_acq <= win_base + hcB) {
-          if (!mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13)) return false;
-          ++win_acq;
-        }
-      }
-      return true;
-    };
-
-    bool valid = item < items;
-    if (valid) {
-      enter_item();
-      ok = acquire();
-      pt.lap(2);
-      if (ok) { enter_stage(); issue(0); }
-    }
-    while (valid && ok) {
+      const bool v1_dead = key < 0 || hc * 32 + 8 * (int)q1 >= g.Cg;
+      const bool v2_dead = key < 0 || hc * 32 + 8 * (int)q2 >= g.Cg;
+      pt.lap(0);
+      ok = mbar_wait2(empty_a + 8 * sa, pa ^ 1u, 8);
+      pt.lap(3);
+      if (!ok) break;
+      const uint32_t stage_row = a_row + sa * (uint32_t)kTileBytes;
+#pragma unroll 1
+      for (int p = 0; p < 2; ++p) {
+        // the vector's entry: weights and offset (both vectors share it unless their deform
+        // groups differ)
+        const uint32_t e = e0 + (uint32_t)(p * 64);
+        const uint32_t dst = stage_row + (uint32_t)(p * 64 * 128);
+        // the lane's two vectors, one after the other (they share the entry unless their deform
+        // groups differ)
 #pragma unroll
-      for (int p = 1; p < kPasses2; ++p) issue(p);
-      // Every read of the finishing stage's table entries has been issued.
-      const uint32_t cur_sa = sa | (pa << 8);   // ring slot and phase of the finishing stage
+        for (int k = 0; k < 2; ++k) {
+          const uint32_t q = k ? q2 : q1, eq = k ? eq2 : eq1;
+          const bool dead = k ? v2_dead : v1_dead;
+          uint32_t tok = 0;
+          uint4 X[4];
+          uint2 w = make_uint2(0u, 0u);
+          uint32_t o = dead_o;
+          if (!dead) { w = lds8(tabw_addr + (e + eq) * 8u); o = lds4(tabo_addr + (e + eq) * 4u); }
+          const bool fg = (o & kWinFlag) != 0u;
+          const uint32_t ob = (o & ~kWinFlag) + 16u * q;
+          if constexpr (kWin) {
+            // The lanes of unit 0 start with the even 64-byte slot of their left/right pair
+            // and those of unit 1 with the odd one (the window's row pitch is an even number
+            // of slots, so the bottom corners repeat the parity): with the rows' vector order,
+            // the eight lanes of a quarter warp cover all 32 banks.
+            const bool sw = (((o >> 6) & 1u) != (uint32_t)usel) && !fg;
+            if (sw) w = make_uint2(__byte_perm(w.x, 0u, 0x1032), __byte_perm(w.y, 0u, 0x1032));
+            const uint32_t sp = wbase + ob;
+            const uint32_t sa_ = sw ? sp + 64u : sp, sb_ = sw ? sp : sp + 64u;
+            if (!__any_sync(0xffffffffu, fg)) {
+              // the usual case: every lane of the warp reads the window
+              X[0] = lds16(sa_, tok); X[1] = lds16(sb_, tok);
+              X[2] = lds16(sa_ + win_rb, tok); X[3] = lds16(sb_ + win_rb, tok);
+            } else {
+              const char *b = gbase + ob;
+              X[0] = ld16_either(fg, b, sa_, tok); X[1] = ld16_either(fg, b + Cb, sb_, tok);
+              X[2] = ld16_either(fg, b + Rb, sa_ + win_rb, tok);
+              X[3] = ld16_either(fg, b + Rb + Cb, sb_ + win_rb, tok);
+            }
+          } else {
+            const char *b = gbase + ob;
+            X[0] = ld16_global(b, tok); X[1] = ld16_global(b + Cb, tok);
+            X[2] = ld16_global(b + Rb, tok); X[3] = ld16_global(b + Rb + Cb, tok);
+          }
+          uint4 wa = table_weights<MODE>(w);
+          wa.x |= tok;  // tok is 0: keeps the blend behind the loads
+          uint4 r;
+          if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
+          else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
+          sts16(dst + ((k ? a_c2 : a_c1) << 4), r);
+        }
+      }
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(full_a + 8 * sa);
+      pt.lap(4);
+      // ---- hand back what the group is done with, move on by kGroups2 stages
       if (seg_per_stage) {
-        // its segment goes back to the builders
-        __syncwarp();
         if (lane == 0) mbar_arrive(tab_empty + 8 * slotS);
-        if (++slotS == (uint32_t)RS) { slotS = 0; phS ^= 1u; }
+        slotS += (uint32_t)kGroups2;
+        while (slotS >= (uint32_t)RS) { slotS -= (uint32_t)RS; phS ^= 1u; }
       }
-      // move the position to the next stage
-      if (++sa == (uint32_t)A) { sa = 0; pa ^= 1u; }
-      tapA += 2;
-      while (tapA >= T) {
-        tapA -= T; ++hcA;
-        if (++inrunA == span) { inrunA = 0; ++runA; }
+      sa += (uint32_t)kGroups2;
+      while (sa >= (uint32_t)A) { sa -= (uint32_t)A; pa ^= 1u; }
+      s += kGroups2;
+      if (s < tp.S) {
+        tapA += 2 * kGroups2;
+        while (tapA >= T) {
+          tapA -= T; ++hcA;
+          if (++inrunA == span) { inrunA = 0; ++runA; }
+        }
+      } else {
+        normalise();
       }
-      if (++s == tp.S) {
-        s = 0; hcA = 0; tapA = 0; runA = 0; inrunA = 0;
-        win_base += (uint32_t)KH;
-        seg_base += (uint32_t)nseg;
-        item += gridDim.x;
-        valid = item < items;
-        if (valid) enter_item();
-      }
+      const bool more = item < items;
       if (!seg_per_stage) {
         // run segments before the next stage's first unit go back to the builders
-        const uint32_t seg_keep = valid ? seg_base + runA : seg_acq;
+        const uint32_t seg_keep = more ? seg_base + runA : seg_acq;
         if (seg_rel < seg_keep) {
-          __syncwarp();
           if (lane == 0)
             for (uint32_t i = seg_rel; i < seg_keep; ++i) mbar_arrive(tab_empty + 8 * (i & 1u));
           seg_rel = seg_keep;
         }
       }
-      pt.lap(4);
-      ok = mbar_wait2(empty_a + 8 * (cur_sa & 0xffu), (cur_sa >> 8) ^ 1u, 8);
-      pt.lap(3);
-      if (!ok) break;
-      const uint32_t cur_addr = a_base + (cur_sa & 0xffu) * (uint32_t)kTileBytes;
-      blend_store(cur_addr, 0);
-      if (valid) {
-        pt.lap(4);
-        ok = acquire();
-        pt.lap(2);
-        if (!ok) break;
-        enter_stage();
-        issue(0);
-      }
-#pragma unroll
-      for (int p = 1; p < kPasses2; ++p) blend_store(cur_addr, p);
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(full_a + 8 * (cur_sa & 0xffu));
       if (kWin) {
-        // all loads from the windows before the next stage's first unit have returned (their
-        // values were consumed above): those windows go back to the loader
-        const uint32_t win_keep = valid ? win_base + (uint32_t)hcA : win_acq;
+        // windows before the next stage's first unit go back to the loader (the loads from
+        // them have returned: their values were consumed above)
+        const uint32_t win_keep = more ? win_base + (uint32_t)hcA : win_acq;
         if (win_rel < win_keep) {
           if (lane == 0)
             for (uint32_t i = win_rel; i < win_keep; ++i) mbar_arrive(win_empty + 8 * (i & 1u));
@@ -987,6 +965,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         }
       }
     }
+    (void)zero_vec;
     if (!ok) *abort_s = 1;
   }
 

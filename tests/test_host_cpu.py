@@ -62,10 +62,10 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
-    # 16-bit tensors run on the second-generation kernel: 4 epilogue + MMA + loader + 2 table
+    # 16-bit tensors run on the second-generation kernel: 4 epilogue + MMA + 2 loaders + 4 table
     # builder + 16 gather warps.  Every 64-channel chunk has deform groups of its own here, so
     # a table segment serves one k-stage.
-    assert info.kernel_version == 2 and info.producer_layout == 2016 and info.block == 24 * 32
+    assert info.kernel_version == 2 and info.producer_layout == 4016 and info.block == 28 * 32
     assert info.table_span == 0 and info.table_slots >= 4
     assert info.operand_stages >= 2 and info.weight_stages == 2
     rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
