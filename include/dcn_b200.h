@@ -110,12 +110,12 @@ typedef struct DcnPlanInfo {
   int32_t operand_stages, weight_stages; /* depth of the two shared-memory rings (tcgen05 path) */
   int32_t producer_layout; /* tcgen05 path, first-generation kernel: groups*100 + warps per
                             * group*10 + rows in flight, +1000 rows software-pipelined, +2000
-                            * per-group tap tables; second generation: 4016 (4 table-builder
-                            * warps, 16 gather warps) */
+                            * per-group tap tables; second generation: 16 (gather warps, which
+                            * build their own tap entries) */
   int32_t kernel_version;  /* tcgen05 path: 1 = first-generation kernel (3xTF32), 2 = second generation, 16-bit operands */
   int32_t window_h, window_w; /* input window kept in shared memory, pixels (0: none) */
-  int32_t table_span;      /* channel chunks served by one tap-table segment (0: one k-stage) */
-  int32_t table_slots;     /* ring depth of the tap table */
+  int32_t table_span;      /* (unused: 0) */
+  int32_t table_slots;     /* (unused: 0) */
   int32_t epilogue_tensor_stores; /* 1: output written by cp.async.bulk.tensor stores */
 } DcnPlanInfo;
 

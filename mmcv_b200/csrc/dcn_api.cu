@@ -61,7 +61,6 @@ struct Knobs {
   int kernel;      // 1: first-generation tensor-core kernel for every mode, 2: default routing
   int window;      // -1: planner's choice, 0: no shared-memory input window, n: margin n
   int epi_tma;     // -1: planner's choice, 0/1
-  int tab_slots;   // 0: planner's choice
   int small_l1;    // 1: give the kernel the largest shared-memory configuration
 };
 const Knobs &knobs() {
@@ -77,7 +76,6 @@ const Knobs &knobs() {
     k.kernel = env_int("DCN_B200_KERNEL", 2, 1, 2);
     k.window = env_int("DCN_B200_WINDOW", -1, -1, 16);
     k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
-    k.tab_slots = env_int("DCN_B200_TAB_SLOTS", 0, 0, 16);
     k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
     g_debug_flags.store(env_int("DCN_B200_DEBUG_FLAGS", 0, 0, 255));
   });
@@ -200,46 +198,24 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   if (tp->items >= 2147483647LL) return;
   TcPlan t = *tp;
   t.version = 2;
-  t.producer_cfg = 4016;  // 4 table-builder warps, 16 gather warps
+  t.producer_cfg = 16;  // 16 gather warps that build their own tap entries
   // K units: (32-channel half-chunk, tap), half-chunk-major; two per k-stage
   t.KH = (g.Cg + 31) / 32;
   t.U = t.KH * g.T;
   t.S = (t.U + 1) / 2;
-  // Table segments.  Half-chunks with the same single deform group share their table entries:
-  // when every tile splits into runs of L >= 2 such half-chunks, one segment (a block per tap)
-  // serves a run and the ring holds two of them; otherwise a segment serves one k-stage (two
-  // units, a block per unit and deform group).
-  int run = -1, ndu = 1;
-  bool uniform = true;
-  for (int grp = 0; grp < g.groups; ++grp) {
-    int prev_lo = -1, prev_nd = 0, len = 0;
-    for (int hc = 0; hc <= t.KH; ++hc) {
-      int lo = -2, nd = 0;
-      if (hc < t.KH) {
-        const int c0 = grp * g.Cg + hc * 32;
-        const int c1 = c0 + 32 < (grp + 1) * g.Cg ? c0 + 32 : (grp + 1) * g.Cg;
-        lo = c0 / g.cpdg;
-        nd = (c1 - 1) / g.cpdg - lo + 1;
-        if (nd > ndu) ndu = nd;
-      }
-      if (lo == prev_lo && nd == prev_nd && nd == 1) { ++len; continue; }
-      if (len > 0) {
-        if (run < 0) run = len;
-        else if (run != len) uniform = false;
-      }
-      prev_lo = lo; prev_nd = nd; len = 1;
+  // A unit must lie inside one deform group (every lane builds the tap entry of one (row, unit)
+  // pair): deform groups that start or end inside a 32-channel half-chunk go to the
+  // first-generation kernel.
+  for (int grp = 0; grp < g.groups; ++grp)
+    for (int hc = 0; hc < t.KH; ++hc) {
+      const int c0 = grp * g.Cg + hc * 32;
+      const int c1 = c0 + 32 < (grp + 1) * g.Cg ? c0 + 32 : (grp + 1) * g.Cg;
+      if (c0 / g.cpdg != (c1 - 1) / g.cpdg) return;
     }
-  }
-  if (ndu > 8) return;
-  t.ndu = ndu;
-  const size_t entry = 12;  // bytes of a table entry
-  t.tab_span = (uniform && run >= 2 && ndu == 1 && t.KH % run == 0 &&
-                (size_t)2 * g.T * (kBM + 4) * entry <= 60 * 1024) ? run : 0;
-  t.tab_slot_blocks = t.tab_span ? g.T : 2 * ndu;
-  // (stage segments: an even ring of at least six slots, so that a slot always serves the same
-  // gather group and no builder warp meets a slot two uses after its last visit)
-  t.tab_slots = t.tab_span ? 2 : (kn.tab_slots >= 6 ? kn.tab_slots / 2 * 2 : 6);
-  if ((size_t)t.tab_slots * t.tab_slot_blocks * (kBM + 4) * entry > 64 * 1024) return;
+  // (the kernel keeps two small lookup tables: up to 64 taps and 1024 half-chunks over all groups)
+  if (g.T > 64 || g.groups * t.KH > 1024) return;
+  t.ndu = 1;
+  t.tab_span = t.tab_slots = t.tab_slot_blocks = 0;
   // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles
   // whose 32-channel slabs never reach into another tile's channels.
   {
@@ -250,13 +226,19 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     const int want = kn.epi_tma < 0 ? 0 : kn.epi_tma;
     t.epi_tma = (want && aligned && slabs_ok && g.N > 0) ? 1 : 0;
   }
+  t.raw_slots = 0;
   // Input window in shared memory: the tile's undeformed footprint plus a margin of m pixels
   // on every side, 32 channels, two buffers.  Largest margin (up to 6) that fits wins; the
   // width is rounded up to an even number of pixels (bank rule of the paired reads).
   const int th = kBM >> t.tw_log2, tw = 1 << t.tw_log2;
   const int fh = (th - 1) * g.stride_h + (g.kh - 1) * g.dil_h + 2;  // + the lower/right corner
   const int fw = (tw - 1) * g.stride_w + (g.kw - 1) * g.dil_w + 2;
-  const int m_max = kn.window < 0 ? 0 : kn.window;
+  // Used when the convolution has unit stride (deformable layers of detection backbones: small
+  // learned offsets around a dense footprint); a strided layer samples too widely for a window
+  // of this size and stays on the first-generation kernel, as does a problem whose window
+  // would have a margin of less than three pixels.
+  const bool auto_win = g.stride_h == 1 && g.stride_w == 1;
+  const int m_max = kn.window < 0 ? (auto_win ? 6 : 0) : kn.window;
   bool found = false;
   for (int m = m_max; m >= 0 && !found; --m) {
     t.win_h = m ? fh + 2 * m : 0;
@@ -267,7 +249,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     // configuration if possible
     const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
     for (int bi = (m || kn.small_l1) ? 1 : 0; bi < 2 && !found; ++bi)
-      for (int as = m ? 3 : 4; as >= 2 && !found; --as) {
+      for (int as = 4; as >= 2 && !found; --as) {
         if (kn.a_stages && as != kn.a_stages) continue;
         t.a_stages = as;
         t.b_stages = kn.b_stages ? kn.b_stages : 2;
@@ -276,6 +258,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
       }
   }
   if (!found) return;
+  if (kn.window < 0 && t.win_my < 3) return;   // no useful window: first-generation kernel
   *tp = t;
 }
 

@@ -70,6 +70,7 @@ struct TcPlan {
   int win_h, win_w;        // input window held in shared memory, in pixels (0: none)
   int win_my, win_mx;      // its margin above / left of the tile's undeformed footprint
   int epi_tma;             // 1: the epilogue stores through the tensor-copy engine
+  int raw_slots;           // ring depth of offset / mask planes staged for the builders (0: none)
 };
 
 enum { kBM = 128 };

@@ -1103,7 +1103,7 @@ cudaError_t launch_io(const TcArgs &a, const TcPlan &tp, cudaStream_t s) {
 }  // namespace
 
 int tc_threads(const TcPlan &tp) {
-  if (tp.version == 2) return 896;  // dcn_fwd_tc2: 4 epilogue, MMA, 2 loaders, (1 idle,) 4 builder and 16 gather warps
+  if (tp.version == 2) return 768;  // dcn_fwd_tc2: 4 epilogue, MMA, 2 loaders, 1 idle and 16 gather warps
   return (kFirstProducerWarp + ((tp.producer_cfg / 100) % 10) * ((tp.producer_cfg / 10) % 10)) * 32;
 }
 

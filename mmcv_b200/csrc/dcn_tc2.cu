@@ -4,18 +4,16 @@
 // Same contraction as dcn_fwd_tc (out[p, co] = sum_k A[p, k] * Wt[co, k], A never written to
 // global memory; it replaces the gather kernel, the per-sample GEMM loop and the bias pass of
 // mmcv/ops/csrc/common/cuda/modulated_deform_conv_cuda_kernel.cuh:186-245 and
-// mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:108-137), with the producer side split into
-// two decoupled roles:
+// mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:108-137), with a different producer side:
 //
-//   * table builders (4 warps; a warp owns every fourth table segment and fills its blocks of
-//     128 entries, four rows per thread) turn offsets and
-//     masks into tap-table entries -- four 16-bit corner weights with the modulation folded
-//     in, and the byte offset of the top-left corner -- and publish them through a ring of
-//     table segments in shared memory.  They run ahead of the gather, which therefore never
-//     waits for an offset or a mask.
-//   * gather warps (16, in two groups that fill alternate k-stages) read an entry, fetch the
-//     four corners, blend them on packed 16-bit FMAs and write the 128-byte-swizzled operand
-//     tile tcgen05.mma reads; a thread blends 16 channels of one (row, unit).  The input is a
+//   * gather warps (16, in two groups that fill alternate k-stages): a warp covers 16 rows of
+//     a stage (two passes of eight), i.e. 32 (row, unit) pairs, and each of its lanes turns
+//     the offsets and mask of ONE of them into a tap entry -- four 16-bit corner weights with
+//     the modulation folded in, and the byte offset of the top-left corner -- one own stage
+//     ahead, from loads issued another stage earlier; the lanes that gather a pair fetch its
+//     entry by warp shuffle.  A lane fetches the four corners, blends them on packed 16-bit
+//     FMAs and writes the 128-byte-swizzled operand tile tcgen05.mma reads; it blends 16
+//     channels of one (row, unit).  No tap table exists in memory.  The input is a
 //     channels-last copy with a one-pixel zero border around every sample: a corner outside
 //     the image reads zeros, a sample outside the sampling gate points at an all-zero
 //     neighbourhood with zero weights, so the loads carry no predicates and a corner inside
@@ -48,23 +46,17 @@ namespace {
 constexpr int kEpiWarps = 4;
 constexpr int kMmaWarp2 = 4;
 constexpr int kLoadWarp2 = 5;
-constexpr int kWinWarp = 6;   // (warp 7 idles: the builders are a warpgroup of their own)
-constexpr int kFirstBuildWarp = 8;
-constexpr int kBuildWarps = 4;
-constexpr int kFirstGatherWarp = kFirstBuildWarp + kBuildWarps;
+constexpr int kWinWarp = 6;   // (warp 7 idles)
+constexpr int kFirstGatherWarp = 8;
 constexpr int kGatherWarps = 16;
-constexpr int kThreads2 = (kFirstGatherWarp + kGatherWarps) * 32;  // 896 = 7 warpgroups: epilogue | MMA, weight loader, window loader, - | 4 builders | 4 x gather
+constexpr int kThreads2 = (kFirstGatherWarp + kGatherWarps) * 32;  // 768: six warps per scheduler, 80 registers per thread
 constexpr int kGroups2 = 2;                              // gather groups; group i fills k-stages i, i + 2, ...
 constexpr int kWarpsPerGroup = kGatherWarps / kGroups2;  // 8 warps: 64 rows per pass, two passes per stage
-constexpr int kTabStride2 = kBM + 8;  // entries of one (unit / tap, deform group) block; the skew puts the
-                                      // blocks of a stage's two units into different bank halves
-constexpr uint32_t kWinFlag = 0x80000000u;  // table entry: the neighbourhood is read from global memory
 
 // Register budget per role (setmaxnreg works on warpgroups of four consecutive warps; the
-// block starts with 72 registers per thread): the two warpgroups that hold the epilogue and the
-// MMA / loader warps give registers back, the four gather warpgroups take them, the builders
-// keep theirs.
-constexpr int kRegsLight = 56, kRegsGather = 80;
+// block starts with 80 registers per thread): the two warpgroups that hold the epilogue and the
+// MMA / loader warps give registers back, the four gather warpgroups take them.
+constexpr int kRegsLight = 64, kRegsGather = 88;
 template <int N>
 __device__ __forceinline__ void reg_dec() {
   asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
@@ -107,20 +99,6 @@ __device__ __forceinline__ uint4 lds16(uint32_t addr, uint32_t &tok) {
   asm volatile("" : "+r"(tok));
   return r;
 }
-// One lane reads global memory, another the shared-memory window: the same 16-byte load, in
-// the lane's own state space.
-__device__ __forceinline__ uint4 ld16_either(bool from_global, const void *gp, uint32_t sp, uint32_t &tok) {
-  uint4 r;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.u32 p, %6, 0;\n\t"
-      "@p ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n\t"
-      "@!p ld.shared.v4.u32 {%0, %1, %2, %3}, [%5];\n\t}"
-      : "=&r"(r.x), "=&r"(r.y), "=&r"(r.z), "=&r"(r.w)
-      : "l"(gp), "r"(sp), "r"((uint32_t)from_global), "r"(tok));
-  asm volatile("" : "+r"(tok));
-  return r;
-}
 __device__ __forceinline__ void sts16(uint32_t addr, const uint4 &v) {
   asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
@@ -128,17 +106,18 @@ __device__ __forceinline__ void sts16(uint32_t addr, const uint4 &v) {
 }
 
 
-// Shared memory: a 1 KiB control block first (barriers, tensor-memory slot, abort flag, the
+// Shared memory: a control block first (barriers, tensor-memory slot, abort flag, the
 // wait limit and the status pointer: at fixed offsets, so that the out-of-line slow path of a
 // wait finds them without arguments), then the rings.
-constexpr uint32_t kCtrlBytes = 1024;
+constexpr uint32_t kCtrlBytes = 4096;   // 1 KiB of fixed fields and barriers, then the two lookup tables
 constexpr uint32_t kCtrlTmemSlot = 512, kCtrlAbort = 520, kCtrlLimit = 528, kCtrlStatus = 536;
+// lookup tables (built once per block): tap -> sampling displacement (dy, dx) as floats, and
+// (conv group, half-chunk) -> deform group
+constexpr uint32_t kLutTapBytes = 2 * 4 * 64;   // up to 64 taps (then 1024 half-chunk entries of 2 bytes)
 
 struct Smem2 {
   uint8_t *a, *b, *win;
   uint8_t *epi;        // staging of the epilogue's tensor stores
-  uint8_t *tab_w;      // four 16-bit corner weights per entry (8 bytes)
-  uint8_t *tab_off;    // byte offset of the top-left corner (bit 31: from global memory)
   uint8_t *bias_s;
 };
 
@@ -159,9 +138,6 @@ __device__ __forceinline__ Smem2 carve2(uint8_t *base, const TcPlan &tp) {
   L.b = p; p += (size_t)tp.b_stages * tp.BN * 128;
   L.win = p; p += 2 * win_bytes(tp);
   L.epi = p; p += epi_bytes(tp);
-  const size_t ents = (size_t)tp.tab_slots * tp.tab_slot_blocks * kTabStride2;
-  L.tab_w = p; p += ents * 8;
-  L.tab_off = p; p += ents * 4;
   L.bias_s = (uint8_t *)(((uintptr_t)p + 15) & ~(uintptr_t)15);
   return L;
 }
@@ -192,22 +168,6 @@ __device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int co
   return mbar_wait_slow2(bar, parity, code, backoff);
 }
 
-__device__ __forceinline__ uint2 lds8(uint32_t addr) {
-  uint2 v;
-  asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ uint32_t lds4(uint32_t addr) {
-  uint32_t v;
-  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts8(uint32_t addr, uint32_t x, uint32_t y) {
-  asm volatile("st.shared.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void sts4(uint32_t addr, uint32_t x) {
-  asm volatile("st.shared.u32 [%0], %1;" ::"r"(addr), "r"(x) : "memory");
-}
 
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
@@ -286,25 +246,23 @@ size_t tc2_smem_bytes(const TcPlan &tp) {
   size_t s = 1024 + kCtrlBytes;  // slack for manual 1024-byte alignment, control block
   s += (size_t)tp.a_stages * kTileBytes + (size_t)tp.b_stages * tp.BN * 128;
   s += 2 * win_bytes(tp) + epi_bytes(tp);
-  s += (size_t)tp.tab_slots * tp.tab_slot_blocks * kTabStride2 * 12;
   s += (size_t)2 * tp.BN * tp.io_bytes + 32;  // bias staging, one copy per accumulator buffer
   return s;
 }
 
-template <typename TIO, int MODE, bool kWin, bool kSegStage>
+template <typename TIO, int MODE, bool kWin>
 __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constant__ Tc2Args a) {
   uint8_t *smem = smem_aligned();
   const Geom &g = a.g;
   const TcPlan &tp = a.tp;
   const Smem2 L = carve2(smem, tp);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int A = tp.a_stages, B = tp.b_stages, RS = tp.tab_slots;
+  const int A = tp.a_stages, B = tp.b_stages;
   const uint32_t bar0 = smem_u32(smem);
   // barrier i lives at bar0 + 8*i
   const uint32_t full_a = bar0, empty_a = full_a + 8 * A, full_b = empty_a + 8 * A,
                  empty_b = full_b + 8 * B, tmem_full = empty_b + 8 * B, tmem_empty = tmem_full + 16,
-                 tab_full = tmem_empty + 16, tab_empty = tab_full + 8 * RS,
-                 win_full = tab_empty + 8 * RS, win_empty = win_full + 16;
+                 win_full = tmem_empty + 16, win_empty = win_full + 16;
   volatile int *abort_s = (volatile int *)(smem + kCtrlAbort);
   const uint32_t b_stage_bytes = (uint32_t)tp.BN * 128u;
 
@@ -323,14 +281,23 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       mbar_init(win_full + 8 * i, 1);
       mbar_init(win_empty + 8 * i, kGatherWarps);
     }
-    for (int i = 0; i < RS; ++i) {
-      mbar_init(tab_full + 8 * i, kSegStage ? 1 : kBuildWarps);   // the segment's owner, or all builders
-      mbar_init(tab_empty + 8 * i, kSegStage ? kWarpsPerGroup : kGatherWarps);
-    }
     *abort_s = 0;
     *(unsigned long long *)(smem + kCtrlLimit) = a.wait_limit_ns;
     *(int **)(smem + kCtrlStatus) = a.status;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  {
+    float *lut_tap = reinterpret_cast<float *>(smem + 1024);
+    unsigned short *lut_dg = reinterpret_cast<unsigned short *>(smem + 1024 + kLutTapBytes);
+    for (int i = threadIdx.x; i < g.T; i += blockDim.x) {
+      const int ti = i / g.kw, tj = i - ti * g.kw;
+      lut_tap[2 * i] = (float)(ti * g.dil_h);
+      lut_tap[2 * i + 1] = (float)(tj * g.dil_w);
+    }
+    for (int i = threadIdx.x; i < g.groups * tp.KH; i += blockDim.x) {
+      const int grp = i / tp.KH, hc = i - grp * tp.KH;
+      lut_dg[i] = (unsigned short)((grp * g.Cg + hc * 32) / g.cpdg);
+    }
   }
   if (warp == kMmaWarp2) {
     tmem_alloc(smem_u32(smem + kCtrlTmemSlot), (uint32_t)tp.tmem_cols);
@@ -346,16 +313,12 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
   const int tw_mask = (1 << tp.tw_log2) - 1;
   const int T = g.T;
   // K is walked in units of (32-channel half-chunk, tap), half-chunk-major; a k-stage holds two
-  // consecutive units (64 bytes each of the operand row).
-  // table segments: one per k-stage (tab_span == 0: two units, ndu deform groups each), or one
-  // per run of tab_span half-chunks that share their single deform group (one block per tap)
-  constexpr bool seg_per_stage = kSegStage;
-  const uint32_t slot_entries = (uint32_t)tp.tab_slot_blocks * kTabStride2;
+  // consecutive units (64 bytes each of the operand row).  A unit lies inside one deform group.
   const uint32_t Wp = (uint32_t)g.W + 2u;
   const uint32_t Cb = (uint32_t)g.C * 2u;       // bytes of one padded pixel
   const uint32_t Rb = Wp * Cb;                  // bytes of one padded row
 
-  if (warp < kFirstBuildWarp) {
+  if (warp < kFirstGatherWarp) {
   reg_dec<kRegsLight>();
   if (warp < kEpiWarps) {
     // ------------------------------ epilogue ------------------------------
@@ -571,401 +534,267 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     }
     __syncwarp();
   }
-  } else if (warp < kFirstGatherWarp) {
-    // ------------------------------ table builders ------------------------------
-    // A block = the 128 entries of one (unit or tap, deform group): four rows per thread.
-    const int bw = warp - kFirstBuildWarp;
-    const TIO *off = (const TIO *)a.offset;
-    const TIO *msk = (const TIO *)a.mask;
-    const uint32_t dead_off = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;  // an all-zero 2x2 neighbourhood
-    const bool dense_planes = g.off_ps == 1 && g.msk_ps == 1 && g.off_cs == plane && g.msk_cs == plane;
-    const int wh = tp.win_h, ww = tp.win_w;
-    const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)lane * 8u;
-    const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)lane * 4u;
-    bool ok = true;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && bw == 0 && lane == 0);
-    const uint32_t nseg = seg_per_stage ? (uint32_t)tp.S : (uint32_t)(tp.KH / tp.tab_span);  // segments per tile
-
-    // Ask L2 for a quarter (this warp's) of the offset and mask planes of tile `nitem` (dense
-    // planes only).
-    auto prefetch_tile = [&](uint32_t nitem) {
-      if (!dense_planes || nitem >= items) return;
-      const TileId2 nt_ = decode_item2(nitem, g, tp);
-      const int lr_log2 = max(0, tp.tw_log2 + (sizeof(TIO) == 4 ? 2 : 1) - 7);
-      const int pp_log2 = (7 - tp.tw_log2) + lr_log2;  // 128-byte lines per plane of the tile
-      const int planes_off = off ? g.dg * 2 * T : 0;
-      const int planes = planes_off + (msk ? g.dg * T : 0);
-      const TIO *obase = off ? off + (long long)nt_.n * g.off_sn : nullptr;
-      const TIO *mbase = msk ? msk + (long long)nt_.n * g.msk_sn : nullptr;
-      for (int idx = bw * 32 + lane; idx < (planes << pp_log2); idx += kBuildWarps * 32) {
-        const int pl = idx >> pp_log2, r = idx & ((1 << pp_log2) - 1);
-        const int ry = r >> lr_log2, rl = r & ((1 << lr_log2) - 1);
-        const int ho = nt_.ho0 + ry;
-        if (ho >= g.Ho) continue;
-        const long long pixel = (long long)ho * g.Wo + nt_.wo0;
-        const TIO *ptr = pl < planes_off ? obase + (long long)pl * plane + pixel
-                                         : mbase + (long long)(pl - planes_off) * plane + pixel;
-        if (nt_.wo0 + rl * (int)(128 / sizeof(TIO)) < g.Wo)
-          prefetch_l2(reinterpret_cast<const char *>(ptr) + rl * 128);
-      }
-    };
-
-    uint32_t cur_item = 0xffffffffu;
-    TileId2 t = {0, 0, 0, 0, 0};
-    int wy0 = 0, wx0 = 0;
-    const TIO *offn = nullptr, *mskn = nullptr;
-    auto enter_tile = [&](uint32_t item) {
-      if (item == cur_item) return;
-      cur_item = item;
-      t = decode_item2(item, g, tp);
-      prefetch_tile(item + gridDim.x);
-      wy0 = win_y0(g, tp, t.ho0); wx0 = win_x0(g, tp, t.wo0);
-      offn = off ? off + (long long)t.n * g.off_sn : nullptr;
-      mskn = msk ? msk + (long long)t.n * g.msk_sn : nullptr;
-    };
-    // The 128 entries of table block `blk` of slot `slot`: tap (ti, tj) = `tap`, deform group dgi.
-    auto do_block = [&](uint32_t slot, uint32_t blk, int tap, int ti, int tj, int dgi) {
-      const float tif = (float)(ti * g.dil_h), tjf = (float)(tj * g.dil_w);
-      const TIO *ob = off ? offn + ((long long)dgi * 2 * T + 2 * tap) * g.off_cs : nullptr;
-      const TIO *mb = msk ? mskn + ((long long)dgi * T + tap) * g.msk_cs : nullptr;
-      const uint32_t e0 = slot * slot_entries + blk * kTabStride2;
-      // this thread's rows: lane, lane + 32, lane + 64, lane + 96, two at a time (the six loads
-      // of a pair in flight together)
-#pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t roh[2], row_[2], rmm[2];
-        float hbf[2], wbf[2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          const int r = lane + 64 * half + 32 * j;
-          const int ho = t.ho0 + (r >> tp.tw_log2), wo = t.wo0 + (r & tw_mask);
-          const bool rv = ho < g.Ho && wo < g.Wo;
-          // a row beyond the image reads pixel 0 and gets a position that fails the gate
-          const long long pix = rv ? (long long)ho * g.Wo + wo : 0;
-          hbf[j] = rv ? (float)(ho * g.stride_h - g.pad_h) + tif : -1.0e9f;
-          wbf[j] = (float)(wo * g.stride_w - g.pad_w) + tjf;
-          roh[j] = 0; row_[j] = 0; rmm[j] = 0;
-          if (off) {
-            const TIO *pp = ob + pix * g.off_ps;
-            roh[j] = ldg_raw_ordered(pp);
-            row_[j] = ldg_raw_ordered(pp + g.off_cs);
-          }
-          if (msk) rmm[j] = ldg_raw_ordered(mb + pix * g.msk_ps);
-        }
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-          float4 wt = make_float4(0.f, 0.f, 0.f, 0.f);
-          uint32_t eo = dead_off;
-          const float h_im = hbf[j] + RawOf<TIO>::to_float(roh[j]);
-          const float w_im = wbf[j] + RawOf<TIO>::to_float(row_[j]);
-          if (h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
-            const float m = msk ? mask_value(g, RawOf<TIO>::to_float(rmm[j])) : 1.f;
-            const float hf = floorf(h_im), wf = floorf(w_im);
-            const float lh = h_im - hf, lw = w_im - wf;
-            const float hh = 1.f - lh, hw = 1.f - lw;
-            wt.x = hh * hw * m; wt.y = hh * lw * m; wt.z = lh * hw * m; wt.w = lh * lw * m;
-            const int hl = (int)hf, wl = (int)wf;
-            // inside the shared-memory window: offset within the window (64 bytes per pixel);
-            // else (flagged) the offset within the padded sample
-            const uint32_t wy = (uint32_t)(hl - wy0), wx = (uint32_t)(wl - wx0);
-            if (kWin && wy < (uint32_t)(wh - 1) && wx < (uint32_t)(ww - 1))
-              eo = (wy * (uint32_t)ww + wx) * 64u;
-            else
-              eo = (((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb) | kWinFlag;
-          }
-          const uint32_t e = e0 + 64u * (uint32_t)half + 32u * (uint32_t)j;
-          sts8(tabw_addr + e * 8u, pack_weights2<MODE>(wt.x, wt.y), pack_weights2<MODE>(wt.z, wt.w));
-          sts4(tabo_addr + e * 4u, eo);
-        }
-      }
-    };
-    prefetch_tile(blockIdx.x);
-    if constexpr (kSegStage) {
-      // Stage segments: builder warp b owns the segments b, b + 4, ... (counted over all tiles
-      // of this block): it alone fills them and hands them over.  (The ring is deeper than the
-      // builders are many, so a warp never meets a slot two uses ahead of its last visit.)
-      uint32_t item = blockIdx.x, sg = (uint32_t)bw, q = (uint32_t)bw;
-      for (;; sg += (uint32_t)kBuildWarps, q += (uint32_t)kBuildWarps) {
-        while (item < items && sg >= nseg) { sg -= nseg; item += gridDim.x; }
-        if (item >= items || !ok) break;
-        enter_tile(item);
-        const uint32_t slot = q % (uint32_t)RS;
-        pt.lap(1);
-        ok = mbar_wait2(tab_empty + 8 * slot, ((q / (uint32_t)RS) & 1u) ^ 1u, 9);
-        pt.lap(6);
-        if (!ok) break;
-        // the segment's two consecutive (half-chunk, tap) units
-        const int n_u = min(2, tp.U - 2 * (int)sg);
-        int u_hc = (2 * (int)sg) / T, u_tap = 2 * (int)sg - u_hc * T;
-        for (int ui = 0; ui < n_u; ++ui) {
-          const int c0 = t.grp * g.Cg + u_hc * 32;
-          const int dg_lo = c0 / g.cpdg;
-          const int nd = (min(c0 + 32, (t.grp + 1) * g.Cg) - 1) / g.cpdg - dg_lo + 1;
-          const int ti = u_tap / g.kw;
-          for (int d = 0; d < nd; ++d)
-            do_block(slot, (uint32_t)(ui * tp.ndu + d), u_tap, ti, u_tap - ti * g.kw, dg_lo + d);
-          if (++u_tap == T) { u_tap = 0; ++u_hc; }
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tab_full + 8 * slot);
-      }
-    } else {
-      // Run segments (one block per tap, two slots): every builder warp visits every segment
-      // and fills every fourth block of it; all of them hand it over.
-      uint32_t q = 0;
-      for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
-        enter_tile(item);
-        for (uint32_t sg = 0; sg < nseg && ok; ++sg, ++q) {
-          const uint32_t slot = q & 1u;
-          pt.lap(1);
-          ok = mbar_wait2(tab_empty + 8 * slot, ((q >> 1) & 1u) ^ 1u, 9);
-          pt.lap(6);
-          if (!ok) break;
-          const int c0 = t.grp * g.Cg + (int)sg * tp.tab_span * 32;
-          const int dgi = c0 / g.cpdg;
-          for (int tap = bw; tap < T; tap += kBuildWarps) {
-            const int ti = tap / g.kw;
-            do_block(slot, (uint32_t)tap, tap, ti, tap - ti * g.kw, dgi);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(tab_full + 8 * slot);
-        }
-      }
-    }
-    if (!ok) *abort_s = 1;
   } else {
     // ------------------------------ gather ------------------------------
     reg_inc<kRegsGather>();
     // Group gi fills the k-stages gi, gi + 2, ... (counted over all tiles of this block).  A
     // stage is two passes of 64 rows; in a pass a warp covers eight rows and a lane blends the
     // 16 channels {q1, q2} x 8 of one (row, unit): lane = 4 * row + 2 * unit + p.
+    // Tap entries: the warp's 16 rows x 2 units of a stage are 32 (row, unit) pairs; lane
+    // 4 * row + 2 * unit + pass builds the entry of (row + 64 * pass, unit), which the two lanes
+    // 4 * row + 2 * unit + {0, 1} fetch by shuffle in pass `pass`.
     const int gw = warp - kFirstGatherWarp;
     const int gi = gw / kWarpsPerGroup, gwl = gw % kWarpsPerGroup;
     const int rr = lane >> 2;          // row within the warp's eight
     const int usel = (lane >> 1) & 1;  // which of the stage's two units
     const int row0 = gwl * 8 + rr;     // pass p: row0 + 64 p
+    const int brow = row0 + 64 * (lane & 1);   // the row whose entry this lane builds
     // Odd rows take their second vector first: the rows of a quarter warp then read (and
     // write) different bank quarters.
     const uint32_t q1 = (uint32_t)(lane & 1) ^ (uint32_t)((rr & 1) << 1), q2 = q1 ^ 2u;
     // operand tile: 16-byte chunk (4 * unit + q) of row r lives at chunk index ^ (r & 7)
     const uint32_t a_row = smem_u32(L.a) + (uint32_t)row0 * 128u;
-    const uint32_t a_c1 = ((uint32_t)(4 * usel) + q1) ^ (uint32_t)(row0 & 7);
-    const uint32_t a_c2 = ((uint32_t)(4 * usel) + q2) ^ (uint32_t)(row0 & 7);
+    const uint32_t a_c1 = (((uint32_t)(4 * usel) + q1) ^ (uint32_t)(row0 & 7)) << 4;
+    const uint32_t a_c2 = (((uint32_t)(4 * usel) + q2) ^ (uint32_t)(row0 & 7)) << 4;
     const char *xpad = reinterpret_cast<const char *>(a.xpad);
+    const TIO *off = (const TIO *)a.offset;
+    const TIO *msk = (const TIO *)a.mask;
     const uint32_t wbytes = (uint32_t)win_bytes(tp);
     const uint32_t win_rb = (uint32_t)tp.win_w * 64u;
     const uint32_t win_s = smem_u32(L.win);
-    const uint32_t tabw_addr = smem_u32(L.tab_w) + (uint32_t)row0 * 8u;
-    const uint32_t tabo_addr = smem_u32(L.tab_off) + (uint32_t)row0 * 4u;
     const int KH = tp.KH;
-    const uint32_t span = seg_per_stage ? 1u : (uint32_t)tp.tab_span;
-    const uint32_t nseg = seg_per_stage ? (uint32_t)tp.S : (uint32_t)KH / span;   // table segments per tile
-    const uint32_t dead_o = ((uint32_t)(g.H + 1) * Rb) | kWinFlag;   // an all-zero neighbourhood
 
-    // position: the k-stage (item, s) this group fills next; its unit A = 2 s is (half-chunk
-    // hcA, tap tapA); with run segments hcA is half-chunk inrunA of run runA
-    uint32_t item = blockIdx.x;
-    int s = gi, hcA = 0, tapA = 0;
-    uint32_t runA = 0, inrunA = 0;
-    uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = ((uint32_t)gi / (uint32_t)A) & 1u;
-    // running counts over the tiles of this block: window of (tile, half-chunk 0), table
-    // segment of (tile, run 0); table ring position of the current stage (stage segments)
-    uint32_t win_base = 0, seg_base = 0;
-    uint32_t slotS = (uint32_t)gi % (uint32_t)RS, phS = ((uint32_t)gi / (uint32_t)RS) & 1u;
-    // windows / run segments: next one to wait for, next one to hand back
-    uint32_t win_acq = 0, win_rel = 0, seg_acq = 0, seg_rel = 0;
-    bool ok = true;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
-
-    // unit A of stage s of a tile: (hcA, tapA) = divmod(2 s, T), and its run
-    auto locate = [&]() {
-      hcA = 0; tapA = 2 * s; runA = 0; inrunA = 0;
-      while (tapA >= T) {
-        tapA -= T; ++hcA;
-        if (++inrunA == span) { inrunA = 0; ++runA; }
-      }
+    const float *lut_tap = reinterpret_cast<const float *>(smem + 1024);
+    const unsigned short *lut_dg = reinterpret_cast<const unsigned short *>(smem + 1024 + kLutTapBytes);
+    // ---- position of a k-stage: tile, stage in the tile, its unit A = 2 s = (half-chunk, tap)
+    struct Pos {
+      uint32_t item;
+      int s, hcA, tapA;
     };
-    // tiles are skipped while the stage index runs past their end
-    auto normalise = [&]() {
-      while (item < items && s >= tp.S) {
-        s -= tp.S;
-        item += gridDim.x;
-        win_base += (uint32_t)KH;
-        seg_base += nseg;
+    uint32_t tiles_done = 0;   // tiles the position `nxt` has left behind
+    auto locate = [&](Pos &p) {
+      while (p.item < items && p.s >= tp.S) {
+        p.s -= tp.S;
+        p.item += gridDim.x;
+        ++tiles_done;
       }
-      locate();
+      p.hcA = 0; p.tapA = 2 * p.s;
+      while (p.tapA >= T) { p.tapA -= T; ++p.hcA; }
     };
-    normalise();
-    int my_hc = -2;
-    uint32_t my_item = 0xffffffffu;
-    const char *gbase = nullptr;   // sample + channel bytes of this lane's unit (global)
-    uint32_t wbase = 0;            // window buffer of the unit's half-chunk (shared address)
-    uint32_t e_fixed = 0;          // table entry of row0 without the stage's (or tap's) part
-    bool zero_vec = false;
-    const char *sbase = nullptr;
-    int grp = 0;
-
-    while (item < items && ok) {
-      // ---- what the stage needs: table segment(s), the windows of both its units
-      uint32_t hcB = (uint32_t)hcA, runB = runA;
-      if (tapA + 1 == T && 2 * s + 1 < tp.U) {
-        ++hcB;
-        if (inrunA + 1u == span) ++runB;
-      }
-      if (seg_per_stage) {
-        ok = mbar_wait2(tab_full + 8 * slotS, phS, 12);
+    auto advance = [&](Pos &p) {   // to the group's next stage
+      p.s += kGroups2;
+      if (p.s < tp.S) {
+        p.tapA += 2 * kGroups2;
+        while (p.tapA >= T) { p.tapA -= T; ++p.hcA; }
       } else {
-        while (ok && seg_acq <= seg_base + runB) {
-          ok = mbar_wait2(tab_full + 8 * (seg_acq & 1u), (seg_acq >> 1) & 1u, 12);
-          ++seg_acq;
+        locate(p);
+      }
+    };
+    // ---- the tile of position `nxt`, decoded when it changes: what the entry of this lane's
+    // (row, unit) needs, and what the gather of that tile needs later
+    uint32_t t_item = 0xffffffffu;
+    int t_grp = 0, t_wy0 = 0, t_wx0 = 0;
+    const char *t_sbase = nullptr;          // the tile's sample in the padded copy
+    const TIO *t_off = nullptr, *t_msk = nullptr;   // the sample's offsets / masks at this lane's pixel
+    float t_hb = -1.0e9f, t_wb = 0.f;       // this lane's row: sampling position without tap and offset
+    auto enter_tile = [&](uint32_t item) {
+      t_item = item;
+      const TileId2 t = decode_item2(item, g, tp);
+      t_grp = t.grp;
+      t_wy0 = win_y0(g, tp, t.ho0); t_wx0 = win_x0(g, tp, t.wo0);
+      t_sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
+      const int ho = t.ho0 + (brow >> tp.tw_log2), wo = t.wo0 + (brow & tw_mask);
+      const bool rv = ho < g.Ho && wo < g.Wo;
+      // a row beyond the image gets a position that fails the sampling gate, and reads pixel 0
+      const long long pix = rv ? (long long)ho * g.Wo + wo : 0;
+      t_hb = rv ? (float)(ho * g.stride_h - g.pad_h) : -1.0e9f;
+      t_wb = (float)(wo * g.stride_w - g.pad_w);
+      t_off = off ? off + (long long)t.n * g.off_sn + pix * g.off_ps : nullptr;
+      t_msk = msk ? msk + (long long)t.n * g.msk_sn + pix * g.msk_ps : nullptr;
+    };
+    // ---- the entry this lane builds for the stage at position p: loads issued by entry_loads,
+    // consumed by entry_build one own stage later
+    uint32_t roh = 0, row_ = 0, rmm = 0;   // raw offset (y, x) and mask elements
+    float bh = -1.0e9f, bw_ = 0.f;          // sampling position without the offset
+    auto entry_loads = [&](const Pos &p) {
+      roh = 0; row_ = 0; rmm = 0; bh = -1.0e9f; bw_ = 0.f;
+      if (p.item >= items) return;
+      if (p.item != t_item) enter_tile(p.item);
+      int hc = p.hcA, tap = p.tapA;
+      if (usel) { if (++tap == T) { tap = 0; ++hc; } }
+      if (2 * p.s + usel >= tp.U) return;            // no such unit: a dead entry
+      bh = t_hb + lut_tap[2 * tap];
+      bw_ = t_wb + lut_tap[2 * tap + 1];
+      const int dgi = (int)lut_dg[t_grp * KH + hc];
+      if (off) {
+        const TIO *pp = t_off + (long long)((dgi * 2 * T + 2 * tap)) * g.off_cs;
+        roh = ldg_raw_ordered(pp);
+        row_ = ldg_raw_ordered(pp + g.off_cs);
+      }
+      if (msk) rmm = ldg_raw_ordered(t_msk + (long long)(dgi * T + tap) * g.msk_cs);
+    };
+    // the entry: weights (w00 w01 | w10 w11), offset of the top-left corner within the padded
+    // sample, and within the shared-memory window (kNoWin: the neighbourhood is not inside it)
+    constexpr uint32_t kNoWin = 0xffffffffu;
+    const uint32_t dead_g = (uint32_t)(g.H + 1) * Rb;   // an all-zero neighbourhood
+    uint32_t ew0 = 0, ew1 = 0, eog = dead_g, eow = kNoWin;
+    auto entry_build = [&]() {
+      // (runs before the loads of the stage after it: t_wy0 / t_wx0 still belong to this entry's tile)
+      ew0 = 0; ew1 = 0; eog = dead_g; eow = kNoWin;
+      const float h_im = bh + RawOf<TIO>::to_float(roh);
+      const float w_im = bw_ + RawOf<TIO>::to_float(row_);
+      if (h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
+        const float m = msk ? mask_value(g, RawOf<TIO>::to_float(rmm)) : 1.f;
+        const float hf = floorf(h_im), wf = floorf(w_im);
+        const float lh = h_im - hf, lw = w_im - wf;
+        const float hh = 1.f - lh, hw = 1.f - lw;
+        ew0 = pack_weights2<MODE>(hh * hw * m, hh * lw * m);
+        ew1 = pack_weights2<MODE>(lh * hw * m, lh * lw * m);
+        const int hl = (int)hf, wl = (int)wf;
+        eog = ((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb;
+        if (kWin) {
+          const uint32_t wy = (uint32_t)(hl - t_wy0), wx = (uint32_t)(wl - t_wx0);
+          if (wy < (uint32_t)(tp.win_h - 1) && wx < (uint32_t)(tp.win_w - 1))
+            eow = (wy * (uint32_t)tp.win_w + wx) * 64u;
         }
       }
+    };
+
+    Pos cur;
+    cur.item = blockIdx.x; cur.s = gi;
+    locate(cur);
+    uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = ((uint32_t)gi / (uint32_t)A) & 1u;
+    uint32_t win_acq = 0, win_rel = 0;   // windows: next one to wait for, next one to hand back
+    bool ok = true;
+    PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
+    // the first stage's entry
+    entry_loads(cur);
+    entry_build();
+    // what the gather of the current tile needs (copied from the decoded tile when `cur` enters it)
+    uint32_t c_item = cur.item, c_win_base = tiles_done * (uint32_t)KH;
+    const char *c_sbase = t_sbase;
+    int c_grp = t_grp;
+    Pos nxt = cur;
+    if (cur.item < items) advance(nxt);
+    entry_loads(nxt);
+
+    while (cur.item < items && ok) {
+      // ---- this lane's unit of the stage
+      int hc = cur.hcA;
+      if (usel && cur.tapA + 1 == T) ++hc;
+      const bool exists = 2 * cur.s + usel < tp.U;
+      const char *gbase = c_sbase + (unsigned long long)(c_grp * g.Cg + (exists ? hc : 0) * 32) * 2ull;
+      const uint32_t wbase = win_s + ((c_win_base + (uint32_t)hc) & 1u) * wbytes;
+      // vectors beyond the unit's channels (a group whose size is not a multiple of 32) are zero
+      const bool v1_dead = !exists || hc * 32 + 8 * (int)q1 >= g.Cg;
+      const bool v2_dead = !exists || hc * 32 + 8 * (int)q2 >= g.Cg;
+      // ---- the windows of both units of the stage (unit B's is the later one)
       if (kWin) {
-        while (ok && win_acq <= win_base + hcB) {
+        const uint32_t hcB = (uint32_t)cur.hcA + ((cur.tapA + 1 == T && 2 * cur.s + 1 < tp.U) ? 1u : 0u);
+        while (ok && win_acq <= c_win_base + hcB) {
           ok = mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13);
           ++win_acq;
         }
       }
       pt.lap(2);
       if (!ok) break;
-      // ---- this lane's unit
-      if (item != my_item) {
-        my_item = item;
-        my_hc = -2;
-        const TileId2 t = decode_item2(item, g, tp);
-        grp = t.grp;
-        sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
-      }
-      int hc = hcA, tap = tapA;
-      uint32_t run = runA;
-      if (usel) {
-        if (++tap == T) {
-          tap = 0; ++hc;
-          if (inrunA + 1u == span) ++run;
-        }
-      }
-      const int key = 2 * s + usel < tp.U ? hc : -1;
-      if (key != my_hc) {
-        my_hc = key;
-        // a unit beyond the tile's last one, or channels beyond the group: zero vectors
-        const int c0 = grp * g.Cg + hc * 32;
-        zero_vec = key < 0 || hc * 32 + 16 * (int)(lane & 1) >= g.Cg;   // (Cg is a multiple of 8; see issue)
-        gbase = sbase + (unsigned long long)(key < 0 ? grp * g.Cg : c0) * 2ull;
-        wbase = win_s + ((win_base + (uint32_t)hc) & 1u) * wbytes;
-        if (seg_per_stage) e_fixed = (uint32_t)(usel * tp.ndu) * kTabStride2;
-        else e_fixed = ((seg_base + run) & 1u) * slot_entries;
-      }
-      const uint32_t e0 = seg_per_stage ? slotS * slot_entries + e_fixed : e_fixed + (uint32_t)tap * kTabStride2;
-      // deform group of each of the two vectors within the unit's set (stage segments; a unit
-      // spans several deform groups only when a deform group has fewer than 32 channels)
-      uint32_t eq1 = 0, eq2 = 0;
-      if (seg_per_stage && tp.ndu > 1 && key >= 0) {
-        const int c0 = grp * g.Cg + hc * 32;
-        eq1 = (uint32_t)((c0 + 8 * (int)q1) / g.cpdg - c0 / g.cpdg) * kTabStride2;
-        eq2 = (uint32_t)((c0 + 8 * (int)q2) / g.cpdg - c0 / g.cpdg) * kTabStride2;
-      }
-      const bool v1_dead = key < 0 || hc * 32 + 8 * (int)q1 >= g.Cg;
-      const bool v2_dead = key < 0 || hc * 32 + 8 * (int)q2 >= g.Cg;
-      pt.lap(0);
       ok = mbar_wait2(empty_a + 8 * sa, pa ^ 1u, 8);
       pt.lap(3);
       if (!ok) break;
       const uint32_t stage_row = a_row + sa * (uint32_t)kTileBytes;
 #pragma unroll 1
       for (int p = 0; p < 2; ++p) {
-        // the vector's entry: weights and offset (both vectors share it unless their deform
-        // groups differ)
-        const uint32_t e = e0 + (uint32_t)(p * 64);
+        // the entry of (row0 + 64 p, unit): built by lane (lane & ~1) | p
+        const int src = (lane & ~1) | p;
+        uint32_t w0 = __shfl_sync(0xffffffffu, ew0, src), w1 = __shfl_sync(0xffffffffu, ew1, src);
         const uint32_t dst = stage_row + (uint32_t)(p * 64 * 128);
-        // the lane's two vectors, one after the other (they share the entry unless their deform
-        // groups differ)
+        bool from_window = false;
+        uint32_t ow = 0;
+        if constexpr (kWin) {
+          ow = __shfl_sync(0xffffffffu, eow, src);
+          // dead vectors (no such unit) read the window's first pixels with zero weights
+          from_window = __all_sync(0xffffffffu, ow != kNoWin || (v1_dead && v2_dead));
+        }
+        if (kWin && from_window) {
+          // The usual case: every lane of the warp reads the window.  The lanes of unit 0 start
+          // with the even 64-byte slot of their left/right pair and those of unit 1 with the
+          // odd one (the window's row pitch is an even number of slots, so the bottom corners
+          // repeat the parity): with the rows' vector order, the eight lanes of a quarter warp
+          // cover all 32 banks.
+          if (ow == kNoWin) ow = 0;
+          const bool sw = ((ow >> 6) & 1u) != (uint32_t)usel;
+          if (sw) { w0 = __byte_perm(w0, 0u, 0x1032); w1 = __byte_perm(w1, 0u, 0x1032); }
+          const uint32_t sp = wbase + ow;
+          const uint32_t s1 = sw ? sp + 64u : sp, s2 = sw ? sp : sp + 64u;
+          const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
 #pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const uint32_t q = k ? q2 : q1, eq = k ? eq2 : eq1;
-          const bool dead = k ? v2_dead : v1_dead;
-          uint32_t tok = 0;
-          uint4 X[4];
-          uint2 w = make_uint2(0u, 0u);
-          uint32_t o = dead_o;
-          if (!dead) { w = lds8(tabw_addr + (e + eq) * 8u); o = lds4(tabo_addr + (e + eq) * 4u); }
-          const bool fg = (o & kWinFlag) != 0u;
-          const uint32_t ob = (o & ~kWinFlag) + 16u * q;
-          if constexpr (kWin) {
-            // The lanes of unit 0 start with the even 64-byte slot of their left/right pair
-            // and those of unit 1 with the odd one (the window's row pitch is an even number
-            // of slots, so the bottom corners repeat the parity): with the rows' vector order,
-            // the eight lanes of a quarter warp cover all 32 banks.
-            const bool sw = (((o >> 6) & 1u) != (uint32_t)usel) && !fg;
-            if (sw) w = make_uint2(__byte_perm(w.x, 0u, 0x1032), __byte_perm(w.y, 0u, 0x1032));
-            const uint32_t sp = wbase + ob;
-            const uint32_t sa_ = sw ? sp + 64u : sp, sb_ = sw ? sp : sp + 64u;
-            if (!__any_sync(0xffffffffu, fg)) {
-              // the usual case: every lane of the warp reads the window
-              X[0] = lds16(sa_, tok); X[1] = lds16(sb_, tok);
-              X[2] = lds16(sa_ + win_rb, tok); X[3] = lds16(sb_ + win_rb, tok);
-            } else {
-              const char *b = gbase + ob;
-              X[0] = ld16_either(fg, b, sa_, tok); X[1] = ld16_either(fg, b + Cb, sb_, tok);
-              X[2] = ld16_either(fg, b + Rb, sa_ + win_rb, tok);
-              X[3] = ld16_either(fg, b + Rb + Cb, sb_ + win_rb, tok);
-            }
-          } else {
-            const char *b = gbase + ob;
+          for (int k = 0; k < 2; ++k) {
+            const uint32_t q16 = 16u * (k ? q2 : q1);
+            uint32_t tok = 0;
+            uint4 X[4];
+            X[0] = lds16(s1 + q16, tok); X[1] = lds16(s2 + q16, tok);
+            X[2] = lds16(s1 + win_rb + q16, tok); X[3] = lds16(s2 + win_rb + q16, tok);
+            uint4 wa = wa0;
+            wa.x |= tok;  // tok is 0: keeps the blend behind the loads
+            uint4 r;
+            if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
+            else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
+            if (k ? v2_dead : v1_dead) r = make_uint4(0u, 0u, 0u, 0u);
+            sts16(dst + (k ? a_c2 : a_c1), r);
+          }
+        } else {
+          // some neighbourhood of the warp's pass lies outside the window (or there is no
+          // window): the whole pass reads the padded copy in global memory
+          const uint32_t og = __shfl_sync(0xffffffffu, eog, src);
+          const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const char *b = gbase + og + 16u * (k ? q2 : q1);
+            uint32_t tok = 0;
+            uint4 X[4];
             X[0] = ld16_global(b, tok); X[1] = ld16_global(b + Cb, tok);
             X[2] = ld16_global(b + Rb, tok); X[3] = ld16_global(b + Rb + Cb, tok);
+            uint4 wa = wa0;
+            wa.x |= tok;
+            uint4 r;
+            if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
+            else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
+            if (k ? v2_dead : v1_dead) r = make_uint4(0u, 0u, 0u, 0u);
+            sts16(dst + (k ? a_c2 : a_c1), r);
           }
-          uint4 wa = table_weights<MODE>(w);
-          wa.x |= tok;  // tok is 0: keeps the blend behind the loads
-          uint4 r;
-          if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
-          else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
-          sts16(dst + ((k ? a_c2 : a_c1) << 4), r);
         }
       }
       fence_proxy_async_smem();
       __syncwarp();
       if (lane == 0) mbar_arrive(full_a + 8 * sa);
       pt.lap(4);
-      // ---- hand back what the group is done with, move on by kGroups2 stages
-      if (seg_per_stage) {
-        if (lane == 0) mbar_arrive(tab_empty + 8 * slotS);
-        slotS += (uint32_t)kGroups2;
-        while (slotS >= (uint32_t)RS) { slotS -= (uint32_t)RS; phS ^= 1u; }
-      }
+      // ---- the next stage: its entry from the loads issued a stage ago, then the loads of the
+      // stage after it
+      entry_build();
       sa += (uint32_t)kGroups2;
       while (sa >= (uint32_t)A) { sa -= (uint32_t)A; pa ^= 1u; }
-      s += kGroups2;
-      if (s < tp.S) {
-        tapA += 2 * kGroups2;
-        while (tapA >= T) {
-          tapA -= T; ++hcA;
-          if (++inrunA == span) { inrunA = 0; ++runA; }
-        }
-      } else {
-        normalise();
+      cur = nxt;
+      if (cur.item != c_item && cur.item < items) {
+        // (`nxt` entered this tile a stage ago: the decoded tile is this one)
+        c_item = cur.item;
+        c_win_base = tiles_done * (uint32_t)KH;
+        c_sbase = t_sbase;
+        c_grp = t_grp;
       }
-      const bool more = item < items;
-      if (!seg_per_stage) {
-        // run segments before the next stage's first unit go back to the builders
-        const uint32_t seg_keep = more ? seg_base + runA : seg_acq;
-        if (seg_rel < seg_keep) {
-          if (lane == 0)
-            for (uint32_t i = seg_rel; i < seg_keep; ++i) mbar_arrive(tab_empty + 8 * (i & 1u));
-          seg_rel = seg_keep;
-        }
-      }
+      if (nxt.item < items) advance(nxt);
+      entry_loads(nxt);
       if (kWin) {
         // windows before the next stage's first unit go back to the loader (the loads from
         // them have returned: their values were consumed above)
-        const uint32_t win_keep = more ? win_base + (uint32_t)hcA : win_acq;
+        const uint32_t win_keep = cur.item < items ? c_win_base + (uint32_t)cur.hcA : win_acq;
         if (win_rel < win_keep) {
           if (lane == 0)
             for (uint32_t i = win_rel; i < win_keep; ++i) mbar_arrive(win_empty + 8 * (i & 1u));
           win_rel = win_keep;
         }
       }
+      pt.lap(0);
     }
-    (void)zero_vec;
     if (!ok) *abort_s = 1;
   }
 
@@ -1007,9 +836,9 @@ EncodeTiledFn encode_fn() {
   return f;
 }
 
-template <typename TIO, int MODE, bool kWin, bool kSegStage>
+template <typename TIO, int MODE, bool kWin>
 cudaError_t launch_one2(const Tc2Args &a, const TcPlan &tp, cudaStream_t s) {
-  auto kern = dcn_fwd_tc2<TIO, MODE, kWin, kSegStage>;
+  auto kern = dcn_fwd_tc2<TIO, MODE, kWin>;
   static std::atomic<unsigned long long> done_mask{0};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -1093,16 +922,13 @@ cudaError_t launch_tc2(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
-  const bool win = tp.win_h > 0, seg_stage = tp.tab_span == 0;
-#define DCN_TC2_LAUNCH(TIO, MODE)                                                              \
-  (win ? (seg_stage ? launch_one2<TIO, MODE, true, true>(a, tp, s)                             \
-                    : launch_one2<TIO, MODE, true, false>(a, tp, s))                           \
-       : (seg_stage ? launch_one2<TIO, MODE, false, true>(a, tp, s)                            \
-                    : launch_one2<TIO, MODE, false, false>(a, tp, s)))
-  if (dtype == DCN_DTYPE_F32) return DCN_TC2_LAUNCH(float, kModeBf16);
-  if (dtype == DCN_DTYPE_F16) return DCN_TC2_LAUNCH(__half, kModeF16);
-  return DCN_TC2_LAUNCH(__nv_bfloat16, kModeBf16);
-#undef DCN_TC2_LAUNCH
+  const bool win = tp.win_h > 0;
+  if (dtype == DCN_DTYPE_F32)
+    return win ? launch_one2<float, kModeBf16, true>(a, tp, s) : launch_one2<float, kModeBf16, false>(a, tp, s);
+  if (dtype == DCN_DTYPE_F16)
+    return win ? launch_one2<__half, kModeF16, true>(a, tp, s) : launch_one2<__half, kModeF16, false>(a, tp, s);
+  return win ? launch_one2<__nv_bfloat16, kModeBf16, true>(a, tp, s)
+             : launch_one2<__nv_bfloat16, kModeBf16, false>(a, tp, s);
 }
 
 }  // namespace dcn

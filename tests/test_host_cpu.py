@@ -62,18 +62,19 @@ def test_plan_routes_and_sizes():
     rc, info = plan(params(N=256, C=256, H=128, W=128, Co=256, dg=8))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_n == 256
     assert info.grid == 148 and info.smem_bytes <= 232448
-    # 16-bit tensors run on the second-generation kernel: 4 epilogue + MMA + 2 loaders + 4 table
-    # builder + 16 gather warps.  Every 64-channel chunk has deform groups of its own here, so
-    # a table segment serves one k-stage.
-    assert info.kernel_version == 2 and info.producer_layout == 4016 and info.block == 28 * 32
-    assert info.table_span == 0 and info.table_slots >= 4
+    # 16-bit tensors run on the second-generation kernel: 4 epilogue + MMA + 2 loader + 1 idle
+    # + 16 gather warps that build their own tap entries
+    assert info.kernel_version == 2 and info.producer_layout == 16 and info.block == 24 * 32
     assert info.operand_stages >= 2 and info.weight_stages == 2
     rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
-    # the eight 32-channel half-chunks of a tile share their deform group: one table segment
-    # per tile, two slots
-    assert rc == 0 and info.kernel_version == 2 and (info.table_span, info.table_slots) == (8, 2)
+    assert rc == 0 and info.kernel_version == 2
+    assert info.window_h >= 10 + 6 and info.window_w >= 18 + 6 and info.window_w % 2 == 0
+    # a strided layer samples too widely for the shared-memory window: first-generation kernel
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
-    assert rc == 0 and (info.table_span, info.table_slots) == (4, 2)   # 128 channels per deform group
+    assert rc == 0 and info.kernel_version == 1 and (info.Ho, info.Wo) == (32, 32)
+    # a deform group of 16 channels starts inside a 32-channel unit: first-generation kernel
+    rc, info = plan(params(C=64, Co=64, dg=4))
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.kernel_version == 1
     rc, info = plan(params(dtype=_lib.DTYPE_F32, math=_lib.MATH_TF32X3, C=256, Co=256, H=100, W=168))
     assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.tile_k == 32
     assert info.smem_bytes <= 232448
