@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DCN_ABI_VERSION 4
+#define DCN_ABI_VERSION 5
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
@@ -95,6 +95,12 @@ typedef struct DcnFwdParams {
   int32_t mask_act;   /* DCN_ACT_SIGMOID: the mask tensor holds logits (what the Pack layers'
                        * branch produces before its sigmoid).  Tensor-core path only. */
   int32_t reserved0;
+  /* Optional: the zero-bordered channels-last copy of `input` that dcn_pad_channels_last()
+   * wrote (16-bit tensors).  The 16-bit tensor-core kernels then read it instead of making
+   * their own copy, so a caller that runs several operators on the same activations (a Pack
+   * layer: offset branch + deformable kernel) pays for the copy once.  NULL = none. */
+  const void *padded_input;
+  int64_t padded_input_bytes;
 } DcnFwdParams;
 
 /* What a call will do; filled by dcn_fwd_plan without touching the device. */
@@ -239,6 +245,32 @@ int dcn_read_status(const void *workspace, void *stream, int32_t *status);
 int dcn_to_channels_last(const void *input, void *output, int32_t dtype, int64_t N, int64_t C,
                          int64_t H, int64_t W, const int64_t in_stride[4], int32_t device,
                          void *stream);
+
+/*
+ * The copy the 16-bit tensor-core kernels sample: channels-last, every sample surrounded by a
+ * one-pixel zero border, one more all-zero row at the end: [N][H+2][W+2][C] + [W+2][C]
+ * elements of the tensor's own 16-bit type (bf16 / fp16; C a multiple of 8).
+ * dcn_padded_bytes reports its size; dcn_pad_channels_last enqueues the copy of a 4-D tensor
+ * [N, C, H, W] with element strides `in_stride` into `padded` (256-byte aligned) on `stream`.
+ * Pass the result in DcnFwdParams.padded_input.  (No counterpart in the reference, which keeps
+ * NCHW and pads inside its gather.)
+ */
+int dcn_padded_bytes(int32_t dtype, int64_t N, int64_t C, int64_t H, int64_t W, size_t *bytes);
+int dcn_pad_channels_last(const void *input, void *padded, int32_t dtype, int64_t N, int64_t C,
+                          int64_t H, int64_t W, const int64_t in_stride[4], int32_t device,
+                          void *stream);
+
+/*
+ * Ordinary convolution (no offsets, no mask: those two fields of `p` are ignored) with the
+ * problem description of dcn_fwd, on a tensor-core kernel whose operand tiles are written by
+ * tensor-map box copies from the padded input: the offset / mask branch of the Pack layers
+ * (mmcv/ops/modulated_deform_conv.py:311-335, mmcv/ops/deform_conv.py:397-415), for which the
+ * reference calls a library convolution.  16-bit tensors; channels per group a multiple of 64
+ * or one group; otherwise DCN_ERR_UNSUPPORTED (dcn_fwd with offset == NULL computes the same
+ * on the general kernel).  Workspace: dcn_conv_workspace_bytes.
+ */
+int dcn_conv_workspace_bytes(const DcnFwdParams *p, size_t *bytes);
+int dcn_conv_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * The two reference entry points with flat arguments, in the reference's own

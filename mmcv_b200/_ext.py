@@ -128,11 +128,12 @@ def _weight_image(lib, p, weight, dev, stream):
 def forward(input, offset, mask, weight, bias, output, stride, padding, dilation,
             groups, deform_groups, math_mode=None, act=_lib.ACT_NONE, act_range=(0, 0),
             offset_batch_stride=0, mask_batch_stride=0, out_batch_stride=0,
-            offset_strides=(0, 0), mask_strides=(0, 0), mask_act=_lib.ACT_NONE):
+            offset_strides=(0, 0), mask_strides=(0, 0), mask_act=_lib.ACT_NONE, padded=None):
     """Launch one forward on the current stream.  offset=None means an ordinary
     convolution, mask=None the unmodulated (v1) operator.  offset_strides / mask_strides are
     (channel, pixel) element strides inside a sample, (0, 0) = dense planes; mask_act =
-    ACT_SIGMOID says the mask tensor holds logits.  Returns the workspace tensor."""
+    ACT_SIGMOID says the mask tensor holds logits; padded = the zero-bordered channels-last copy
+    of `input` from pad_channels_last(), when the caller has one.  Returns the workspace tensor."""
     lib = _lib.load()
     dev = _require_cuda(input=input, offset=offset, mask=mask, weight=weight, bias=bias,
                         output=output)
@@ -162,6 +163,8 @@ def forward(input, offset, mask, weight, bias, output, stride, padding, dilation
     p.offset_channel_stride, p.offset_pixel_stride = offset_strides
     p.mask_channel_stride, p.mask_pixel_stride = mask_strides
     p.mask_act = mask_act
+    if padded is not None:
+        p.padded_input, p.padded_input_bytes = _ptr(padded), padded.numel()
     p.act, p.act_lo, p.act_hi = act, act_range[0], act_range[1]
     p.device = dev.index if dev.index is not None else torch.cuda.current_device()
     nbytes = ctypes.c_size_t(0)
@@ -211,7 +214,7 @@ def _check_shapes(input, weight, offset, mask, output, stride, padding, dilation
 
 
 def forward_from_branch(input, branch, n_offset, weight, bias, output, stride, padding, dilation,
-                        groups, deform_groups):
+                        groups, deform_groups, padded=None):
     """Deformable convolution whose offsets are the first n_offset channels of `branch` (the
     raw output of a Pack layer's offset convolution, NCHW-contiguous or channels-last) and
     whose mask logits are the remaining channels (none: the v1 operator).  The kernel reads
@@ -248,7 +251,7 @@ def forward_from_branch(input, branch, n_offset, weight, bias, output, stride, p
                 deform_groups, offset_batch_stride=Ct * Ho * Wo,
                 mask_batch_stride=Ct * Ho * Wo if modulated else 0, offset_strides=strides,
                 mask_strides=strides if modulated else (0, 0),
-                mask_act=_lib.ACT_SIGMOID if modulated else _lib.ACT_NONE)
+                mask_act=_lib.ACT_SIGMOID if modulated else _lib.ACT_NONE, padded=padded)
     except _lib.Unsupported:
         return False
     return True
@@ -270,6 +273,80 @@ def to_channels_last(x):
         _lib.check(lib.dcn_to_channels_last(
             _ptr(x), _ptr(out), _dtype_code(x), x.size(0), x.size(1), x.size(2), x.size(3),
             strides, dev.index if dev.index is not None else torch.cuda.current_device(), stream))
+    return out
+
+
+def pad_channels_last(x):
+    """The zero-bordered channels-last copy of x [N, C, H, W] that the 16-bit tensor-core kernels
+    sample (a flat uint8 tensor), made once for all operators that read the same activations;
+    None when x is not a 16-bit CUDA tensor with a multiple of 8 channels."""
+    if x.dim() != 4 or not x.is_cuda or x.dtype not in (torch.bfloat16, torch.float16):
+        return None
+    if x.size(1) % 8 != 0 or x.numel() == 0:
+        return None
+    lib = _lib.load()
+    nbytes = ctypes.c_size_t(0)
+    _lib.check(lib.dcn_padded_bytes(_dtype_code(x), x.size(0), x.size(1), x.size(2), x.size(3),
+                                    ctypes.byref(nbytes)))
+    dev = x.device
+    with torch.cuda.device(dev):
+        out = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        strides = (ctypes.c_int64 * 4)(*x.stride())
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dcn_pad_channels_last(
+            _ptr(x), _ptr(out), _dtype_code(x), x.size(0), x.size(1), x.size(2), x.size(3), strides,
+            dev.index if dev.index is not None else torch.cuda.current_device(), stream))
+    return out
+
+
+def conv_forward(x, weight, bias, stride, padding, dilation, padded=None, act=_lib.ACT_NONE,
+                 act_range=(0, 0)):
+    """Ordinary convolution of x with `weight` (+ bias) on this library's kernels: the
+    tensor-map convolution when the problem fits it (16-bit, channels a multiple of 64 or one
+    group), else the general kernel with zero offsets.  Returns [N, Cout, Ho, Wo]."""
+    lib = _lib.load()
+    ho, wo = _out_hw(x, weight, stride, padding, dilation)
+    out = x.new_empty((x.size(0), weight.size(0), ho, wo))
+    if x.numel() == 0 or out.numel() == 0:
+        return out
+    dev = _require_cuda(input=x, weight=weight, bias=bias)
+    x = _input_layout(x)
+    weight = weight.contiguous()
+    bias = None if bias is None else bias.contiguous()
+    if x.dtype in (torch.bfloat16, torch.float16):
+        p = _lib.DcnFwdParams()
+        p.input, p.weight, p.bias, p.output = _ptr(x), _ptr(weight), _ptr(bias), _ptr(out)
+        p.dtype, p.math_mode = _dtype_code(x), _lib.MATH_AUTO
+        p.N, p.C, p.H, p.W = x.shape
+        p.Co, p.kh, p.kw = weight.shape[0], weight.shape[2], weight.shape[3]
+        p.stride_h, p.stride_w = stride
+        p.pad_h, p.pad_w = padding
+        p.dil_h, p.dil_w = dilation
+        p.groups, p.deform_groups = 1, 1
+        for i, s in enumerate(x.stride()):
+            p.in_stride[i] = s
+        p.act, p.act_lo, p.act_hi = act, act_range[0], act_range[1]
+        p.device = dev.index if dev.index is not None else torch.cuda.current_device()
+        if padded is not None:
+            p.padded_input, p.padded_input_bytes = _ptr(padded), padded.numel()
+        nbytes = ctypes.c_size_t(0)
+        rc = lib.dcn_conv_workspace_bytes(ctypes.byref(p), ctypes.byref(nbytes))
+        if rc == 0:
+            with torch.cuda.device(dev):
+                ws = torch.empty(nbytes.value, dtype=torch.uint8, device=dev)
+                stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+                _lib.check(lib.dcn_conv_fwd(ctypes.byref(p), _ptr(ws), nbytes.value, stream))
+                if _check_status:
+                    st = ctypes.c_int32(0)
+                    _lib.check(lib.dcn_read_status(_ptr(ws), stream, ctypes.byref(st)))
+                    if st.value != 0:
+                        raise RuntimeError(f'dcn_b200: device-side wait {st.value} timed out; the '
+                                           'output is not valid')
+            return out
+        if rc != -2:
+            _lib.check(rc)
+    forward(x, None, None, weight, bias, out, stride, padding, dilation, 1, 1, act=act,
+            act_range=act_range, padded=padded)
     return out
 
 
@@ -362,20 +439,13 @@ def deform_conv_forward(input, weight, offset, output, columns, ones, kW, kH, dW
             (dilationH, dilationW), group, deformable_group)
 
 
-def conv_offset_forward(x, weight, bias, stride, padding, dilation, sigmoid_from=None):
-    """The offset(/mask) branch of the Pack layers as an ordinary convolution on the same
-    implicit-GEMM kernel (zero offsets, unit mask), with the sigmoid of the mask channels
-    [sigmoid_from, Cout) fused into the epilogue.  Returns [N, Cout, Ho, Wo]."""
-    kh, kw = weight.shape[2], weight.shape[3]
-    ho = (x.size(2) + 2 * padding[0] - (dilation[0] * (kh - 1) + 1)) // stride[0] + 1
-    wo = (x.size(3) + 2 * padding[1] - (dilation[1] * (kw - 1) + 1)) // stride[1] + 1
-    out = x.new_empty((x.size(0), weight.size(0), ho, wo))
+def conv_offset_forward(x, weight, bias, stride, padding, dilation, sigmoid_from=None, padded=None):
+    """The offset(/mask) branch of the Pack layers as an ordinary convolution on this library's
+    kernels, optionally with the sigmoid of the mask channels [sigmoid_from, Cout) fused into
+    the epilogue.  Returns [N, Cout, Ho, Wo]."""
     act = _lib.ACT_SIGMOID if sigmoid_from is not None else _lib.ACT_NONE
     rng = (sigmoid_from, weight.size(0)) if sigmoid_from is not None else (0, 0)
-    forward(_input_layout(x), None, None, weight.contiguous(),
-            None if bias is None else bias.contiguous(), out, stride, padding, dilation, 1, 1,
-            act=act, act_range=rng)
-    return out
+    return conv_forward(x, weight, bias, stride, padding, dilation, padded=padded, act=act, act_range=rng)
 
 
 # ---------------------------------------------------------------------------------------

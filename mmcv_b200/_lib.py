@@ -14,12 +14,13 @@ MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 4   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
+ABI_VERSION = 5   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_fwd_workspace_bytes', 'dcn_weight_image_bytes', 'dcn_prepare_weights', 'dcn_fwd', 'dcn_fwd_profiled', 'dcn_fwd_static_scratch',
-           'dcn_read_counters', 'dcn_read_status', 'dcn_debug_configure', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
+           'dcn_read_counters', 'dcn_read_status', 'dcn_debug_configure', 'dcn_padded_bytes',
+           'dcn_pad_channels_last', 'dcn_conv_workspace_bytes', 'dcn_conv_fwd', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
            'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
            'dcn_forward_workspace_bytes']
@@ -48,6 +49,7 @@ class DcnFwdParams(ctypes.Structure):
         ('offset_channel_stride', ctypes.c_int64), ('offset_pixel_stride', ctypes.c_int64),
         ('mask_channel_stride', ctypes.c_int64), ('mask_pixel_stride', ctypes.c_int64),
         ('mask_act', ctypes.c_int32), ('reserved0', ctypes.c_int32),
+        ('padded_input', ctypes.c_void_p), ('padded_input_bytes', ctypes.c_int64),
     ]
 
 
@@ -100,6 +102,10 @@ def load():
     lib.dcn_read_counters.argtypes = [vp, vp, P(ctypes.c_uint64)]
     lib.dcn_read_status.argtypes = [vp, vp, P(i32)]
     lib.dcn_debug_configure.argtypes = [ctypes.c_uint64, i32]
+    lib.dcn_padded_bytes.argtypes = [i32, i64, i64, i64, i64, P(sz)]
+    lib.dcn_pad_channels_last.argtypes = [vp, vp, i32, i64, i64, i64, i64, P(i64), i32, vp]
+    lib.dcn_conv_workspace_bytes.argtypes = [P(DcnFwdParams), P(sz)]
+    lib.dcn_conv_fwd.argtypes = [P(DcnFwdParams), vp, sz, vp]
     lib.dcn_modulated_deform_conv_forward.argtypes = (
         [vp] * 6 + [i32] + [i64] * 5 + [i32] * 12 + [vp, sz, vp])
     lib.dcn_deform_conv_forward.argtypes = (

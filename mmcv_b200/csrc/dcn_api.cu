@@ -223,7 +223,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     const bool aligned = (g.Wo * es) % 16 == 0 && ((long long)g.Ho * g.Wo * es) % 16 == 0 &&
                          (g.out_sn * es) % 16 == 0 && ((uintptr_t)p->output & 15) == 0;
     const bool slabs_ok = g.Cog % t.BN == 0 || g.groups * t.NT == 1;
-    const int want = kn.epi_tma < 0 ? 0 : kn.epi_tma;
+    const int want = kn.epi_tma < 0 ? 1 : kn.epi_tma;
     t.epi_tma = (want && aligned && slabs_ok && g.N > 0) ? 1 : 0;
   }
   t.raw_slots = 0;
@@ -263,7 +263,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
 }
 
 // Decide whether the tensor-core kernel can take the problem and with what tiling.
-bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
+bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp, bool allow_v2 = true) {
   const int math = resolved_math(p);
   if (math != DCN_MATH_BF16 && math != DCN_MATH_TF32X3) return false;
   const bool tf32 = math == DCN_MATH_TF32X3;
@@ -365,9 +365,11 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp) {
   tp->items = mtiles * g.groups * tp->NT;
   tp->grid = (int)(tp->items < sms ? tp->items : sms);
   tp->version = 1;
-  if (!tf32 && kn.kernel == 2) plan_tc2(p, g, tp);
+  if (!tf32 && kn.kernel == 2 && allow_v2) plan_tc2(p, g, tp);
   return true;
 }
+
+size_t padded_copy_bytes(const Geom &g) { return ((size_t)g.N * (g.H + 2) + 1) * (g.W + 2) * g.C * 2; }
 
 void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPlan &tp,
                       Workspace *ws) {
@@ -379,9 +381,12 @@ void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPla
     off = align_up(off + ws->wtile_bytes, 256);
     if (tp.version == 2) {
       // channels-last copy with a one-pixel zero border per sample and one more zero row
-      ws->xcl_off = off;
-      ws->xcl_bytes = ((size_t)g.N * (g.H + 2) + 1) * (g.W + 2) * g.C * 2;
-      off = align_up(off + ws->xcl_bytes, 256);
+      // (unless the caller brings it)
+      if (!p->padded_input) {
+        ws->xcl_off = off;
+        ws->xcl_bytes = padded_copy_bytes(g);
+        off = align_up(off + ws->xcl_bytes, 256);
+      }
     } else if (!input_is_ready(p, g, tp.op_format)) {
       ws->xcl_off = off;
       ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * (tp.tiles_per_stage == 2 ? 4 : 2);
@@ -446,6 +451,10 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
   // meet the fp32 tolerance, so the request degrades instead of failing.
   layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);
   pl->stage = pl->tc && pl->ws.xcl_bytes != 0;
+  if (pl->tc && pl->tp.version == 2 && p->padded_input &&
+      ((size_t)p->padded_input_bytes != padded_copy_bytes(pl->g) || ((uintptr_t)p->padded_input & 255)))
+    return fail(DCN_ERR_ARG, "padded_input must be %zu bytes and 256-byte aligned (got %lld)",
+                padded_copy_bytes(pl->g), (long long)p->padded_input_bytes);
   pl->have_image = pl->tc && p->weight_image != nullptr;
   pl->launches = pl->tc ? (2 + (pl->have_image ? 0 : 1) + (pl->stage ? 1 : 0)) : 2;
   return DCN_OK;
@@ -547,7 +556,7 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
     if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;
   }
-  const void *xcl = p->input;
+  const void *xcl = (pl.tp.version == 2 && p->padded_input) ? p->padded_input : p->input;
   if (pl.stage) {
     void *dst = ws + pl.ws.xcl_off;
     e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.op_format,
@@ -738,6 +747,131 @@ int dcn_to_channels_last(const void *input, void *output, int32_t dtype, int64_t
   const int op_format = dtype == DCN_DTYPE_F32 ? 2 : (dtype == DCN_DTYPE_F16 ? 0 : 1);
   e = launch_stage_input_cl(g, input, dtype, output, op_format, 0, (cudaStream_t)stream);
   return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "layout copy launch: %s", cudaGetErrorString(e));
+}
+
+
+int dcn_padded_bytes(int32_t dtype, int64_t N, int64_t C, int64_t H, int64_t W, size_t *bytes) {
+  if (!bytes) return fail(DCN_ERR_ARG, "bytes is NULL");
+  if (dtype != DCN_DTYPE_BF16 && dtype != DCN_DTYPE_F16)
+    return fail(DCN_ERR_UNSUPPORTED, "the padded copy exists for bf16 and fp16 tensors");
+  if (N < 0 || C < 1 || H < 1 || W < 1 || C % 8 != 0)
+    return fail(DCN_ERR_ARG, "bad shape [%lld, %lld, %lld, %lld] (C must be a multiple of 8)", (long long)N,
+                (long long)C, (long long)H, (long long)W);
+  *bytes = ((size_t)N * (H + 2) + 1) * (W + 2) * C * 2;
+  return DCN_OK;
+}
+
+int dcn_pad_channels_last(const void *input, void *padded, int32_t dtype, int64_t N, int64_t C,
+                          int64_t H, int64_t W, const int64_t in_stride[4], int32_t device,
+                          void *stream) {
+  size_t bytes = 0;
+  int rc = dcn_padded_bytes(dtype, N, C, H, W, &bytes);
+  if (rc) return rc;
+  if (!in_stride) return fail(DCN_ERR_ARG, "in_stride is NULL");
+  if (N > 2147483647LL || C > 2147483647LL || H * W > 2147483647LL)
+    return fail(DCN_ERR_UNSUPPORTED, "tensor too large for 32-bit pixel and channel indices");
+  if (N == 0) return DCN_OK;
+  if (!input || !padded || ((uintptr_t)padded & 255))
+    return fail(DCN_ERR_ARG, "input and a 256-byte aligned destination are required");
+  DeviceInfo *dev = nullptr;
+  rc = probe_device(device, &dev);
+  if (rc) return rc;
+  DeviceScope scope(device);
+  if (scope.err != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(scope.err));
+  Geom g;
+  memset(&g, 0, sizeof(g));
+  g.N = (int)N; g.C = (int)C; g.H = (int)H; g.W = (int)W;
+  g.in_sn = in_stride[0]; g.in_sc = in_stride[1]; g.in_sh = in_stride[2]; g.in_sw = in_stride[3];
+  cudaError_t e = launch_stage_input_cl(g, input, dtype, padded, dtype == DCN_DTYPE_F16 ? 0 : 1, 1,
+                                        (cudaStream_t)stream);
+  return e == cudaSuccess ? DCN_OK : fail(DCN_ERR_CUDA, "padded copy launch: %s", cudaGetErrorString(e));
+}
+
+namespace {
+struct ConvPlan {
+  Geom g;
+  TcPlan tp;
+  size_t wtile_off, wtile_bytes, xpad_off, xpad_bytes, total;
+};
+int make_conv_plan(const DcnFwdParams *p, int sms, ConvPlan *cp) {
+  int rc = build_geom(p, &cp->g);
+  if (rc) return rc;
+  if (p->dtype == DCN_DTYPE_F32)
+    return fail(DCN_ERR_UNSUPPORTED, "the tensor-map convolution takes bf16 and fp16 tensors");
+  DcnFwdParams q = *p;
+  q.math_mode = DCN_MATH_BF16;
+  if (!plan_tc(&q, cp->g, sms, &cp->tp, false) || !conv_tma_supported(cp->g, cp->tp))
+    return fail(DCN_ERR_UNSUPPORTED, "the tensor-map convolution needs channels per group to be a multiple "
+                "of 64 (or one group) and a multiple of 8 (got %d)", cp->g.Cg);
+  size_t off = 256;
+  cp->wtile_off = off;
+  cp->wtile_bytes = (size_t)cp->g.groups * cp->tp.NT * cp->tp.S * cp->tp.BN * 128;
+  off = align_up(off + cp->wtile_bytes, 256);
+  cp->xpad_off = cp->xpad_bytes = 0;
+  if (!p->padded_input) {
+    cp->xpad_off = off;
+    cp->xpad_bytes = padded_copy_bytes(cp->g);
+    off = align_up(off + cp->xpad_bytes, 256);
+  } else if ((size_t)p->padded_input_bytes != padded_copy_bytes(cp->g) || ((uintptr_t)p->padded_input & 255)) {
+    return fail(DCN_ERR_ARG, "padded_input must be %zu bytes and 256-byte aligned (got %lld)",
+                padded_copy_bytes(cp->g), (long long)p->padded_input_bytes);
+  }
+  cp->total = off;
+  return DCN_OK;
+}
+}  // namespace
+
+int dcn_conv_workspace_bytes(const DcnFwdParams *p, size_t *bytes) {
+  if (!bytes) return fail(DCN_ERR_ARG, "bytes is NULL");
+  ConvPlan cp;
+  int rc = make_conv_plan(p, kSmCountFallback, &cp);
+  if (rc) return rc;
+  *bytes = cp.total;
+  return DCN_OK;
+}
+
+int dcn_conv_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_bytes, void *stream) {
+  if (!p) return fail(DCN_ERR_ARG, "params is NULL");
+  DeviceInfo *dev = nullptr;
+  int rc = probe_device(p->device, &dev);
+  if (rc) return rc;
+  ConvPlan cp;
+  rc = make_conv_plan(p, dev->sms, &cp);
+  if (rc) return rc;
+  if (cp.g.P != 0 && (!p->input || !p->weight || !p->output))
+    return fail(DCN_ERR_ARG, "input, weight and output pointers must be non-NULL");
+  if (!workspace || workspace_bytes < cp.total)
+    return fail(DCN_ERR_WORKSPACE, "workspace of %zu bytes needed, %zu given", cp.total,
+                workspace ? workspace_bytes : (size_t)0);
+  if (((uintptr_t)workspace & 255) != 0) return fail(DCN_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  DeviceScope scope(p->device);
+  cudaError_t e = scope.err;
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+  cudaStream_t s = (cudaStream_t)stream;
+  uint8_t *ws = (uint8_t *)workspace;
+  e = launch_clear_status((int *)ws, s);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "status clear: %s", cudaGetErrorString(e));
+  if (cp.g.P == 0) return DCN_OK;
+  const void *xpad = p->padded_input;
+  if (!xpad) {
+    e = launch_stage_input_cl(cp.g, p->input, p->dtype, ws + cp.xpad_off, cp.tp.op_format, 1, s);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "input staging launch: %s", cudaGetErrorString(e));
+    xpad = ws + cp.xpad_off;
+  }
+  const void *wimage = ws + cp.wtile_off;
+  if (p->weight_image) {
+    if ((size_t)p->weight_image_bytes != cp.wtile_bytes || ((uintptr_t)p->weight_image & 255))
+      return fail(DCN_ERR_ARG, "weight_image must be %zu bytes and 256-byte aligned (got %lld)", cp.wtile_bytes,
+                  (long long)p->weight_image_bytes);
+    wimage = p->weight_image;
+  } else {
+    e = launch_weight_tiles(cp.g, cp.tp, p->weight, p->dtype, ws + cp.wtile_off, s);
+    if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "weight tiling launch: %s", cudaGetErrorString(e));
+  }
+  Ptrs ptrs{p->input, nullptr, nullptr, p->weight, p->bias, p->output};
+  e = launch_conv_tma(cp.g, cp.tp, ptrs, p->dtype, xpad, wimage, (int *)ws, g_wait_limit_ns.load(), s);
+  if (e != cudaSuccess) return fail(DCN_ERR_CUDA, "convolution kernel launch: %s", cudaGetErrorString(e));
+  return DCN_OK;
 }
 
 static void fill_dense(DcnFwdParams *q, int32_t elem, int64_t batch, int64_t channels,

@@ -150,6 +150,11 @@ cudaError_t launch_tc2(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype
                        const void *wtiles, int *status, unsigned long long *counters,
                        unsigned long long wait_limit_ns, int debug_flags, cudaStream_t s);
 
+bool conv_tma_supported(const Geom &g, const TcPlan &tp);
+cudaError_t launch_conv_tma(const Geom &g, const TcPlan &tp, const Ptrs &p, int dtype, const void *xpad,
+                            const void *wtiles, int *status, unsigned long long wait_limit_ns,
+                            cudaStream_t s);
+
 cudaError_t launch_bwd_columns(const Geom &g, const Ptrs &p, int dtype, int n0, int ns, float *col,
                                cudaStream_t s);
 cudaError_t launch_bwd_input(const Geom &g, const Ptrs &p, int dtype, int n0, int ns,

@@ -162,21 +162,25 @@ class DeformConv2dPack(DeformConv2d):
     def forward(self, x: Tensor) -> Tensor:  # type: ignore[override]
         if fused_branch_applies(x, self.conv_offset):
             dtype = branch_dtype(x)
-            x = shared_layout(x.to(dtype))
+            x = x.to(dtype)
+            padded = None
             if mdc.OFFSET_BRANCH == 'kernel':
+                # one zero-bordered channels-last copy feeds the branch and the deformable kernel
+                padded = ext_module.pad_channels_last(x)
                 offset = ext_module.conv_offset_forward(
                     x, ext_module.cast_weight(self.conv_offset.weight, dtype),
                     ext_module.cast_weight(self.conv_offset.bias, dtype),
-                    _pair(self.stride), _pair(self.padding), _pair(self.dilation))
+                    _pair(self.stride), _pair(self.padding), _pair(self.dilation), padded=padded)
             else:
+                x = shared_layout(x)
                 offset = mdc.branch_conv(x, self.conv_offset, dtype)
-                if x.size(0) % min(self.im2col_step, x.size(0)) == 0:
-                    y = mdc.deform_from_branch(x, offset, offset.size(1), self.weight, None,
-                                               self.stride, self.padding, self.dilation,
-                                               self.groups, self.deform_groups)
-                    if y is not None:
-                        return y
-                offset = offset.contiguous()
+            if x.size(0) > 0 and x.size(0) % min(self.im2col_step, x.size(0)) == 0:
+                y = mdc.deform_from_branch(x, offset, offset.size(1), self.weight, None,
+                                           self.stride, self.padding, self.dilation,
+                                           self.groups, self.deform_groups, padded=padded)
+                if y is not None:
+                    return y
+            offset = offset.contiguous()
         else:
             offset = self.conv_offset(x)
         return deform_conv2d(x, offset, self.weight, self.stride, self.padding, self.dilation,

@@ -91,12 +91,11 @@ class ModulatedDeformConv2dFunction(Function):
 modulated_deform_conv2d = ModulatedDeformConv2dFunction.apply
 
 
-# How an inference-time Pack layer computes its offset branch: 'library' = the branch's own
-# nn.Conv2d arithmetic (cuDNN) on the channels-last copy of the input that the deformable
-# kernel reads as well; 'kernel' = one launch of this library's implicit-GEMM kernel with zero
-# offsets and the sigmoid fused.  Measured on B200 the library convolution is about three times
-# faster for these 18- and 27-channel outputs, so it is the default.
-OFFSET_BRANCH = os.environ.get('DCN_B200_OFFSET_BRANCH', 'library')
+# How an inference-time Pack layer computes its offset branch: 'kernel' (default) = this
+# library's tensor-map convolution, reading the same zero-bordered channels-last copy of the
+# input as the deformable kernel (the copy is made once per layer); 'library' = the branch's own
+# nn.Conv2d arithmetic (cuDNN) on a channels-last copy of the input.
+OFFSET_BRANCH = os.environ.get('DCN_B200_OFFSET_BRANCH', 'kernel')
 
 
 def branch_conv(x, conv, dtype):
@@ -125,7 +124,7 @@ def library_offset_branch(x, conv, dtype, sigmoid_from=None):
 
 
 def deform_from_branch(x, out, n_offset, weight, bias, stride, padding, dilation, groups,
-                       deform_groups):
+                       deform_groups, padded=None):
     """The deformable convolution fed by the raw branch output `out` (offsets, then mask
     logits), which the tensor-core kernel reads where it lies, sigmoid included: no split,
     copy or sigmoid pass.  Returns None when the problem runs on another kernel."""
@@ -133,7 +132,8 @@ def deform_from_branch(x, out, n_offset, weight, bias, stride, padding, dilation
     bias = ext_module.cast_weight(bias, x.dtype)
     y = x.new_empty(conv_output_size(x, weight, _pair(stride), _pair(padding), _pair(dilation)))
     done = ext_module.forward_from_branch(x, out, n_offset, weight, bias, y, _pair(stride),
-                                          _pair(padding), _pair(dilation), groups, deform_groups)
+                                          _pair(padding), _pair(dilation), groups, deform_groups,
+                                          padded=padded)
     return y if done else None
 
 
@@ -255,21 +255,25 @@ class ModulatedDeformConv2dPack(ModulatedDeformConv2d):
         if fused_branch_applies(x, self.conv_offset):
             # the branch and the deformable kernel read one channels-last copy of the input
             dtype = branch_dtype(x)
-            x = shared_layout(x.to(dtype))
+            x = x.to(dtype)
+            padded = None
             if OFFSET_BRANCH == 'kernel':
+                # one zero-bordered channels-last copy feeds the branch and the deformable kernel
+                padded = ext_module.pad_channels_last(x)
                 out = ext_module.conv_offset_forward(
                     x, ext_module.cast_weight(self.conv_offset.weight, dtype),
                     ext_module.cast_weight(self.conv_offset.bias, dtype),
-                    self.stride, self.padding, self.dilation, sigmoid_from=two_thirds)
-                offset, mask = out[:, :two_thirds], out[:, two_thirds:]
+                    self.stride, self.padding, self.dilation, padded=padded)
             else:
+                x = shared_layout(x)
                 out = branch_conv(x, self.conv_offset, dtype)
-                y = deform_from_branch(x, out, two_thirds, self.weight, self.bias, self.stride,
-                                       self.padding, self.dilation, self.groups,
-                                       self.deform_groups)
-                if y is not None:
-                    return y
-                offset, mask = split_branch(out, two_thirds)
+            # the deformable kernel reads offsets and mask logits where the branch left them
+            y = deform_from_branch(x, out, two_thirds, self.weight, self.bias, self.stride,
+                                   self.padding, self.dilation, self.groups,
+                                   self.deform_groups, padded=padded)
+            if y is not None:
+                return y
+            offset, mask = split_branch(out, two_thirds)
         else:
             out = self.conv_offset(x)
             offset = out[:, :two_thirds].contiguous()
