@@ -77,7 +77,6 @@ const Knobs &knobs() {
     k.window = env_int("DCN_B200_WINDOW", -1, -1, 16);
     k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
     k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
-    g_debug_flags.store(env_int("DCN_B200_DEBUG_FLAGS", 0, 0, 255));
   });
   return k;
 }

@@ -81,6 +81,14 @@ enum { kBM = 128 };
 // (mmcv/ops/csrc/common/cuda/modulated_deform_conv_cuda_kernel.cuh:80-108) and the
 // sampling gate of its caller (same file, :237-239).  A position that is NaN or
 // outside (-1, H) x (-1, W) yields four zero weights.
+//
+// A weight of +0 (all bits clear) marks a corner that the reference does not read: it lies
+// outside the plane, or the whole position fails the gate.  A corner inside the plane whose
+// weight happens to be zero (a grid-aligned position, a zero mask value) is read by the
+// reference and multiplied -- 0 * Inf and 0 * NaN give NaN there -- so its weight is returned
+// as -0: consumers test the BITS (corner_is_read) and multiply whatever they read.
+__device__ __forceinline__ float read_weight(float w) { return w == 0.f ? -0.f : w; }
+__device__ __forceinline__ bool corner_is_read(float w) { return __float_as_uint(w) != 0u; }
 __device__ __forceinline__ void tap_weights(float off_h, float off_w, float m,
                                             int h_base, int w_base, int H, int W,
                                             float4 &wt, int &h_low, int &w_low) {
@@ -97,10 +105,10 @@ __device__ __forceinline__ void tap_weights(float off_h, float off_w, float m,
     const float hh = 1.f - lh, hw = 1.f - lw;
     const bool top = h_low >= 0, left = w_low >= 0;
     const bool bot = h_low + 1 <= H - 1, right = w_low + 1 <= W - 1;
-    wt.x = (top && left) ? hh * hw * m : 0.f;
-    wt.y = (top && right) ? hh * lw * m : 0.f;
-    wt.z = (bot && left) ? lh * hw * m : 0.f;
-    wt.w = (bot && right) ? lh * lw * m : 0.f;
+    wt.x = (top && left) ? read_weight(hh * hw * m) : 0.f;
+    wt.y = (top && right) ? read_weight(hh * lw * m) : 0.f;
+    wt.z = (bot && left) ? read_weight(lh * hw * m) : 0.f;
+    wt.w = (bot && right) ? read_weight(lh * lw * m) : 0.f;
   }
 }
 

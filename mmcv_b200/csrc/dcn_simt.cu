@@ -48,15 +48,15 @@ dcn_fwd_simt_direct(const Geom g, const T *__restrict__ x, const T *__restrict__
           int h_low, w_low;
           tap_weights(oh, ow, m, ho * g.stride_h - g.pad_h + i * g.dil_h,
                       wo * g.stride_w - g.pad_w + j * g.dil_w, g.H, g.W, wt, h_low, w_low);
-          if (wt.x == 0.f && wt.y == 0.f && wt.z == 0.f && wt.w == 0.f) continue;
+          if (!(corner_is_read(wt.x) || corner_is_read(wt.y) || corner_is_read(wt.z) || corner_is_read(wt.w))) continue;
           const long long o00 = (long long)h_low * g.in_sh + (long long)w_low * g.in_sw;
           for (int c = c0; c < c1; ++c) {
             const T *pl = x_n + (long long)c * g.in_sc + o00;
             float v = 0.f;
-            if (wt.x != 0.f) v += wt.x * ld_as_float(pl, 0);
-            if (wt.y != 0.f) v += wt.y * ld_as_float(pl, g.in_sw);
-            if (wt.z != 0.f) v += wt.z * ld_as_float(pl, g.in_sh);
-            if (wt.w != 0.f) v += wt.w * ld_as_float(pl, g.in_sh + g.in_sw);
+            if (corner_is_read(wt.x)) v += wt.x * ld_as_float(pl, 0);
+            if (corner_is_read(wt.y)) v += wt.y * ld_as_float(pl, g.in_sw);
+            if (corner_is_read(wt.z)) v += wt.z * ld_as_float(pl, g.in_sh);
+            if (corner_is_read(wt.w)) v += wt.w * ld_as_float(pl, g.in_sh + g.in_sw);
             acc += v * ld_as_float(w_co, (long long)(c - c_begin) * g.T + tap);
           }
         }
@@ -188,10 +188,10 @@ dcn_fwd_simt_tiled(const Geom g, const T *__restrict__ x, const T *__restrict__ 
       const T *pl = x_n + (long long)(c0 + cl) * g.in_sc + (long long)hw.x * g.in_sh +
                     (long long)hw.y * g.in_sw;
       float v = 0.f;
-      if (wt.x != 0.f) v = fmaf(wt.x, ld_as_float(pl, 0), v);
-      if (wt.y != 0.f) v = fmaf(wt.y, ld_as_float(pl, g.in_sw), v);
-      if (wt.z != 0.f) v = fmaf(wt.z, ld_as_float(pl, g.in_sh), v);
-      if (wt.w != 0.f) v = fmaf(wt.w, ld_as_float(pl, g.in_sh + g.in_sw), v);
+      if (corner_is_read(wt.x)) v = fmaf(wt.x, ld_as_float(pl, 0), v);
+      if (corner_is_read(wt.y)) v = fmaf(wt.y, ld_as_float(pl, g.in_sw), v);
+      if (corner_is_read(wt.z)) v = fmaf(wt.z, ld_as_float(pl, g.in_sh), v);
+      if (corner_is_read(wt.w)) v = fmaf(wt.w, ld_as_float(pl, g.in_sh + g.in_sw), v);
       col_s[r * kTP + gpx] = v;
     }
     // weight slice: w_s[r][co] = W[co0 + co][c0 - c_begin + r / T][r % T]

@@ -535,14 +535,16 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                   tap_weights(RawOf<TIO>::to_float(oh[k]), RawOf<TIO>::to_float(ow[k]),
                               mskp ? mask_value(g, RawOf<TIO>::to_float(mm[k])) : 1.f, hb + ei * g.dil_h,
                               wb + ej * g.dil_w, g.H, g.W, wt, h_low, w_low);
-                // a weight that is (or rounds to) zero is stored as the integer 0: such a
-                // corner is not read
+                // a corner the reference does not read has the integer 0 as its weight and is not
+                // read here either; a corner it reads with a weight that is (or rounds to) zero
+                // keeps a signed zero, so that a non-finite sample under it gives NaN as it does
+                // in the reference
                 typename MT::TabW wq;
                 if constexpr (MODE == kModeTf32x3) {
-                  wq.x = wt.x == 0.f ? 0u : __float_as_uint(wt.x);
-                  wq.y = wt.y == 0.f ? 0u : __float_as_uint(wt.y);
-                  wq.z = wt.z == 0.f ? 0u : __float_as_uint(wt.z);
-                  wq.w = wt.w == 0.f ? 0u : __float_as_uint(wt.w);
+                  wq.x = __float_as_uint(wt.x);
+                  wq.y = __float_as_uint(wt.y);
+                  wq.z = __float_as_uint(wt.z);
+                  wq.w = __float_as_uint(wt.w);
                 } else {
                   uint32_t b0, b1, b2, b3;
                   if constexpr (MODE == kModeBf16) {
@@ -556,8 +558,10 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                     b2 = __half_as_ushort(__float2half_rn(wt.z));
                     b3 = __half_as_ushort(__float2half_rn(wt.w));
                   }
-                  b0 = (b0 & 0x7fffu) ? b0 : 0u; b1 = (b1 & 0x7fffu) ? b1 : 0u;
-                  b2 = (b2 & 0x7fffu) ? b2 : 0u; b3 = (b3 & 0x7fffu) ? b3 : 0u;
+                  b0 = (b0 & 0x7fffu) ? b0 : (corner_is_read(wt.x) ? 0x8000u : 0u);
+                  b1 = (b1 & 0x7fffu) ? b1 : (corner_is_read(wt.y) ? 0x8000u : 0u);
+                  b2 = (b2 & 0x7fffu) ? b2 : (corner_is_read(wt.z) ? 0x8000u : 0u);
+                  b3 = (b3 & 0x7fffu) ? b3 : (corner_is_read(wt.w) ? 0x8000u : 0u);
                   wq.x = b0 | (b1 << 16);
                   wq.y = b2 | (b3 << 16);
                 }

@@ -147,7 +147,11 @@ __device__ __forceinline__ Smem2 carve2(uint8_t *base, const TcPlan &tp) {
 __device__ __forceinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, int code, int backoff) {
   uint8_t *ctrl = smem_aligned();
   volatile int *abort_s = (volatile int *)(ctrl + kCtrlAbort);
-  const unsigned long long limit = *(const unsigned long long *)(ctrl + kCtrlLimit);
+  // The tensor-core issuer sits in the middle of every dependency chain (codes 4-6): its waits
+  // run out after the limit, everybody else's after twice the limit, so that the recorded code
+  // names the hand-over nearest to the producer that went missing.
+  unsigned long long limit = *(const unsigned long long *)(ctrl + kCtrlLimit);
+  if (code < 4 || code > 6) limit *= 2;
   const unsigned long long t0 = globaltimer_ns();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;

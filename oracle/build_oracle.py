@@ -4,6 +4,10 @@ Two artefacts, both git-ignored and both carried to a GPU machine as files:
 
 * ``oracle/libdcn_oracle.so`` -- the plain-C restatement in ``dcn_oracle.c``
   (gcc, OpenMP).
+* ``oracle/_ref/pywrap/`` -- the reference's three unchanged Python files of this path
+  (the two operator wrappers and the extension loader they import), copied so that the GPU
+  tests can run the reference's own wrappers on top of this library's extension module on a
+  machine without the reference checkout.  git-ignored like the rest of ``oracle/_ref/``.
 * ``oracle/_ref/dcn_ref_ext.so`` -- the UNMODIFIED reference CPU implementation,
   compiled from the reference checkout where it lies (four translation units of
   mmcv/ops/csrc/pytorch plus the two helper headers in mmcv/ops/csrc/common),
@@ -22,7 +26,11 @@ PORT_SO = os.path.join(HERE, 'libdcn_oracle.so')
 REF_DIR = os.path.join(HERE, '_ref')
 REF_NAME = 'dcn_ref_ext'
 REF_SO = os.path.join(REF_DIR, REF_NAME + '.so')
-DEFAULT_REF_ROOT = os.environ.get('DCN_REFERENCE_ROOT', '/root/reference')
+# where the reference checkout lies: from the environment (no default location is assumed)
+DEFAULT_REF_ROOT = os.environ.get('DCN_REFERENCE_ROOT', '')
+WRAP_DIR = os.path.join(REF_DIR, 'pywrap')
+# the reference's Python wrappers of this path (+ the loader they import), relative to its root
+REF_WRAPPERS = ['mmcv/utils/ext_loader.py', 'mmcv/ops/modulated_deform_conv.py', 'mmcv/ops/deform_conv.py']
 
 # The reference's translation units for this path, relative to its root.
 REF_UNITS = [
@@ -50,10 +58,23 @@ def build_port(force=False):
     return PORT_SO
 
 
+def copy_wrappers(ref_root=DEFAULT_REF_ROOT):
+    """Copies the reference's wrapper files into oracle/_ref/pywrap (same relative paths)."""
+    import shutil
+    if not ref_root or not os.path.isdir(ref_root):
+        return WRAP_DIR if os.path.isdir(WRAP_DIR) else None
+    for rel in REF_WRAPPERS:
+        dst = os.path.join(WRAP_DIR, rel)
+        os.makedirs(os.path.dirname(dst), exist_ok=True)
+        shutil.copyfile(os.path.join(ref_root, rel), dst)
+    return WRAP_DIR
+
+
 def build_ref(ref_root=DEFAULT_REF_ROOT, force=False):
     """Compile the reference CPU path; returns the .so path or None."""
-    if not os.path.isdir(ref_root):
+    if not ref_root or not os.path.isdir(ref_root):
         return REF_SO if os.path.exists(REF_SO) else None
+    copy_wrappers(ref_root)
     binding = os.path.join(HERE, 'ref_binding.cpp')
     ref_sources = [os.path.join(ref_root, rel) for _, rel in REF_UNITS]
     if not force and _newer(REF_SO, [binding] + ref_sources):

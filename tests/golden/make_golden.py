@@ -11,7 +11,7 @@ extension built by ``python oracle/build_oracle.py``.  Writes
   offset branch produced, and the gradients of the reference test).
 * ``dcn_cases.npz`` -- seeded small cases (inputs, parameters, forward output and
   gradients) covering kernel/stride/padding/dilation/group/deform-group
-  variety, out-of-range, grid-aligned and non-finite offsets.
+  variety, out-of-range, grid-aligned and non-finite offsets, non-finite input samples.
 
 Run: ``python tests/golden/make_golden.py``
 """
@@ -31,7 +31,7 @@ sys.path.insert(0, HERE)
 import oracle  # noqa: E402
 import ref_wrappers  # noqa: E402
 
-REF_ROOT = os.environ.get('DCN_REFERENCE_ROOT', '/root/reference')
+REF_ROOT = os.environ.get('DCN_REFERENCE_ROOT', '')   # the reference checkout (required)
 
 
 def module_literals(path, names):
@@ -65,6 +65,11 @@ CASES = [
     ('v1_g2_dg2_d2', 2, 8, 10, 8, 4, (3, 3), (1, 1), (2, 2), (2, 2), 2, 2, False, False, 2.0, 'int'),
     ('v1_k2_nopad', 3, 3, 5, 5, 2, (2, 2), (1, 1), (0, 0), (1, 1), 1, 1, False, False, 0.7, ''),
     ('v1_c64', 1, 64, 10, 14, 32, (3, 3), (1, 1), (1, 1), (1, 1), 1, 1, False, False, 1.5, ''),
+    # Inf / NaN among the input samples, with some grid-aligned offsets (a corner of weight zero
+    # over a non-finite sample gives NaN in the reference: 0 * Inf) and some zero mask values
+    ('v2_input_nonfinite', 1, 8, 9, 9, 8, (3, 3), (1, 1), (1, 1), (1, 1), 1, 2, True, True, 1.5, 'input_nonfinite int'),
+    ('v2_c64_input_nonfinite', 1, 64, 12, 12, 64, (3, 3), (1, 1), (1, 1), (1, 1), 1, 1, True, True, 1.5, 'input_nonfinite int'),
+    ('v1_input_nonfinite', 1, 8, 9, 9, 8, (3, 3), (1, 1), (1, 1), (1, 1), 1, 1, False, False, 1.5, 'input_nonfinite int'),
 ]
 
 
@@ -88,6 +93,15 @@ def make_case(spec, seed):
         flat[idx[6:]] = float('-inf')
     mask = (torch.sigmoid(torch.randn(N, dg * kh * kw, Ho, Wo, generator=gen))
             if with_mask else None)
+    if 'input_nonfinite' in special:
+        flat = x.view(-1)
+        idx = torch.randperm(flat.numel(), generator=gen)[:6]
+        flat[idx[:2]] = float('nan')
+        flat[idx[2:4]] = float('inf')
+        flat[idx[4:]] = float('-inf')
+        if mask is not None:
+            mask = torch.where(torch.rand(mask.shape, generator=gen) < 0.1,
+                               torch.zeros_like(mask), mask)
     bound = 1.0 / (C // g * kh * kw) ** 0.5
     w = (torch.rand(Co, C // g, kh, kw, generator=gen) * 2 - 1) * bound * 3 ** 0.5
     b = (torch.rand(Co, generator=gen) * 0.2 - 0.1) if with_bias else None
@@ -107,7 +121,7 @@ def run_case(v2, v1, spec, t):
         y = v1.deform_conv2d(leaf['x'], leaf['offset'], leaf['weight'], s, p, d,
                              g, dg, False, 32)
     out = {'out': y.detach()}
-    if 'nonfinite' not in special:
+    if 'nonfinite' not in special:   # (either kind: no gradients for non-finite cases)
         y.backward(t['grad_out'])
         for n in ('x', 'offset', 'mask', 'weight', 'bias'):
             if leaf[n] is not None:

@@ -72,8 +72,22 @@ def _exec(name, path, package):
     return mod
 
 
-def load(ext, ref_root='/root/reference'):
+def default_root():
+    """Where the reference's wrapper files are: the checkout named by DCN_REFERENCE_ROOT, else
+    the copies the checker's build recipe left under oracle/_ref/pywrap; None if neither exists."""
+    root = os.environ.get('DCN_REFERENCE_ROOT', '')
+    if root and os.path.isfile(os.path.join(root, 'mmcv/ops/deform_conv.py')):
+        return root
+    here = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    wrap = os.path.join(here, 'oracle', '_ref', 'pywrap')
+    return wrap if os.path.isfile(os.path.join(wrap, 'mmcv/ops/deform_conv.py')) else None
+
+
+def load(ext, ref_root=None):
     """Returns (modulated_deform_conv module, deform_conv module, registry)."""
+    ref_root = ref_root or default_root()
+    if ref_root is None:
+        raise FileNotFoundError('the reference wrapper files are not available')
     for n in _NAMES:
         sys.modules.pop(n, None)
     reg = _Registry()

@@ -243,13 +243,14 @@ def test_state_dict_key_upgrade():
         assert 'conv2_offset.weight' in legacy2
 
 
-@pytest.mark.skipif(not os.path.isdir('/root/reference/mmcv'), reason='no reference checkout')
 def test_reference_wrappers_accept_this_extension():
     # The reference's unchanged Python wrappers load on top of this _ext (all five names are
     # found) and reach it; on CPU tensors the call must fail loudly instead of falling back.
     import sys
     sys.path.insert(0, os.path.join(ROOT, 'tests', 'golden'))
     import ref_wrappers
+    if ref_wrappers.default_root() is None:
+        pytest.skip('the reference wrapper files are not available (oracle/build_oracle.py copies them)')
     v2, v1, reg = ref_wrappers.load(_ext)
     try:
         assert set(reg.modules) == {'DCN', 'DCNv2'}
