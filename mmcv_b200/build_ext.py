@@ -15,6 +15,7 @@ LIB_DIR = os.path.join(PKG, 'lib')
 LIB = os.path.join(LIB_DIR, 'libdcn_b200.so')
 SOURCES = ['dcn_api.cu', 'dcn_simt.cu', 'dcn_tc.cu', 'dcn_tc2.cu', 'dcn_conv.cu', 'dcn_static.cu', 'dcn_bwd.cu']
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
+EXTRA_FLAGS = os.environ.get('DCN_B200_NVCC_FLAGS', '').split()   # e.g. -DDCN_TC2_ABLATE for experiments
 
 
 def _deps():
@@ -39,6 +40,7 @@ def _compile(src, obj, verbose):
         return ''
     cmd = [NVCC, '-gencode', 'arch=compute_100a,code=sm_100a', '-lineinfo', '-O3',
            '-std=c++17', '-Xcompiler', '-fPIC', '-I', os.path.join(ROOT, 'include'), '-I', CSRC]
+    cmd += EXTRA_FLAGS
     if verbose:
         cmd += ['-Xptxas', '-v']
     cmd += ['-c', src, '-o', obj]

@@ -58,7 +58,7 @@ int env_int(const char *name, int dflt, int lo, int hi) {
 // All of them, read once per process (the first call that plans a problem).
 struct Knobs {
   int a_stages, b_stages, producers, tile_w, simt_tiled, counters;
-  int kernel;      // 1: first-generation tensor-core kernel for every mode, 2: default routing
+  int kernel;      // 1: first-generation tensor-core kernel always, 2: default routing, 3: second generation wherever it fits
   int window;      // -1: planner's choice, 0: no shared-memory input window, n: margin n
   int epi_tma;     // -1: planner's choice, 0/1
   int small_l1;    // 1: give the kernel the largest shared-memory configuration
@@ -73,7 +73,7 @@ const Knobs &knobs() {
     k.tile_w = env_int("DCN_B200_TILE_W", 0, 0, 128);
     k.simt_tiled = env_int("DCN_B200_SIMT_TILED", 1, 0, 1);
     k.counters = env_int("DCN_B200_COUNTERS", 0, 0, 1);
-    k.kernel = env_int("DCN_B200_KERNEL", 2, 1, 2);
+    k.kernel = env_int("DCN_B200_KERNEL", 2, 1, 3);
     k.window = env_int("DCN_B200_WINDOW", -1, -1, 16);
     k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
     k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
@@ -195,6 +195,11 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   // offsets into the padded copy are 31-bit byte offsets within a sample
   if ((long long)(g.H + 3) * (g.W + 2) * g.C * 2 >= 2147483647LL) return;
   if (tp->items >= 2147483647LL) return;
+  // Routing (measured on C = 64..512, 1..8 deform groups): every lane of this kernel computes
+  // the tap entry of its (row, unit) afresh, while the first-generation kernel shares one tap
+  // table between the chunks of a deform group.  With 64 or fewer channels per deform group
+  // there is little to share and this kernel wins; above that the first generation does.
+  if (kn.kernel != 3 && g.cpdg > 64) return;
   TcPlan t = *tp;
   t.version = 2;
   t.producer_cfg = 16;  // 16 gather warps that build their own tap entries
@@ -269,7 +274,7 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp, bool all
   const int ch = tf32 ? 32 : 64, cpv = tf32 ? 4 : 8;
   if (g.Cg % cpv != 0 || g.cpdg % cpv != 0) return false;
   if ((long long)g.N * g.H * g.W >= 2147483647LL) return false;
-  if ((long long)g.H * g.W * g.C * (tf32 ? 4 : 2) >= 4294967295LL) return false;
+  if ((long long)(g.H + 2) * (g.W + 2) * g.C * (tf32 ? 4 : 2) >= 4294967295LL) return false;
   if (g.kh > 255 || g.kw > 255 || g.T > 4095) return false;
   const Knobs &kn = knobs();
   const int a_forced = kn.a_stages, b_forced = kn.b_stages;
@@ -364,7 +369,9 @@ bool plan_tc(const DcnFwdParams *p, const Geom &g, int sms, TcPlan *tp, bool all
   tp->items = mtiles * g.groups * tp->NT;
   tp->grid = (int)(tp->items < sms ? tp->items : sms);
   tp->version = 1;
-  if (!tf32 && kn.kernel == 2 && allow_v2) plan_tc2(p, g, tp);
+  if (!tf32 && kn.kernel >= 2 && allow_v2) plan_tc2(p, g, tp);
+  // the first-generation 16-bit kernel reads a caller's zero-bordered copy in place
+  tp->in_pad = (tp->version == 1 && !tf32 && p->padded_input) ? 1 : 0;
   return true;
 }
 
@@ -386,6 +393,8 @@ void layout_workspace(const DcnFwdParams *p, const Geom &g, bool tc, const TcPla
         ws->xcl_bytes = padded_copy_bytes(g);
         off = align_up(off + ws->xcl_bytes, 256);
       }
+    } else if (tp.in_pad) {
+      // reads the caller's zero-bordered copy
     } else if (!input_is_ready(p, g, tp.op_format)) {
       ws->xcl_off = off;
       ws->xcl_bytes = (size_t)g.N * g.H * g.W * g.C * (tp.tiles_per_stage == 2 ? 4 : 2);
@@ -450,7 +459,7 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
   // meet the fp32 tolerance, so the request degrades instead of failing.
   layout_workspace(p, pl->g, pl->tc, pl->tp, &pl->ws);
   pl->stage = pl->tc && pl->ws.xcl_bytes != 0;
-  if (pl->tc && pl->tp.version == 2 && p->padded_input &&
+  if (pl->tc && (pl->tp.version == 2 || pl->tp.in_pad) && p->padded_input &&
       ((size_t)p->padded_input_bytes != padded_copy_bytes(pl->g) || ((uintptr_t)p->padded_input & 255)))
     return fail(DCN_ERR_ARG, "padded_input must be %zu bytes and 256-byte aligned (got %lld)",
                 padded_copy_bytes(pl->g), (long long)p->padded_input_bytes);
@@ -555,7 +564,7 @@ static int run_fwd(const DcnFwdParams *p, void *workspace, size_t workspace_byte
     if (ev) cudaEventRecord(ev[3], s);
     return DCN_OK;
   }
-  const void *xcl = (pl.tp.version == 2 && p->padded_input) ? p->padded_input : p->input;
+  const void *xcl = ((pl.tp.version == 2 || pl.tp.in_pad) && p->padded_input) ? p->padded_input : p->input;
   if (pl.stage) {
     void *dst = ws + pl.ws.xcl_off;
     e = launch_stage_input_cl(pl.g, p->input, p->dtype, dst, pl.tp.op_format,

@@ -61,6 +61,7 @@ struct TcPlan {
   int io_bytes;            // element size of the tensors (bias staging in the epilogue)
   // --- second-generation 16-bit kernel (dcn_tc2.cu) ---
   int version;             // 1: dcn_fwd_tc, 2: dcn_fwd_tc2
+  int in_pad;              // first-generation kernel: 1 when it reads the zero-bordered copy (pitch W + 2)
   int KH;                  // 32-channel half-chunks per conv group
   int U;                   // (half-chunk, tap) units per tile = KH*T; a k-stage holds two
   int ndu;                 // max deform groups touched by one half-chunk

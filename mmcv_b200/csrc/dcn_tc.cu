@@ -373,7 +373,8 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     const int v = lane & 7;      // 16-byte vector (8 bf16 / 4 fp32 channels) of the 128-byte row
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
-    const uint32_t cW2 = (uint32_t)g.C * MT::kEsz, cH2 = (uint32_t)g.W * (uint32_t)g.C * MT::kEsz;
+    const uint32_t Wp = (uint32_t)(g.W + 2 * tp.in_pad);   // row pitch of the copy, in pixels
+    const uint32_t cW2 = (uint32_t)g.C * MT::kEsz, cH2 = Wp * (uint32_t)g.C * MT::kEsz;
     const uint32_t cHW2 = cH2 + cW2;
     // this thread's first row of a stage and where its 16 bytes go (128-byte swizzle); its
     // other rows are kRowStep rows further, which keeps the swizzle phase
@@ -445,7 +446,8 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
         }
       }
       pt.lap(17);
-      const char *xb = reinterpret_cast<const char *>(a.xcl) + (long long)t.n * g.H * g.W * g.C * MT::kEsz;
+      const char *xb = reinterpret_cast<const char *>(a.xcl) +
+                       (long long)t.n * (g.H + 2 * tp.in_pad) * Wp * g.C * MT::kEsz;
       int cur_lo = -1, cur_nd = 0;
       for (int cc = 0; cc < tp.KC && ok; ++cc) {
         const int c0 = t.grp * g.Cg + cc * MT::kCh;
@@ -567,7 +569,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
                 }
                 const int slot = (tab0 + etap * tp.ndgc + edgl) * kTabStride + trow;
                 tabw[slot] = wq;
-                L.tab_off[slot] = (uint32_t)((h_low * g.W + w_low) * g.C * MT::kEsz);
+                L.tab_off[slot] = (uint32_t)(((h_low + tp.in_pad) * (int)Wp + w_low + tp.in_pad) * g.C * MT::kEsz);
               }
             }
           }

@@ -150,15 +150,18 @@ __device__ __forceinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, i
   // The tensor-core issuer sits in the middle of every dependency chain (codes 4-6): its waits
   // run out after the limit, everybody else's after twice the limit, so that the recorded code
   // names the hand-over nearest to the producer that went missing.
-  unsigned long long limit = *(const unsigned long long *)(ctrl + kCtrlLimit);
-  if (code < 4 || code > 6) limit *= 2;
-  const unsigned long long t0 = globaltimer_ns();
+  // (the timer is first read at the sixteenth poll: short waits, the usual case, never pay for it)
+  unsigned long long t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if (backoff) __nanosleep((unsigned)backoff);
     if ((it & 15u) == 0u) {
       if (*abort_s) return false;
-      if (globaltimer_ns() - t0 > limit) {
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      unsigned long long limit = *(const unsigned long long *)(ctrl + kCtrlLimit);
+      if (code < 4 || code > 6) limit *= 2;
+      if (now - t0 > limit) {
         *abort_s = 1;
         atomicCAS(*(int **)(ctrl + kCtrlStatus), 0, code);
         return false;
@@ -167,7 +170,10 @@ __device__ __forceinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, i
   }
 }
 // Bounded wait.  Returns false when the block is aborting.
-__device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int code, int backoff = 100) {
+#ifndef DCN_TC2_BACKOFF
+#define DCN_TC2_BACKOFF 100
+#endif
+__device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int code, int backoff = DCN_TC2_BACKOFF) {
   if (mbar_try_wait(bar, parity)) return true;
   return mbar_wait_slow2(bar, parity, code, backoff);
 }
@@ -366,6 +372,13 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         staged_co0[buf] = co0;
       }
       const uint32_t taddr = tmem_base + (uint32_t)(buf * tp.BN) + ((uint32_t)(warp * 32) << 16);
+#ifdef DCN_TC2_ABLATE
+      if (a.debug_flags & 32) {
+        uint32_t r[16];
+        tmem_ld16(taddr, r);
+        tmem_ld_wait();
+      } else
+#endif
       if (tp.epi_tma) {
         for (int c0 = 0; c0 < ncols; c0 += 32) {
           // the slab about to be overwritten must have been read by the store issued from it
@@ -473,6 +486,9 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         const uint64_t adesc = smem_desc_sw128(smem_u32(L.a) + sa * (uint32_t)kTileBytes);
         const uint64_t bdesc = smem_desc_sw128(smem_u32(L.b) + sb * b_stage_bytes);
         if (elect_one()) {
+#ifdef DCN_TC2_ABLATE
+          if (!(a.debug_flags & 64))
+#endif
 #pragma unroll
           for (int k = 0; k < 4; ++k)
             umma_bf16(d_tmem, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), idesc,
@@ -504,6 +520,11 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           if (!ok) break;
           pt.lap(14);
           const bool withhold = (a.debug_flags & 1) && item + gridDim.x >= items && ks == tp.S - 1;
+#ifdef DCN_TC2_ABLATE
+          if (a.debug_flags & 512) {
+            mbar_arrive(full_b + 8 * sb);
+          } else
+#endif
           if (!withhold) {
             mbar_arrive_expect_tx(full_b + 8 * sb, b_stage_bytes);
             bulk_copy_g2s(smem_u32(L.b) + sb * b_stage_bytes, src + (size_t)ks * b_stage_bytes,
@@ -529,6 +550,9 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           // buffer wb was last used by window wq - 2
           ok = mbar_wait2(win_empty + 8 * wb, ((wq >> 1) & 1u) ^ 1u, 11);
           if (!ok) break;
+#ifdef DCN_TC2_ABLATE
+          if (a.debug_flags & 1024) { mbar_arrive(win_full + 8 * wb); continue; }
+#endif
           mbar_arrive_expect_tx(win_full + 8 * wb, wbytes);
           // coordinates in the padded tensor: (channel, column + 1, row + 1, sample)
           tma_load_4d(smem_u32(L.win) + wb * wbytes, &a.win_map, t.grp * g.Cg + hc * 32,
@@ -706,8 +730,14 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       pt.lap(3);
       if (!ok) break;
       const uint32_t stage_row = a_row + sa * (uint32_t)kTileBytes;
+#ifdef DCN_TC2_ABLATE
+      const int abl = a.debug_flags;
+#else
+      constexpr int abl = 0;
+#endif
 #pragma unroll 1
       for (int p = 0; p < 2; ++p) {
+        if (abl & 16) break;
         // the entry of (row0 + 64 p, unit): built by lane (lane & ~1) | p
         const int src = (lane & ~1) | p;
         uint32_t w0 = __shfl_sync(0xffffffffu, ew0, src), w1 = __shfl_sync(0xffffffffu, ew1, src);
@@ -718,6 +748,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           ow = __shfl_sync(0xffffffffu, eow, src);
           // dead vectors (no such unit) read the window's first pixels with zero weights
           from_window = __all_sync(0xffffffffu, ow != kNoWin || (v1_dead && v2_dead));
+          if (abl & 256) from_window = true;
         }
         if (kWin && from_window) {
           // The usual case: every lane of the warp reads the window.  The lanes of unit 0 start
@@ -736,15 +767,20 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
             const uint32_t q16 = 16u * (k ? q2 : q1);
             uint32_t tok = 0;
             uint4 X[4];
+            if (abl & 2) {
+              X[0] = X[1] = X[2] = X[3] = make_uint4(w0, w1, ow, q16);
+            } else {
             X[0] = lds16(s1 + q16, tok); X[1] = lds16(s2 + q16, tok);
             X[2] = lds16(s1 + win_rb + q16, tok); X[3] = lds16(s2 + win_rb + q16, tok);
+            }
             uint4 wa = wa0;
             wa.x |= tok;  // tok is 0: keeps the blend behind the loads
             uint4 r;
-            if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
+            if (abl & 8) r = X[0];
+            else if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
             else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
             if (k ? v2_dead : v1_dead) r = make_uint4(0u, 0u, 0u, 0u);
-            sts16(dst + (k ? a_c2 : a_c1), r);
+            if (!(abl & 128)) sts16(dst + (k ? a_c2 : a_c1), r);
           }
         } else {
           // some neighbourhood of the warp's pass lies outside the window (or there is no
@@ -774,7 +810,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       pt.lap(4);
       // ---- the next stage: its entry from the loads issued a stage ago, then the loads of the
       // stage after it
-      entry_build();
+      if (!(abl & 4)) entry_build();
       sa += (uint32_t)kGroups2;
       while (sa >= (uint32_t)A) { sa -= (uint32_t)A; pa ^= 1u; }
       cur = nxt;
@@ -786,7 +822,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         c_grp = t_grp;
       }
       if (nxt.item < items) advance(nxt);
-      entry_loads(nxt);
+      if (!(abl & 4)) entry_loads(nxt);
       if (kWin) {
         // windows before the next stage's first unit go back to the loader (the loads from
         // them have returned: their values were consumed above)

@@ -66,9 +66,12 @@ def test_plan_routes_and_sizes():
     # + 16 gather warps that build their own tap entries
     assert info.kernel_version == 2 and info.producer_layout == 16 and info.block == 24 * 32
     assert info.operand_stages >= 2 and info.weight_stages == 2
-    rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
+    rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=4))
     assert rc == 0 and info.kernel_version == 2
     assert info.window_h >= 10 + 6 and info.window_w >= 18 + 6 and info.window_w % 2 == 0
+    # more than 64 channels per deform group: the first-generation kernel's shared tap table wins
+    rc, info = plan(params(N=8, C=256, H=100, W=168, Co=256, dg=1))
+    assert rc == 0 and info.path == _lib.PATH_TCGEN05 and info.kernel_version == 1
     # a strided layer samples too widely for the shared-memory window: first-generation kernel
     rc, info = plan(params(C=512, Co=512, H=64, W=64, s=2, p=2, d=2, dg=4))
     assert rc == 0 and info.kernel_version == 1 and (info.Ho, info.Wo) == (32, 32)
