@@ -40,12 +40,11 @@ WORKLOADS = {
                desc='DCNv2 N=4 C=512 64x64 3x3 s2 p2 d2 dg=4 bias'),
 }
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel, from the
-# committed ncu summary under profiles/ (None until a capture exists for the workload).
+# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the main kernel per sample, from
+# an ncu capture of dcn_fwd_tc2 at batch 16 (253.3 MB read + 104.3 MB written = 357.6 MB); the
+# traffic grows in proportion to the samples processed.  None where no capture exists.
 NCU_TRAFFIC_BYTES = {
-    # 356.9 MB measured at batch 16 (profiles/dcn_fwd_tc_bf16_c5_batch16_ncu_full.md), scaled
-    # by the batch: traffic grows in proportion to the samples processed
-    'c5': 356.9e6 / 16,
+    'c5': 357.6e6 / 16,
 }
 
 
@@ -579,12 +578,21 @@ def main():
                          'and re-laid-out once, as in serving)')
     ap.add_argument('--counters', action='store_true',
                     help='also report the in-kernel phase counters of the first CTA')
+    ap.add_argument('--ablate', type=int, default=0,
+                    help='timing experiments only (results are wrong): bit mask handed to '
+                         'dcn_debug_configure; needs a library built with '
+                         'DCN_B200_NVCC_FLAGS=-DDCN_TC2_ABLATE.  2: gather loads nothing, 8: no blend, '
+                         '128: no operand store, 16: no gather body, 4: tap entries built once, '
+                         '32: epilogue reads one chunk and stores nothing, 64: no MMA, 512: no weight '
+                         'copies, 1024: no window copies, 256: every pass reads the window')
     ap.add_argument('--dtype', default='bf16', choices=['bf16', 'fp32'])
     ap.add_argument('--fp32-math', default='tf32x3', choices=['tf32x3', 'ffma'],
                     help='contraction arithmetic for --dtype fp32')
     args = ap.parse_args()
     if args.counters:
         os.environ['DCN_B200_COUNTERS'] = '1'
+    if args.ablate:
+        args.no_shard_check = args.no_per_config = args.no_cpu_baseline = True
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
     if args.workload == 'c4':
         if args.impl == 'reference':
@@ -616,6 +624,8 @@ def main():
     from mmcv_b200 import _ext, _lib
     from mmcv_b200.ops import deform_conv2d, modulated_deform_conv2d
     lib = _lib.load()
+    if args.ablate:
+        _lib.check(lib.dcn_debug_configure(0, args.ablate))
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: there is no CPU path')
     torch.cuda.set_device(local)
@@ -861,6 +871,8 @@ def main():
             line['cpu_baseline'] = cpu_reference_sample(wl)
         if shard_check is not None:
             line['shard_check'] = shard_check
+        if args.ablate:
+            line['ablate'] = args.ablate   # a timing experiment: the outputs of this run are wrong
         if world == 1 and args.workload == 'c5' and not args.batch and not args.no_per_config:
             # every other configuration of the metric, at full size, on this GPU
             del x, off, msk, out, hx, hoff, hmsk, hout

@@ -81,6 +81,27 @@ struct alignas(64) Tc2Args {
   int debug_flags;
 };
 
+// Offsets and mask elements are read once: they bypass L1, which is left to the prefetched
+// corner runs of the samples outside the window.
+__device__ __forceinline__ uint32_t ldg_raw_stream(const float *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.b32 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_raw_stream(const __nv_bfloat16 *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint32_t ldg_raw_stream(const __half *p) {
+  uint32_t v;
+  asm volatile("ld.global.nc.L1::no_allocate.u16 %0, [%1];" : "=r"(v) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void prefetch_l1(const void *p) {
+  asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
+}
+
 // 16-byte loads.  `tok` is passed through untouched; code that must come after a load's issue
 // takes `tok` as an input.
 __device__ __forceinline__ uint4 ld16_global(const void *p, uint32_t &tok) {
@@ -644,6 +665,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     // consumed by entry_build one own stage later
     uint32_t roh = 0, row_ = 0, rmm = 0;   // raw offset (y, x) and mask elements
     float bh = -1.0e9f, bw_ = 0.f;          // sampling position without the offset
+    uint32_t e_cb = 0;                      // byte offset of the unit's first channel inside a pixel
     auto entry_loads = [&](const Pos &p) {
       roh = 0; row_ = 0; rmm = 0; bh = -1.0e9f; bw_ = 0.f;
       if (p.item >= items) return;
@@ -654,21 +676,24 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       bh = t_hb + lut_tap[2 * tap];
       bw_ = t_wb + lut_tap[2 * tap + 1];
       const int dgi = (int)lut_dg[t_grp * KH + hc];
+      e_cb = (uint32_t)(t_grp * g.Cg + hc * 32) * 2u;
       if (off) {
         const TIO *pp = t_off + (long long)((dgi * 2 * T + 2 * tap)) * g.off_cs;
-        roh = ldg_raw_ordered(pp);
-        row_ = ldg_raw_ordered(pp + g.off_cs);
+        roh = ldg_raw_stream(pp);
+        row_ = ldg_raw_stream(pp + g.off_cs);
       }
-      if (msk) rmm = ldg_raw_ordered(t_msk + (long long)(dgi * T + tap) * g.msk_cs);
+      if (msk) rmm = ldg_raw_stream(t_msk + (long long)(dgi * T + tap) * g.msk_cs);
     };
     // the entry: weights (w00 w01 | w10 w11), offset of the top-left corner within the padded
     // sample, and within the shared-memory window (kNoWin: the neighbourhood is not inside it)
-    constexpr uint32_t kNoWin = 0xffffffffu;
+    // (kDeadWin: the sample contributes nothing -- its position fails the sampling gate, or the
+    // unit does not exist; the gather then stores zeros without reading anything)
+    constexpr uint32_t kNoWin = 0xffffffffu, kDeadWin = 0xfffffffeu;
     const uint32_t dead_g = (uint32_t)(g.H + 1) * Rb;   // an all-zero neighbourhood
-    uint32_t ew0 = 0, ew1 = 0, eog = dead_g, eow = kNoWin;
+    uint32_t ew0 = 0, ew1 = 0, eog = dead_g, eow = kDeadWin;
     auto entry_build = [&]() {
-      // (runs before the loads of the stage after it: t_wy0 / t_wx0 still belong to this entry's tile)
-      ew0 = 0; ew1 = 0; eog = dead_g; eow = kNoWin;
+      // (runs before the loads of the stage after it: t_wy0 / t_wx0 / t_sbase still belong to this entry's tile)
+      ew0 = 0; ew1 = 0; eog = dead_g; eow = kDeadWin;
       const float h_im = bh + RawOf<TIO>::to_float(roh);
       const float w_im = bw_ + RawOf<TIO>::to_float(row_);
       if (h_im > -1.f && w_im > -1.f && h_im < (float)g.H && w_im < (float)g.W) {
@@ -680,10 +705,18 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         ew1 = pack_weights2<MODE>(lh * hw * m, lh * lw * m);
         const int hl = (int)hf, wl = (int)wf;
         eog = ((uint32_t)(hl + 1) * Wp + (uint32_t)(wl + 1)) * Cb;
+        eow = kNoWin;
         if (kWin) {
           const uint32_t wy = (uint32_t)(hl - t_wy0), wx = (uint32_t)(wl - t_wx0);
-          if (wy < (uint32_t)(tp.win_h - 1) && wx < (uint32_t)(tp.win_w - 1))
+          if (wy < (uint32_t)(tp.win_h - 1) && wx < (uint32_t)(tp.win_w - 1)) {
             eow = (wy * (uint32_t)tp.win_w + wx) * 64u;
+          } else {
+            // outside the window (rare): the two lanes that gather this (row, unit) will read the
+            // padded copy a stage from now; ask for its four 64-byte corner runs now
+            const char *b = t_sbase + e_cb + eog;
+            prefetch_l1(b); prefetch_l1(b + 32); prefetch_l1(b + Cb); prefetch_l1(b + Cb + 32);
+            prefetch_l1(b + Rb); prefetch_l1(b + Rb + 32); prefetch_l1(b + Rb + Cb); prefetch_l1(b + Rb + Cb + 32);
+          }
         }
       }
     };
@@ -742,25 +775,26 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         const int src = (lane & ~1) | p;
         uint32_t w0 = __shfl_sync(0xffffffffu, ew0, src), w1 = __shfl_sync(0xffffffffu, ew1, src);
         const uint32_t dst = stage_row + (uint32_t)(p * 64 * 128);
-        bool from_window = false;
-        uint32_t ow = 0;
         if constexpr (kWin) {
-          ow = __shfl_sync(0xffffffffu, eow, src);
-          // dead vectors (no such unit) read the window's first pixels with zero weights
-          from_window = __all_sync(0xffffffffu, ow != kNoWin || (v1_dead && v2_dead));
-          if (abl & 256) from_window = true;
-        }
-        if (kWin && from_window) {
-          // The usual case: every lane of the warp reads the window.  The lanes of unit 0 start
-          // with the even 64-byte slot of their left/right pair and those of unit 1 with the
-          // odd one (the window's row pitch is an even number of slots, so the bottom corners
-          // repeat the parity): with the rows' vector order, the eight lanes of a quarter warp
-          // cover all 32 banks.
-          if (ow == kNoWin) ow = 0;
-          const bool sw = ((ow >> 6) & 1u) != (uint32_t)usel;
+          // Every lane reads its four corner vectors from the window; a lane whose neighbourhood
+          // lies outside it (rare; the builder asked for those lines a stage ago) reads the padded
+          // copy instead, and a dead sample reads the window's first pixel and stores zeros.
+          // The lanes of unit 0 start with the even 64-byte slot of their left/right pair and
+          // those of unit 1 with the odd one (the window's row pitch is an even number of slots,
+          // so the bottom corners repeat the parity): with the rows' vector order, the eight
+          // lanes of a quarter warp cover all 32 banks.
+          uint32_t ow = __shfl_sync(0xffffffffu, eow, src);
+          bool miss = ow == kNoWin;
+          if (abl & 256) miss = false;
+          const bool dead = ow == kDeadWin;
+          uint32_t og = 0;
+          if (__any_sync(0xffffffffu, miss)) og = __shfl_sync(0xffffffffu, eog, src);
+          if (ow >= kDeadWin) ow = 0;
+          const bool sw = !miss && ((ow >> 6) & 1u) != (uint32_t)usel;
           if (sw) { w0 = __byte_perm(w0, 0u, 0x1032); w1 = __byte_perm(w1, 0u, 0x1032); }
           const uint32_t sp = wbase + ow;
           const uint32_t s1 = sw ? sp + 64u : sp, s2 = sw ? sp : sp + 64u;
+          const char *gb = gbase + og;
           const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
 #pragma unroll
           for (int k = 0; k < 2; ++k) {
@@ -769,9 +803,13 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
             uint4 X[4];
             if (abl & 2) {
               X[0] = X[1] = X[2] = X[3] = make_uint4(w0, w1, ow, q16);
+            } else if (miss) {
+              const char *b = gb + q16;
+              X[0] = ld16_global(b, tok); X[1] = ld16_global(b + Cb, tok);
+              X[2] = ld16_global(b + Rb, tok); X[3] = ld16_global(b + Rb + Cb, tok);
             } else {
-            X[0] = lds16(s1 + q16, tok); X[1] = lds16(s2 + q16, tok);
-            X[2] = lds16(s1 + win_rb + q16, tok); X[3] = lds16(s2 + win_rb + q16, tok);
+              X[0] = lds16(s1 + q16, tok); X[1] = lds16(s2 + q16, tok);
+              X[2] = lds16(s1 + win_rb + q16, tok); X[3] = lds16(s2 + win_rb + q16, tok);
             }
             uint4 wa = wa0;
             wa.x |= tok;  // tok is 0: keeps the blend behind the loads
@@ -779,12 +817,12 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
             if (abl & 8) r = X[0];
             else if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
             else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
-            if (k ? v2_dead : v1_dead) r = make_uint4(0u, 0u, 0u, 0u);
+            if ((k ? v2_dead : v1_dead) || dead) r = make_uint4(0u, 0u, 0u, 0u);
             if (!(abl & 128)) sts16(dst + (k ? a_c2 : a_c1), r);
           }
         } else {
-          // some neighbourhood of the warp's pass lies outside the window (or there is no
-          // window): the whole pass reads the padded copy in global memory
+          // no window: every lane reads the padded copy in global memory (a dead sample reads the
+          // all-zero neighbourhood with zero weights)
           const uint32_t og = __shfl_sync(0xffffffffu, eog, src);
           const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
 #pragma unroll
