@@ -141,6 +141,59 @@ class ClockSampler:
         return out
 
 
+def measure_msda(dev, dtype_name, peaks, reps=10):
+    """Multi-scale deformable attention (the sibling sampler) at the size of a Deformable-DETR
+    encoder layer on an 800x1066 image: levels 100x134, 50x67, 25x34, 13x17, every key a query,
+    8 heads x 32 channels, 4 points, batch 2.  Device time of the forward kernel (median), the
+    bytes it must move (value, locations, weights, output, once each) against the HBM peak, the
+    corner bytes it gathers (4 per sample) per second, and a checker comparison on a slice."""
+    from mmcv_b200 import _ext
+    from oracle.msda import msda_forward
+    dtype = torch.bfloat16 if dtype_name == 'bf16' else torch.float32
+    esize = 2 if dtype_name == 'bf16' else 4
+    B, M, D, P = 2, 8, 32, 4
+    shapes = torch.tensor([[100, 134], [50, 67], [25, 34], [13, 17]])
+    L = shapes.size(0)
+    S = int(shapes.prod(1).sum())
+    Q = S
+    gen = torch.Generator().manual_seed(0)
+    value = torch.randn(B, S, M, D, generator=gen).to(dtype)
+    ref_pts = torch.rand(B, Q, 1, 1, 1, 2, generator=gen)
+    loc = (ref_pts + torch.randn(B, Q, M, L, P, 2, generator=gen) * 0.03).to(dtype)
+    attn = torch.rand(B, Q, M, L * P, generator=gen).softmax(-1).view(B, Q, M, L, P).to(dtype)
+    starts = torch.cat((shapes.new_zeros((1,)), shapes.prod(1).cumsum(0)[:-1]))
+    d = [t.to(dev) for t in (value, shapes, starts, loc, attn)]
+    ts = []
+    for i in range(3 + reps):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        out = _ext.ms_deform_attn_forward(*d, im2col_step=64)
+        e1.record()
+        torch.cuda.synchronize(dev)
+        if i >= 3:
+            ts.append(e0.elapsed_time(e1))
+    ts.sort()
+    ms = ts[len(ts) // 2]
+    nq = 128   # checker slice: the first queries of the last batch entry
+    ref = msda_forward(value[-1:].double(), shapes, loc[-1:, :nq].double(), attn[-1:, :nq].double())
+    got = out[-1:, :nq].double().cpu()
+    err = ((got - ref).norm() / ref.norm()).item()
+    ok = err <= (1e-2 if dtype_name == 'bf16' else 1e-5)
+    compulsory = esize * (value.numel() + loc.numel() + attn.numel() + out.numel())
+    gathered = esize * B * Q * M * L * P * 4 * D
+    hbm = peaks.get('hbm_gbs', 6650.0)
+    return dict(workload=f'multi-scale deformable attention B={B} keys=queries={S} heads={M}x{D} levels={L} '
+                         f'points={P}', dtype=dtype_name, kernel='msda_forward_kernel', ms_per_step=ms,
+                compulsory_bytes=compulsory, gathered_bytes=gathered,
+                roofline=dict(bound='hbm', achieved=compulsory / (ms * 1e-3) / 1e9, peak=hbm, unit='GB/s',
+                              frac=compulsory / (ms * 1e-3) / 1e9 / hbm,
+                              gathered_gbs=gathered / (ms * 1e-3) / 1e9,
+                              note='the gather re-reads value 4*L*P/1 times per query from L2; the '
+                                   'compulsory bytes alone would take '
+                                   f'{compulsory / hbm / 1e6:.4f} ms'),
+                parity_ok=bool(ok), parity_err=err, parity_samples=f'{nq} queries of the last batch entry')
+
+
 def measure_tf32_peak(dev):
     """Dense TF32 matmul rate of this GPU (library GEMM, best of 5): the denominator of the
     3xTF32 roofline, measured the way the bf16 peak of MEASURED_PEAKS.json was."""
@@ -883,6 +936,8 @@ def main():
                                       'c2_bf16': ('c2', 'bf16', ''), 'c2_fp32_tf32x3': ('c2', 'fp32', 'tf32x3'),
                                       'c3_bf16': ('c3', 'bf16', ''), 'c3_fp32_tf32x3': ('c3', 'fp32', 'tf32x3')}.items():
                 per_config[key] = measure_config(_lib, lib, nm, dt, fm, dev, peaks, tf32)
+            for dt in ('bf16', 'fp32'):
+                per_config['msda_' + dt] = measure_msda(dev, dt, peaks)
             c4args = argparse.Namespace(**vars(args))
             c4args.batch, c4args.steps, c4args.e2e_steps = 0, 5, 1
             c4 = run_c4(c4args, 0, 1, local, dist_ready=True, emit=False)

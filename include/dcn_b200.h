@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define DCN_ABI_VERSION 5
+#define DCN_ABI_VERSION 6
 
 enum { DCN_DTYPE_F32 = 0, DCN_DTYPE_BF16 = 1, DCN_DTYPE_F16 = 2 };
 
@@ -317,6 +317,41 @@ int dcn_forward_workspace_bytes(int32_t elem, int32_t modulated, int64_t batch,
                                 int32_t pad_h, int32_t pad_w, int32_t dilation_h,
                                 int32_t dilation_w, int32_t group,
                                 int32_t deformable_group, size_t *bytes);
+
+/*
+ * Multi-scale deformable attention, the sibling sampler of the deformable convolutions
+ * (same bilinear gather, gate and per-corner validity; a weighted sum over levels and points
+ * instead of a contraction with weights).
+ *
+ * dcn_msda_forward is what a binding of
+ *   ms_deform_attn_forward(value, spatial_shapes, level_start_index, sampling_loc, attn_weight,
+ *                          im2col_step)
+ * (mmcv/ops/csrc/pytorch/pybind.cpp:172-176, :812-816; CUDA body
+ * mmcv/ops/csrc/pytorch/cuda/ms_deform_attn_cuda.cu:203-277) calls after allocating `output`
+ * [batch][num_query][num_heads * channels]; the reference's loop over im2col_step chunks has no
+ * counterpart (one launch covers the batch; the binding keeps the divisibility check).
+ * value is [batch][spatial_size][num_heads][channels], sampling_loc
+ * [batch][num_query][num_heads][num_levels][num_point][2] as (x, y) in [0, 1], attn_weight the
+ * same without the last axis; all three and output have element type `dtype`;
+ * spatial_shapes ([num_levels][2] as (h, w)) and level_start_index ([num_levels]) are int64
+ * arrays in DEVICE memory, as in the reference.  Asynchronous on `stream`, no allocation.
+ *
+ * dcn_msda_backward replaces ms_deform_attn_backward (pybind.cpp:177-184, :817-824; CUDA body
+ * ms_deform_attn_cuda.cu:279-351): it ADDS to grad_value ([batch][spatial_size][num_heads][channels])
+ * and writes grad_sampling_loc and grad_attn_weight (shapes of sampling_loc and attn_weight); the
+ * three gradient buffers are fp32 whatever `dtype` is and must be zero on entry.
+ */
+int dcn_msda_forward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                     const void *sampling_loc, const void *attn_weight, void *output, int32_t dtype,
+                     int64_t batch, int64_t spatial_size, int64_t num_heads, int64_t channels,
+                     int64_t num_levels, int64_t num_query, int64_t num_point, int32_t device,
+                     void *stream);
+int dcn_msda_backward(const void *value, const int64_t *spatial_shapes, const int64_t *level_start_index,
+                      const void *sampling_loc, const void *attn_weight, const void *grad_output,
+                      float *grad_value, float *grad_sampling_loc, float *grad_attn_weight, int32_t dtype,
+                      int64_t batch, int64_t spatial_size, int64_t num_heads, int64_t channels,
+                      int64_t num_levels, int64_t num_query, int64_t num_point, int32_t device,
+                      void *stream);
 
 #ifdef __cplusplus
 }

@@ -20,15 +20,17 @@ def frozen_weights():
 def install():
     """Make an installed ``mmcv`` use this library for the deformable-conv forward.
 
-    Replaces the module-global ``ext_module`` that ``mmcv.ops.modulated_deform_conv`` and
-    ``mmcv.ops.deform_conv`` look their compiled entry points up on
-    (mmcv/ops/modulated_deform_conv.py:17-19, mmcv/ops/deform_conv.py:19-22).  Returns
+    Replaces the module-global ``ext_module`` that ``mmcv.ops.modulated_deform_conv``,
+    ``mmcv.ops.deform_conv`` and ``mmcv.ops.multi_scale_deform_attn`` look their compiled entry
+    points up on (mmcv/ops/modulated_deform_conv.py:17-19, mmcv/ops/deform_conv.py:19-22,
+    mmcv/ops/multi_scale_deform_attn.py:19-20).  Returns
     the list of patched modules; raises ImportError if ``mmcv`` is not importable.
     """
     import importlib
     from . import _ext
     patched = []
-    for name in ('mmcv.ops.modulated_deform_conv', 'mmcv.ops.deform_conv'):
+    for name in ('mmcv.ops.modulated_deform_conv', 'mmcv.ops.deform_conv',
+                 'mmcv.ops.multi_scale_deform_attn'):
         mod = importlib.import_module(name)
         mod.ext_module = _ext
         patched.append(name)

@@ -582,3 +582,99 @@ def deform_conv_backward_parameters(input, offset, gradOutput, gradWeight, colum
                             want_input=False)
     gradWeight.add_((gw * scale).to(gradWeight.dtype))
 
+
+
+# ---------------------------------------------------------------------------------------------
+# Multi-scale deformable attention (the sibling sampler; reference entry points
+# mmcv/ops/csrc/pytorch/ms_deform_attn.cpp:38-60, CUDA bodies
+# mmcv/ops/csrc/pytorch/cuda/ms_deform_attn_cuda.cu:203-351)
+
+def _msda_check(value, value_spatial_shapes, value_level_start_index, sampling_locations,
+                attention_weights, im2col_step, extra=()):
+    names = ['value', 'spatial_shapes', 'level_start_index', 'sampling_loc', 'attn_weight']
+    tensors = [value, value_spatial_shapes, value_level_start_index, sampling_locations,
+               attention_weights]
+    for name, t in list(zip(names, tensors)) + list(extra):
+        if not t.is_contiguous():
+            raise RuntimeError(f'{name} tensor has to be contiguous')
+        if not t.is_cuda:
+            raise RuntimeError(f'{name} must be a CUDA tensor')
+    if value.dim() != 4 or sampling_locations.dim() != 6 or attention_weights.dim() != 5:
+        raise RuntimeError('ms_deform_attn: value must be 4-D, sampling_loc 6-D, attn_weight 5-D')
+    if value_spatial_shapes.dtype != torch.int64 or value_level_start_index.dtype != torch.int64:
+        raise RuntimeError('ms_deform_attn: spatial_shapes and level_start_index must be int64')
+    for name, t in (('sampling_loc', sampling_locations), ('attn_weight', attention_weights)):
+        if t.dtype != value.dtype:
+            raise RuntimeError(f'ms_deform_attn: {name} has dtype {t.dtype}, value has {value.dtype}')
+    batch = value.size(0)
+    step = min(batch, int(im2col_step))
+    if batch > 0 and (step <= 0 or batch % step != 0):
+        raise RuntimeError(f'batch({batch}) must divide im2col_step({step})')
+    B, S, M, D = value.shape
+    L = value_spatial_shapes.size(0)
+    Q, P = sampling_locations.size(1), sampling_locations.size(4)
+    if tuple(sampling_locations.shape) != (B, Q, M, L, P, 2) or \
+            tuple(attention_weights.shape) != (B, Q, M, L, P) or \
+            tuple(value_spatial_shapes.shape) != (L, 2) or value_level_start_index.numel() != L:
+        raise RuntimeError('ms_deform_attn: argument shapes do not match each other')
+    return B, S, M, D, L, Q, P
+
+
+def ms_deform_attn_forward(value, value_spatial_shapes, value_level_start_index,
+                           sampling_locations, attention_weights, im2col_step):
+    """Same contract as the reference entry of this name: returns the attention output
+    [batch, num_query, num_heads * channels] in value's dtype; ``im2col_step`` is validated
+    (the batch must be a multiple of min(batch, im2col_step)) and otherwise unused."""
+    lib = _lib.load()
+    B, S, M, D, L, Q, P = _msda_check(value, value_spatial_shapes, value_level_start_index,
+                                      sampling_locations, attention_weights, im2col_step)
+    code = _dtype_code(value)
+    dev = value.device
+    with torch.cuda.device(dev):
+        out = value.new_empty((B, Q, M * D))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dcn_msda_forward(_ptr(value), _ptr(value_spatial_shapes),
+                                        _ptr(value_level_start_index), _ptr(sampling_locations),
+                                        _ptr(attention_weights), _ptr(out), code, B, S, M, D, L, Q, P,
+                                        dev.index if dev.index is not None else torch.cuda.current_device(),
+                                        stream))
+    return out
+
+
+def ms_deform_attn_backward(value, value_spatial_shapes, value_level_start_index,
+                            sampling_locations, attention_weights, grad_output, grad_value,
+                            grad_sampling_loc, grad_attn_weight, im2col_step):
+    """Same contract as the reference entry of this name: adds to ``grad_value`` and writes
+    ``grad_sampling_loc`` / ``grad_attn_weight`` in place (the caller passes them zeroed)."""
+    lib = _lib.load()
+    B, S, M, D, L, Q, P = _msda_check(value, value_spatial_shapes, value_level_start_index,
+                                      sampling_locations, attention_weights, im2col_step,
+                                      extra=[('grad_output', grad_output)])
+    code = _dtype_code(value)
+    dev = value.device
+    if grad_output.dtype != value.dtype:
+        raise RuntimeError('ms_deform_attn: grad_output must have value\'s dtype')
+    with torch.cuda.device(dev):
+        f32 = value.dtype == torch.float32
+        direct = f32 and all(t.is_contiguous() and t.dtype == torch.float32
+                             for t in (grad_value, grad_sampling_loc, grad_attn_weight))
+        if direct:
+            gv, gl, ga = grad_value, grad_sampling_loc, grad_attn_weight
+            gl.zero_()
+            ga.zero_()
+        else:
+            # the kernels produce fp32 gradients; 16-bit tensors get them rounded once
+            gv = torch.zeros(value.shape, dtype=torch.float32, device=dev)
+            gl = torch.zeros(sampling_locations.shape, dtype=torch.float32, device=dev)
+            ga = torch.zeros(attention_weights.shape, dtype=torch.float32, device=dev)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(lib.dcn_msda_backward(_ptr(value), _ptr(value_spatial_shapes),
+                                         _ptr(value_level_start_index), _ptr(sampling_locations),
+                                         _ptr(attention_weights), _ptr(grad_output), _ptr(gv), _ptr(gl),
+                                         _ptr(ga), code, B, S, M, D, L, Q, P,
+                                         dev.index if dev.index is not None else torch.cuda.current_device(),
+                                         stream))
+        if not direct:
+            grad_value.add_(gv.to(grad_value.dtype))
+            grad_sampling_loc.copy_(gl)
+            grad_attn_weight.copy_(ga)

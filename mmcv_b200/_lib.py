@@ -14,7 +14,7 @@ MATH_AUTO, MATH_FFMA, MATH_TF32X3, MATH_BF16 = 0, 1, 2, 3
 PATH_TCGEN05, PATH_SIMT_TILED, PATH_SIMT_DIRECT = 1, 2, 3
 ACT_NONE, ACT_SIGMOID = 0, 1
 STATIC_SCRATCH_BYTES = 32 << 20
-ABI_VERSION = 5   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
+ABI_VERSION = 6   # DCN_ABI_VERSION of include/dcn_b200.h (DcnFwdParams layout)
 
 # Every symbol include/dcn_b200.h declares.
 EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
@@ -23,7 +23,7 @@ EXPORTS = ['dcn_abi_version', 'dcn_last_error', 'dcn_fwd_plan',
            'dcn_pad_channels_last', 'dcn_conv_workspace_bytes', 'dcn_conv_fwd', 'dcn_to_channels_last', 'dcn_bwd_columns', 'dcn_bwd_input',
            'dcn_bwd_coord',
            'dcn_modulated_deform_conv_forward', 'dcn_deform_conv_forward',
-           'dcn_forward_workspace_bytes']
+           'dcn_forward_workspace_bytes', 'dcn_msda_forward', 'dcn_msda_backward']
 
 
 class DcnFwdParams(ctypes.Structure):
@@ -112,6 +112,8 @@ def load():
         [vp] * 4 + [i32] + [i64] * 5 + [i32] * 12 + [vp, sz, vp])
     lib.dcn_forward_workspace_bytes.argtypes = (
         [i32, i32] + [i64] * 5 + [i32] * 10 + [P(sz)])
+    lib.dcn_msda_forward.argtypes = [vp] * 6 + [i32] + [i64] * 7 + [i32, vp]
+    lib.dcn_msda_backward.argtypes = [vp] * 9 + [i32] + [i64] * 7 + [i32, vp]
     for name in EXPORTS:
         getattr(lib, name)  # raises AttributeError if a declared symbol is missing
         if name not in ('dcn_last_error',):

@@ -13,7 +13,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, 'csrc')
 LIB_DIR = os.path.join(PKG, 'lib')
 LIB = os.path.join(LIB_DIR, 'libdcn_b200.so')
-SOURCES = ['dcn_api.cu', 'dcn_simt.cu', 'dcn_tc.cu', 'dcn_tc2.cu', 'dcn_conv.cu', 'dcn_static.cu', 'dcn_bwd.cu']
+SOURCES = ['dcn_api.cu', 'dcn_simt.cu', 'dcn_tc.cu', 'dcn_tc2.cu', 'dcn_conv.cu', 'dcn_static.cu', 'dcn_bwd.cu', 'dcn_msda.cu']
 NVCC = os.environ.get('NVCC', '/usr/local/cuda/bin/nvcc')
 EXTRA_FLAGS = os.environ.get('DCN_B200_NVCC_FLAGS', '').split()   # e.g. -DDCN_TC2_ABLATE for experiments
 

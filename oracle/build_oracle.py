@@ -30,7 +30,8 @@ REF_SO = os.path.join(REF_DIR, REF_NAME + '.so')
 DEFAULT_REF_ROOT = os.environ.get('DCN_REFERENCE_ROOT', '')
 WRAP_DIR = os.path.join(REF_DIR, 'pywrap')
 # the reference's Python wrappers of this path (+ the loader they import), relative to its root
-REF_WRAPPERS = ['mmcv/utils/ext_loader.py', 'mmcv/ops/modulated_deform_conv.py', 'mmcv/ops/deform_conv.py']
+REF_WRAPPERS = ['mmcv/utils/ext_loader.py', 'mmcv/ops/modulated_deform_conv.py', 'mmcv/ops/deform_conv.py',
+                'mmcv/ops/multi_scale_deform_attn.py']
 
 # The reference's translation units for this path, relative to its root.
 REF_UNITS = [

@@ -9,6 +9,10 @@ extension built by ``python oracle/build_oracle.py``.  Writes
   tests/test_ops/test_deform_conv.py:27-35), together with what the reference
   wrappers + CPU extension produce on them (forward output, the offset/mask the
   offset branch produced, and the gradients of the reference test).
+* ``msda_cases.npz`` -- seeded cases of multi-scale deformable attention: inputs, outputs and
+  gradients from the reference's own pure-PyTorch implementation
+  (mmcv/ops/multi_scale_deform_attn.py:113-170), among them the case of the reference's tests
+  (tests/test_ops/test_ms_deformable_attn.py:101-118).
 * ``dcn_cases.npz`` -- seeded small cases (inputs, parameters, forward output and
   gradients) covering kernel/stride/padding/dilation/group/deform-group
   variety, out-of-range, grid-aligned and non-finite offsets, non-finite input samples.
@@ -195,9 +199,53 @@ def reference_kat(v2, v1):
     return kat
 
 
+MSDA_CASES = [
+    # name, B, M, D, Q, shapes, P, location range, seed
+    ('ref_test', 1, 2, 2, 2, [(6, 4), (3, 2)], 2, (0.0, 1.0), 3),      # the reference tests' own case
+    ('detr_like', 1, 8, 32, 64, [(12, 16), (6, 8), (3, 4), (2, 2)], 4, (-0.15, 1.15), 11),
+    ('odd_channels', 2, 3, 5, 17, [(7, 5), (4, 3), (1, 1)], 3, (-0.3, 1.3), 12),
+    ('wide_head', 1, 2, 64, 33, [(9, 11), (5, 6)], 2, (-0.1, 1.1), 13),
+    ('edges', 1, 4, 8, 64, [(4, 4), (2, 2)], 4, (-0.5, 1.5), 14),
+]
+
+
+def msda_cases(msda):
+    """Inputs, outputs and gradients of multi-scale deformable attention from the reference's
+    own pure-PyTorch implementation (multi_scale_deformable_attn_pytorch), computed in double
+    and stored as fp32 (inputs are fp32 values, so the double result is the exact target)."""
+    blob = {}
+    for name, B, M, D, Q, shapes, P, (lo, hi), seed in MSDA_CASES:
+        torch.manual_seed(seed)
+        shp = torch.as_tensor(shapes, dtype=torch.long)
+        S = int(shp.prod(1).sum())
+        L = len(shapes)
+        value = torch.rand(B, S, M, D) * (0.01 if name == 'ref_test' else 1.0)
+        loc = torch.rand(B, Q, M, L, P, 2) * (hi - lo) + lo
+        if name == 'edges':   # exact cell centres and borders among the locations
+            sel = torch.rand(loc.shape) < 0.3
+            loc = torch.where(sel, (loc * 8).round() / 8, loc)
+        attn = torch.rand(B, Q, M, L, P) + 1e-5
+        attn /= attn.sum(-1, keepdim=True).sum(-2, keepdim=True)
+        gout = torch.randn(B, Q, M * D)
+        v64 = value.double().requires_grad_(True)
+        l64 = loc.double().requires_grad_(True)
+        a64 = attn.double().requires_grad_(True)
+        out = msda.multi_scale_deformable_attn_pytorch(v64, shp, l64, a64)
+        out.backward(gout.double())
+        for k, t in dict(value=value, shapes=shp, loc=loc, attn=attn, grad_out=gout, out=out.detach().float(),
+                         grad_value=v64.grad.float(), grad_loc=l64.grad.float(),
+                         grad_attn=a64.grad.float()).items():
+            blob[f'{name}/{k}'] = t.numpy()
+    return blob
+
+
 def main():
     ext = oracle.load_ref()
     v2, v1, _ = ref_wrappers.load(ext, REF_ROOT)
+    import types
+    msda = ref_wrappers.load_msda(types.SimpleNamespace(ms_deform_attn_forward=None,
+                                                        ms_deform_attn_backward=None), REF_ROOT)
+    np.savez_compressed(os.path.join(HERE, 'msda_cases.npz'), **msda_cases(msda))
     np.savez_compressed(os.path.join(HERE, 'reference_kat.npz'), **reference_kat(v2, v1))
     blob, meta = {}, {}
     for i, spec in enumerate(CASES):

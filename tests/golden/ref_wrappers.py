@@ -18,9 +18,9 @@ import types
 import torch
 
 _NAMES = ['mmengine', 'mmengine.logging', 'mmengine.registry', 'mmengine.utils',
-          'mmengine.utils.dl_utils', 'mmcv', 'mmcv.utils', 'mmcv.utils.ext_loader',
+          'mmengine.utils.dl_utils', 'mmengine.model', 'mmcv', 'mmcv.utils', 'mmcv.utils.ext_loader',
           'mmcv._ext', 'mmcv.ops', 'mmcv.ops.modulated_deform_conv',
-          'mmcv.ops.deform_conv']
+          'mmcv.ops.deform_conv', 'mmcv.ops.multi_scale_deform_attn']
 
 
 class _Registry:
@@ -72,6 +72,30 @@ def _exec(name, path, package):
     return mod
 
 
+class _BaseModule(torch.nn.Module):
+    def __init__(self, init_cfg=None):
+        super().__init__()
+        self.init_cfg = init_cfg
+        self._is_init = False
+
+
+def _constant_init(module, val, bias=0):
+    if getattr(module, 'weight', None) is not None:
+        torch.nn.init.constant_(module.weight, val)
+    if getattr(module, 'bias', None) is not None:
+        torch.nn.init.constant_(module.bias, bias)
+
+
+def _xavier_init(module, gain=1, bias=0, distribution='normal'):
+    if getattr(module, 'weight', None) is not None:
+        if distribution == 'uniform':
+            torch.nn.init.xavier_uniform_(module.weight, gain=gain)
+        else:
+            torch.nn.init.xavier_normal_(module.weight, gain=gain)
+    if getattr(module, 'bias', None) is not None:
+        torch.nn.init.constant_(module.bias, bias)
+
+
 def default_root():
     """Where the reference's wrapper files are: the checkout named by DCN_REFERENCE_ROOT, else
     the copies the checker's build recipe left under oracle/_ref/pywrap; None if neither exists."""
@@ -91,7 +115,10 @@ def load(ext, ref_root=None):
     for n in _NAMES:
         sys.modules.pop(n, None)
     reg = _Registry()
-    sys.modules['mmengine'] = _module('mmengine', __path__=[])
+    sys.modules['mmengine'] = _module('mmengine', __path__=[], ConfigDict=dict)
+    sys.modules['mmengine.model'] = _module(
+        'mmengine.model', BaseModule=_BaseModule, constant_init=_constant_init,
+        xavier_init=_xavier_init)
     sys.modules['mmengine.logging'] = _module(
         'mmengine.logging', print_log=lambda *a, **k: None)
     sys.modules['mmengine.registry'] = _module('mmengine.registry', MODELS=reg)
@@ -117,6 +144,17 @@ def load(ext, ref_root=None):
     v1 = _exec('mmcv.ops.deform_conv',
                os.path.join(ref_root, 'mmcv/ops/deform_conv.py'), 'mmcv.ops')
     return v2, v1, reg
+
+
+def load_msda(ext, ref_root=None):
+    """The reference's unchanged mmcv/ops/multi_scale_deform_attn.py on top of `ext` (which must
+    have ms_deform_attn_forward / ms_deform_attn_backward); call after load()."""
+    ref_root = ref_root or default_root()
+    path = os.path.join(ref_root, 'mmcv/ops/multi_scale_deform_attn.py')
+    if not os.path.isfile(path):
+        raise FileNotFoundError('the reference wrapper file of multi-scale deformable attention is not available')
+    sys.modules['mmcv._ext'] = ext
+    return _exec('mmcv.ops.multi_scale_deform_attn', path, 'mmcv.ops')
 
 
 def unload():
