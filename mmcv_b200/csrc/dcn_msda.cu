@@ -110,7 +110,7 @@ __device__ __forceinline__ void store_vec(T *p, const float (&v)[V]) {
 // h_im > -1 && w_im > -1 && h_im < H && w_im < W; a corner outside the map contributes 0.
 struct Sample {
   float w[4];       // hh*hw, hh*lw, lh*hw, lh*lw
-  long long o[4];   // element offsets of the four corners
+  int o[4];         // element offsets of the four corners (one batch entry holds fewer than 2^31 elements)
   bool ok[4];
   float hh, hw, lh, lw;
   bool live;
@@ -127,9 +127,9 @@ __device__ __forceinline__ Sample make_sample(float loc_w, float loc_h, int H, i
   const bool top = h_low >= 0, left = w_low >= 0, bot = h_low + 1 <= H - 1, right = w_low + 1 <= W - 1;
   s.ok[0] = s.live && top && left; s.ok[1] = s.live && top && right;
   s.ok[2] = s.live && bot && left; s.ok[3] = s.live && bot && right;
-  const long long base = ((long long)h_low * W + w_low) * pix_stride;
+  const int base = (h_low * W + w_low) * pix_stride;
   s.o[0] = base; s.o[1] = base + pix_stride;
-  s.o[2] = base + (long long)W * pix_stride; s.o[3] = s.o[2] + pix_stride;
+  s.o[2] = base + W * pix_stride; s.o[3] = s.o[2] + pix_stride;
   return s;
 }
 
@@ -328,7 +328,7 @@ int check_geom(int32_t dtype, int64_t B, int64_t S, int64_t M, int64_t D, int64_
     return set_error(DCN_ERR_UNSUPPORTED, "multi-scale deformable attention takes fp32, bf16 and fp16 tensors");
   if (B < 0 || S < 0 || Q < 0 || M <= 0 || D <= 0 || L <= 0 || P <= 0)
     return set_error(DCN_ERR_ARG, "multi-scale deformable attention: sizes must be positive");
-  if (M * D > 2147483647LL / 4 || S * M * D >= (1LL << 40) || L > 1024 || P > 1024)
+  if (M * D > 2147483647LL / 4 || (S + 2) * M * D >= 2147483647LL || L > 1024 || P > 1024)
     return set_error(DCN_ERR_UNSUPPORTED, "multi-scale deformable attention: problem too large");
   g->B = B; g->S = S; g->Q = Q; g->M = (int)M; g->D = (int)D; g->L = (int)L; g->P = (int)P;
   return DCN_OK;
