@@ -216,8 +216,12 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
       const int c1 = c0 + 32 < (grp + 1) * g.Cg ? c0 + 32 : (grp + 1) * g.Cg;
       if (c0 / g.cpdg != (c1 - 1) / g.cpdg) return;
     }
-  // (the kernel keeps two small lookup tables: up to 64 taps and 1024 half-chunks over all groups)
-  if (g.T > 64 || g.groups * t.KH > 1024) return;
+  // (the kernel keeps a 3 KiB lookup table of its K units: 16 bytes x 2 S entries x conv groups,
+  // with 8-bit half-chunk numbers, 16-bit offset / mask channel numbers and 23-bit channel byte
+  // offsets)
+  if ((long long)g.groups * 2 * t.S * 16 > 3072 || t.KH > 255 || (long long)g.dg * g.T > 32767 ||
+      g.C >= (1 << 22))
+    return;
   t.ndu = 1;
   t.tab_span = t.tab_slots = t.tab_slot_blocks = 0;
   // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles

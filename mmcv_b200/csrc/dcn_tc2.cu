@@ -102,6 +102,18 @@ __device__ __forceinline__ void prefetch_l1(const void *p) {
   asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
+// In-kernel phase timers are compiled in only with -DDCN_TC2_COUNTERS (they cost the gather warps
+// four registers and a dozen instructions per stage).
+#ifdef DCN_TC2_COUNTERS
+using Timer2 = PhaseTimer;
+#else
+struct Timer2 {
+  __device__ __forceinline__ Timer2(unsigned long long *, bool) {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void count(int) {}
+};
+#endif
+
 // 16-byte loads.  `tok` is passed through untouched; code that must come after a load's issue
 // takes `tok` as an input.
 __device__ __forceinline__ uint4 ld16_global(const void *p, uint32_t &tok) {
@@ -110,6 +122,16 @@ __device__ __forceinline__ uint4 ld16_global(const void *p, uint32_t &tok) {
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p), "r"(tok));
   asm volatile("" : "+r"(tok));
+  return r;
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+  uint4 r;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "r"(addr));
+  return r;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t r;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(r) : "r"(addr));
   return r;
 }
 __device__ __forceinline__ uint4 lds16(uint32_t addr, uint32_t &tok) {
@@ -134,7 +156,7 @@ constexpr uint32_t kCtrlBytes = 4096;   // 1 KiB of fixed fields and barriers, t
 constexpr uint32_t kCtrlTmemSlot = 512, kCtrlAbort = 520, kCtrlLimit = 528, kCtrlStatus = 536;
 // lookup tables (built once per block): tap -> sampling displacement (dy, dx) as floats, and
 // (conv group, half-chunk) -> deform group
-constexpr uint32_t kLutTapBytes = 2 * 4 * 64;   // up to 64 taps (then 1024 half-chunk entries of 2 bytes)
+constexpr uint32_t kLutBytes = 3072;   // the K-unit table: 16 bytes x 2 S entries x conv groups
 
 struct Smem2 {
   uint8_t *a, *b, *win;
@@ -191,8 +213,23 @@ __device__ __forceinline__ bool mbar_wait_slow2(uint32_t bar, uint32_t parity, i
   }
 }
 // Bounded wait.  Returns false when the block is aborting.
+// Sleep between the polls of a wait, in ns, by role (0: poll back to back).  try_wait already
+// suspends the thread in hardware for a while; the sleep keeps the waiting roles from taking issue
+// slots from the gather warps.
 #ifndef DCN_TC2_BACKOFF
 #define DCN_TC2_BACKOFF 100
+#endif
+#ifndef TC2_BO_EPI
+#define TC2_BO_EPI 200
+#endif
+#ifndef TC2_BO_MMA
+#define TC2_BO_MMA 0
+#endif
+#ifndef TC2_BO_LOAD
+#define TC2_BO_LOAD DCN_TC2_BACKOFF
+#endif
+#ifndef TC2_BO_GATHER
+#define TC2_BO_GATHER DCN_TC2_BACKOFF
 #endif
 __device__ __forceinline__ bool mbar_wait2(uint32_t bar, uint32_t parity, int code, int backoff = DCN_TC2_BACKOFF) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -318,16 +355,25 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   {
-    float *lut_tap = reinterpret_cast<float *>(smem + 1024);
-    unsigned short *lut_dg = reinterpret_cast<unsigned short *>(smem + 1024 + kLutTapBytes);
-    for (int i = threadIdx.x; i < g.T; i += blockDim.x) {
-      const int ti = i / g.kw, tj = i - ti * g.kw;
-      lut_tap[2 * i] = (float)(ti * g.dil_h);
-      lut_tap[2 * i + 1] = (float)(tj * g.dil_w);
-    }
-    for (int i = threadIdx.x; i < g.groups * tp.KH; i += blockDim.x) {
-      const int grp = i / tp.KH, hc = i - grp * tp.KH;
-      lut_dg[i] = (unsigned short)((grp * g.Cg + hc * 32) / g.cpdg);
+    // One 16-byte entry per (conv group, K unit u = half-chunk * T + tap), 2 S entries per group:
+    // tap displacement (dy, dx) as floats; channel of the unit's y-offset plane | channel of its
+    // mask plane << 16; half-chunk | exists << 8 | byte offset of the unit's first channel
+    // inside a pixel << 9.
+    uint4 *lut = reinterpret_cast<uint4 *>(smem + 1024);
+    const int per_grp = 2 * tp.S;
+    for (int i = threadIdx.x; i < g.groups * per_grp; i += blockDim.x) {
+      const int grp = i / per_grp, u = i - grp * per_grp;
+      const bool exists = u < tp.U;
+      const int hc = exists ? u / g.T : 0, tap = exists ? u - hc * g.T : 0;
+      const int ti = tap / g.kw, tj = tap - ti * g.kw;
+      const int c0 = grp * g.Cg + hc * 32;
+      const int dgi = c0 / g.cpdg;
+      uint4 e;
+      e.x = __float_as_uint((float)(ti * g.dil_h));
+      e.y = __float_as_uint((float)(tj * g.dil_w));
+      e.z = (uint32_t)(dgi * 2 * g.T + 2 * tap) | ((uint32_t)(dgi * g.T + tap) << 16);
+      e.w = (uint32_t)hc | (exists ? 256u : 0u) | ((uint32_t)(c0 * 2) << 9);
+      lut[i] = e;
     }
   }
   if (warp == kMmaWarp2) {
@@ -363,7 +409,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     const int row = warp * 32 + lane;
     const int ty = row >> tp.tw_log2, tx = row & tw_mask;
     const bool act_any = g.act == DCN_ACT_SIGMOID && g.act_hi > g.act_lo;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
+    Timer2 pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     uint32_t li = 0;
     int staged_co0[2] = {-1, -1};
     uint32_t slab = 0;  // tensor-store staging buffer in use (two per warp)
@@ -377,7 +423,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const int co0 = t.grp * g.Cog + t.nt * tp.BN;
       const bool act_tile = act_any && co0 < g.act_hi && co0 + ncols > g.act_lo;
       pt.lap(13);
-      bool ok = mbar_wait2(tmem_full + 8 * buf, par, 3, 200);
+      bool ok = mbar_wait2(tmem_full + 8 * buf, par, 3, TC2_BO_EPI);
       ok = __all_sync(0xffffffffu, ok);  // the tcgen05 instructions below need the whole warp
       if (!ok) break;
       pt.lap(12);
@@ -486,21 +532,21 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
                            ((uint32_t)(kBM >> 4) << 24);
     uint32_t sa = 0, pa = 0, sb = 0, pb = 0, li = 0;
     bool ok = true;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && lane == 0);
+    Timer2 pt(a.counters, blockIdx.x == 0 && lane == 0);
     for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x, ++li) {
       const int buf = (int)(li & 1);
       const uint32_t par = (li >> 1) & 1u;
       pt.lap(11);
-      ok = __all_sync(0xffffffffu, mbar_wait2(tmem_empty + 8 * buf, par ^ 1u, 4, 0));
+      ok = __all_sync(0xffffffffu, mbar_wait2(tmem_empty + 8 * buf, par ^ 1u, 4, TC2_BO_MMA));
       if (!ok) break;
       pt.lap(10);
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)(buf * tp.BN);
       for (int ks = 0; ks < tp.S; ++ks) {
-        ok = __all_sync(0xffffffffu, mbar_wait2(full_b + 8 * sb, pb, 5, 0));
+        ok = __all_sync(0xffffffffu, mbar_wait2(full_b + 8 * sb, pb, 5, TC2_BO_MMA));
         if (!ok) break;
         pt.lap(8);
-        ok = __all_sync(0xffffffffu, mbar_wait2(full_a + 8 * sa, pa, 6, 0));
+        ok = __all_sync(0xffffffffu, mbar_wait2(full_a + 8 * sa, pa, 6, TC2_BO_MMA));
         if (!ok) break;
         pt.lap(9);
         tc_fence_after();
@@ -531,13 +577,13 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const uint32_t per_mt = (uint32_t)(g.groups * tp.NT);
       uint32_t sb = 0, pb = 0;
       bool ok = true;
-      PhaseTimer pt(a.counters, blockIdx.x == 0);
+      Timer2 pt(a.counters, blockIdx.x == 0);
       for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const uint32_t rem = item % per_mt;
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
         for (int ks = 0; ks < tp.S; ++ks) {
           pt.lap(15);
-          ok = mbar_wait2(empty_b + 8 * sb, pb ^ 1u, 7);
+          ok = mbar_wait2(empty_b + 8 * sb, pb ^ 1u, 7, TC2_BO_LOAD);
           if (!ok) break;
           pt.lap(14);
           const bool withhold = (a.debug_flags & 1) && item + gridDim.x >= items && ks == tp.S - 1;
@@ -569,7 +615,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         for (int hc = 0; hc < tp.KH; ++hc, ++wq) {
           const uint32_t wb = wq & 1u;
           // buffer wb was last used by window wq - 2
-          ok = mbar_wait2(win_empty + 8 * wb, ((wq >> 1) & 1u) ^ 1u, 11);
+          ok = mbar_wait2(win_empty + 8 * wb, ((wq >> 1) & 1u) ^ 1u, 11, TC2_BO_LOAD);
           if (!ok) break;
 #ifdef DCN_TC2_ABLATE
           if (a.debug_flags & 1024) { mbar_arrive(win_full + 8 * wb); continue; }
@@ -613,12 +659,13 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     const uint32_t win_s = smem_u32(L.win);
     const int KH = tp.KH;
 
-    const float *lut_tap = reinterpret_cast<const float *>(smem + 1024);
-    const unsigned short *lut_dg = reinterpret_cast<const unsigned short *>(smem + 1024 + kLutTapBytes);
-    // ---- position of a k-stage: tile, stage in the tile, its unit A = 2 s = (half-chunk, tap)
+    const uint32_t lut_s = smem_u32(smem + 1024);
+    const uint32_t lut_grp_bytes = (uint32_t)(2 * tp.S) * 16u;
+    const uint32_t off_cs = (uint32_t)g.off_cs, msk_cs = (uint32_t)g.msk_cs;   // (a sample's planes hold < 2^31 elements)
+    // ---- position of a k-stage: tile and stage in the tile (its units are 2 s and 2 s + 1)
     struct Pos {
       uint32_t item;
-      int s, hcA, tapA;
+      int s;
     };
     uint32_t tiles_done = 0;   // tiles the position `nxt` has left behind
     auto locate = [&](Pos &p) {
@@ -627,29 +674,23 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         p.item += gridDim.x;
         ++tiles_done;
       }
-      p.hcA = 0; p.tapA = 2 * p.s;
-      while (p.tapA >= T) { p.tapA -= T; ++p.hcA; }
     };
     auto advance = [&](Pos &p) {   // to the group's next stage
       p.s += kGroups2;
-      if (p.s < tp.S) {
-        p.tapA += 2 * kGroups2;
-        while (p.tapA >= T) { p.tapA -= T; ++p.hcA; }
-      } else {
-        locate(p);
-      }
+      locate(p);
     };
     // ---- the tile of position `nxt`, decoded when it changes: what the entry of this lane's
     // (row, unit) needs, and what the gather of that tile needs later
     uint32_t t_item = 0xffffffffu;
-    int t_grp = 0, t_wy0 = 0, t_wx0 = 0;
+    uint32_t t_lut = lut_s;                 // the tile's conv group in the unit table
+    int t_wy0 = 0, t_wx0 = 0;
     const char *t_sbase = nullptr;          // the tile's sample in the padded copy
     const TIO *t_off = nullptr, *t_msk = nullptr;   // the sample's offsets / masks at this lane's pixel
     float t_hb = -1.0e9f, t_wb = 0.f;       // this lane's row: sampling position without tap and offset
     auto enter_tile = [&](uint32_t item) {
       t_item = item;
       const TileId2 t = decode_item2(item, g, tp);
-      t_grp = t.grp;
+      t_lut = lut_s + (uint32_t)t.grp * lut_grp_bytes;
       t_wy0 = win_y0(g, tp, t.ho0); t_wx0 = win_x0(g, tp, t.wo0);
       t_sbase = xpad + (unsigned long long)t.n * ((unsigned long long)(g.H + 2) * Rb);
       const int ho = t.ho0 + (brow >> tp.tw_log2), wo = t.wo0 + (brow & tw_mask);
@@ -665,24 +706,27 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     // consumed by entry_build one own stage later
     uint32_t roh = 0, row_ = 0, rmm = 0;   // raw offset (y, x) and mask elements
     float bh = -1.0e9f, bw_ = 0.f;          // sampling position without the offset
-    uint32_t e_cb = 0;                      // byte offset of the unit's first channel inside a pixel
+    uint32_t n_misc = 0;                    // the unit's table word 3 (half-chunk, exists, channel byte offset)
+    uint32_t n_hcA = 0, n_hcB = 0;          // half-chunks of the stage's first and last existing unit
     auto entry_loads = [&](const Pos &p) {
-      roh = 0; row_ = 0; rmm = 0; bh = -1.0e9f; bw_ = 0.f;
+      roh = 0; row_ = 0; rmm = 0; bh = -1.0e9f; bw_ = 0.f; n_misc = 0;
       if (p.item >= items) return;
       if (p.item != t_item) enter_tile(p.item);
-      int hc = p.hcA, tap = p.tapA;
-      if (usel) { if (++tap == T) { tap = 0; ++hc; } }
-      if (2 * p.s + usel >= tp.U) return;            // no such unit: a dead entry
-      bh = t_hb + lut_tap[2 * tap];
-      bw_ = t_wb + lut_tap[2 * tap + 1];
-      const int dgi = (int)lut_dg[t_grp * KH + hc];
-      e_cb = (uint32_t)(t_grp * g.Cg + hc * 32) * 2u;
+      const uint32_t ea = t_lut + (uint32_t)p.s * 32u;     // unit 2 s; unit 2 s + 1 follows
+      const uint4 e = lds128(ea + (uint32_t)usel * 16u);
+      const uint32_t mA = lds32(ea + 12u), mB = lds32(ea + 28u);
+      n_hcA = mA & 255u;
+      n_hcB = (mB & 256u) ? (mB & 255u) : n_hcA;
+      n_misc = e.w;
+      if (!(e.w & 256u)) return;            // no such unit: a dead entry
+      bh = t_hb + __uint_as_float(e.x);
+      bw_ = t_wb + __uint_as_float(e.y);
       if (off) {
-        const TIO *pp = t_off + (long long)((dgi * 2 * T + 2 * tap)) * g.off_cs;
+        const TIO *pp = t_off + (e.z & 0xffffu) * off_cs;
         roh = ldg_raw_stream(pp);
-        row_ = ldg_raw_stream(pp + g.off_cs);
+        row_ = ldg_raw_stream(pp + off_cs);
       }
-      if (msk) rmm = ldg_raw_stream(t_msk + (long long)(dgi * T + tap) * g.msk_cs);
+      if (msk) rmm = ldg_raw_stream(t_msk + (e.z >> 16) * msk_cs);
     };
     // the entry: weights (w00 w01 | w10 w11), offset of the top-left corner within the padded
     // sample, and within the shared-memory window (kNoWin: the neighbourhood is not inside it)
@@ -713,7 +757,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           } else {
             // outside the window (rare): the two lanes that gather this (row, unit) will read the
             // padded copy a stage from now; ask for its four 64-byte corner runs now
-            const char *b = t_sbase + e_cb + eog;
+            const char *b = t_sbase + (n_misc >> 9) + eog;
             prefetch_l1(b); prefetch_l1(b + 32); prefetch_l1(b + Cb); prefetch_l1(b + Cb + 32);
             prefetch_l1(b + Rb); prefetch_l1(b + Rb + 32); prefetch_l1(b + Rb + Cb); prefetch_l1(b + Rb + Cb + 32);
           }
@@ -727,39 +771,39 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = ((uint32_t)gi / (uint32_t)A) & 1u;
     uint32_t win_acq = 0, win_rel = 0;   // windows: next one to wait for, next one to hand back
     bool ok = true;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
+    Timer2 pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
     // the first stage's entry
     entry_loads(cur);
     entry_build();
-    // what the gather of the current tile needs (copied from the decoded tile when `cur` enters it)
+    // what the gather of the current stage needs: its tile (copied from the decoded tile when
+    // `cur` enters it) and its units' table words (loaded with the entry a stage earlier)
     uint32_t c_item = cur.item, c_win_base = tiles_done * (uint32_t)KH;
     const char *c_sbase = t_sbase;
-    int c_grp = t_grp;
+    uint32_t c_misc = n_misc, c_hcA = n_hcA, c_hcB = n_hcB;
+    const bool ragged = (g.Cg & 31) != 0;   // the last half-chunk of a group is partly beyond its channels
     Pos nxt = cur;
     if (cur.item < items) advance(nxt);
     entry_loads(nxt);
 
     while (cur.item < items && ok) {
       // ---- this lane's unit of the stage
-      int hc = cur.hcA;
-      if (usel && cur.tapA + 1 == T) ++hc;
-      const bool exists = 2 * cur.s + usel < tp.U;
-      const char *gbase = c_sbase + (unsigned long long)(c_grp * g.Cg + (exists ? hc : 0) * 32) * 2ull;
-      const uint32_t wbase = win_s + ((c_win_base + (uint32_t)hc) & 1u) * wbytes;
-      // vectors beyond the unit's channels (a group whose size is not a multiple of 32) are zero
-      const bool v1_dead = !exists || hc * 32 + 8 * (int)q1 >= g.Cg;
-      const bool v2_dead = !exists || hc * 32 + 8 * (int)q2 >= g.Cg;
+      const uint32_t hc = c_misc & 255u;
+      const char *gbase = c_sbase + (c_misc >> 9);
+      const uint32_t wbase = win_s + ((c_win_base + hc) & 1u) * wbytes;
+      // vectors beyond the unit's channels (a group whose size is not a multiple of 32) are zero;
+      // a unit that does not exist has a dead entry and needs nothing here
+      const bool v1_dead = ragged && (int)hc * 32 + 8 * (int)q1 >= g.Cg;
+      const bool v2_dead = ragged && (int)hc * 32 + 8 * (int)q2 >= g.Cg;
       // ---- the windows of both units of the stage (unit B's is the later one)
       if (kWin) {
-        const uint32_t hcB = (uint32_t)cur.hcA + ((cur.tapA + 1 == T && 2 * cur.s + 1 < tp.U) ? 1u : 0u);
-        while (ok && win_acq <= c_win_base + hcB) {
-          ok = mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13);
+        while (ok && win_acq <= c_win_base + c_hcB) {
+          ok = mbar_wait2(win_full + 8 * (win_acq & 1u), (win_acq >> 1) & 1u, 13, TC2_BO_GATHER);
           ++win_acq;
         }
       }
       pt.lap(2);
       if (!ok) break;
-      ok = mbar_wait2(empty_a + 8 * sa, pa ^ 1u, 8);
+      ok = mbar_wait2(empty_a + 8 * sa, pa ^ 1u, 8, TC2_BO_GATHER);
       pt.lap(3);
       if (!ok) break;
       const uint32_t stage_row = a_row + sa * (uint32_t)kTileBytes;
@@ -852,19 +896,19 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       sa += (uint32_t)kGroups2;
       while (sa >= (uint32_t)A) { sa -= (uint32_t)A; pa ^= 1u; }
       cur = nxt;
+      c_misc = n_misc; c_hcA = n_hcA; c_hcB = n_hcB;
       if (cur.item != c_item && cur.item < items) {
         // (`nxt` entered this tile a stage ago: the decoded tile is this one)
         c_item = cur.item;
         c_win_base = tiles_done * (uint32_t)KH;
         c_sbase = t_sbase;
-        c_grp = t_grp;
       }
       if (nxt.item < items) advance(nxt);
       if (!(abl & 4)) entry_loads(nxt);
       if (kWin) {
         // windows before the next stage's first unit go back to the loader (the loads from
         // them have returned: their values were consumed above)
-        const uint32_t win_keep = cur.item < items ? c_win_base + (uint32_t)cur.hcA : win_acq;
+        const uint32_t win_keep = cur.item < items ? c_win_base + c_hcA : win_acq;
         if (win_rel < win_keep) {
           if (lane == 0)
             for (uint32_t i = win_rel; i < win_keep; ++i) mbar_arrive(win_empty + 8 * (i & 1u));
