@@ -630,7 +630,8 @@ def main():
                     help='c4 only: run the stack inside mmcv_b200.frozen_weights() (weights cast '
                          'and re-laid-out once, as in serving)')
     ap.add_argument('--counters', action='store_true',
-                    help='also report the in-kernel phase counters of the first CTA')
+                    help='also report the in-kernel phase counters of the first CTA (needs a library built '
+                         'with DCN_B200_NVCC_FLAGS=-DDCN_B200_PHASE_COUNTERS)')
     ap.add_argument('--ablate', type=int, default=0,
                     help='timing experiments only (results are wrong): bit mask handed to '
                          'dcn_debug_configure; needs a library built with '

@@ -97,6 +97,20 @@ struct PhaseTimer {
   }
 };
 
+// The kernels use PhaseTimer only when built with -DDCN_B200_PHASE_COUNTERS (the timers cost
+// the gather / producer warps four registers and a dozen instructions per stage); otherwise
+// this stand-in, whose calls vanish.
+struct NoTimer {
+  __device__ __forceinline__ NoTimer(unsigned long long *, bool) {}
+  __device__ __forceinline__ void lap(int) {}
+  __device__ __forceinline__ void count(int) {}
+};
+#ifdef DCN_B200_PHASE_COUNTERS
+using StageTimer = PhaseTimer;
+#else
+using StageTimer = NoTimer;
+#endif
+
 __device__ __forceinline__ void prefetch_l2(const void *p) {
   asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }

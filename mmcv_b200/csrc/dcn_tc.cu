@@ -219,7 +219,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     const int row = warp * 32 + lane;
     const int ty = row >> tp.tw_log2, tx = row & tw_mask;
     const bool act_any = g.act == DCN_ACT_SIGMOID && g.act_hi > g.act_lo;
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
+    StageTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     long long li = 0;
     int staged_co0[2] = {-1, -1};
     for (long long item = blockIdx.x; item < items; item += gridDim.x, ++li) {
@@ -289,7 +289,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       uint32_t sa = 0, pa = 0, sb = 0, pb = 0;
       long long li = 0;
       bool ok = true;
-      PhaseTimer pt(a.counters, blockIdx.x == 0 && lane == 0);
+      StageTimer pt(a.counters, blockIdx.x == 0 && lane == 0);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x, ++li) {
         const int buf = (int)(li & 1);
         const uint32_t par = (uint32_t)((li >> 1) & 1);
@@ -346,7 +346,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
       const int per_mt = g.groups * tp.NT;
       uint32_t sb = 0, pb = 0;
       bool ok = true;
-      PhaseTimer pt(a.counters, blockIdx.x == 0);
+      StageTimer pt(a.counters, blockIdx.x == 0);
       for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const int rem = (int)(item % per_mt);
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
@@ -400,7 +400,7 @@ dcn_fwd_tc(const __grid_constant__ TcArgs a) {
     };
     uint32_t tcount = 0;  // global k-stage counter of this CTA (same in every producer)
     bool built = false;   // (per-group tables) this group has a table that may still be read
-    PhaseTimer pt(a.counters, blockIdx.x == 0 && ptid == 0);
+    StageTimer pt(a.counters, blockIdx.x == 0 && ptid == 0);
     for (long long item = blockIdx.x; item < items && ok; item += gridDim.x) {
       const TileId t = decode_item(item, g, tp);
       pt.lap(0);

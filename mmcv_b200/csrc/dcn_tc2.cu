@@ -102,18 +102,6 @@ __device__ __forceinline__ void prefetch_l1(const void *p) {
   asm volatile("prefetch.global.L1 [%0];" ::"l"(p));
 }
 
-// In-kernel phase timers are compiled in only with -DDCN_TC2_COUNTERS (they cost the gather warps
-// four registers and a dozen instructions per stage).
-#ifdef DCN_TC2_COUNTERS
-using Timer2 = PhaseTimer;
-#else
-struct Timer2 {
-  __device__ __forceinline__ Timer2(unsigned long long *, bool) {}
-  __device__ __forceinline__ void lap(int) {}
-  __device__ __forceinline__ void count(int) {}
-};
-#endif
-
 // 16-byte loads.  `tok` is passed through untouched; code that must come after a load's issue
 // takes `tok` as an input.
 __device__ __forceinline__ uint4 ld16_global(const void *p, uint32_t &tok) {
@@ -409,7 +397,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     const int row = warp * 32 + lane;
     const int ty = row >> tp.tw_log2, tx = row & tw_mask;
     const bool act_any = g.act == DCN_ACT_SIGMOID && g.act_hi > g.act_lo;
-    Timer2 pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
+    StageTimer pt(a.counters, blockIdx.x == 0 && threadIdx.x == 0);
     uint32_t li = 0;
     int staged_co0[2] = {-1, -1};
     uint32_t slab = 0;  // tensor-store staging buffer in use (two per warp)
@@ -532,7 +520,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
                            ((uint32_t)(kBM >> 4) << 24);
     uint32_t sa = 0, pa = 0, sb = 0, pb = 0, li = 0;
     bool ok = true;
-    Timer2 pt(a.counters, blockIdx.x == 0 && lane == 0);
+    StageTimer pt(a.counters, blockIdx.x == 0 && lane == 0);
     for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x, ++li) {
       const int buf = (int)(li & 1);
       const uint32_t par = (li >> 1) & 1u;
@@ -577,7 +565,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const uint32_t per_mt = (uint32_t)(g.groups * tp.NT);
       uint32_t sb = 0, pb = 0;
       bool ok = true;
-      Timer2 pt(a.counters, blockIdx.x == 0);
+      StageTimer pt(a.counters, blockIdx.x == 0);
       for (uint32_t item = blockIdx.x; item < items && ok; item += gridDim.x) {
         const uint32_t rem = item % per_mt;
         const uint8_t *src = a.wtiles + (size_t)rem * tp.S * b_stage_bytes;
@@ -771,7 +759,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
     uint32_t sa = (uint32_t)gi % (uint32_t)A, pa = ((uint32_t)gi / (uint32_t)A) & 1u;
     uint32_t win_acq = 0, win_rel = 0;   // windows: next one to wait for, next one to hand back
     bool ok = true;
-    Timer2 pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
+    StageTimer pt(a.counters, blockIdx.x == 0 && gw == 0 && lane == 0);
     // the first stage's entry
     entry_loads(cur);
     entry_build();
