@@ -620,25 +620,27 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
   } else {
     // ------------------------------ gather ------------------------------
     reg_inc<kRegsGather>();
-    // Group gi fills the k-stages gi, gi + 2, ... (counted over all tiles of this block).  A
-    // stage is two passes of 64 rows; in a pass a warp covers eight rows and a lane blends the
-    // 16 channels {q1, q2} x 8 of one (row, unit): lane = 4 * row + 2 * unit + p.
-    // Tap entries: the warp's 16 rows x 2 units of a stage are 32 (row, unit) pairs; lane
-    // 4 * row + 2 * unit + pass builds the entry of (row + 64 * pass, unit), which the two lanes
-    // 4 * row + 2 * unit + {0, 1} fetch by shuffle in pass `pass`.
+    // Group gi fills the k-stages gi, gi + 2, ... (counted over all tiles of this block).  In a
+    // stage a warp covers sixteen rows and a lane owns one (row, unit): lane = 2 * row + unit.
+    // It computes that pair's tap entry a stage ahead (from offset / mask elements loaded a stage
+    // before that) and then blends the unit's 32 channels, four 16-byte vectors, itself: no
+    // entry ever leaves its lane.
     const int gw = warp - kFirstGatherWarp;
     const int gi = gw / kWarpsPerGroup, gwl = gw % kWarpsPerGroup;
-    const int rr = lane >> 2;          // row within the warp's eight
-    const int usel = (lane >> 1) & 1;  // which of the stage's two units
-    const int row0 = gwl * 8 + rr;     // pass p: row0 + 64 p
-    const int brow = row0 + 64 * (lane & 1);   // the row whose entry this lane builds
-    // Odd rows take their second vector first: the rows of a quarter warp then read (and
-    // write) different bank quarters.
-    const uint32_t q1 = (uint32_t)(lane & 1) ^ (uint32_t)((rr & 1) << 1), q2 = q1 ^ 2u;
+    const int rr = lane >> 1;          // row within the warp's sixteen
+    const int usel = lane & 1;         // which of the stage's two units
+    const int row0 = gwl * 16 + rr;    // this lane's row of the tile
+    const int brow = row0;             // (the row whose entry this lane builds: its own)
+    // Vector order.  A lane walks the unit's four 16-byte vectors in the order q0 ^ k, k = 0..3,
+    // with q0 = sigma(row & 3), sigma = (0, 3, 1, 2).  Both r -> sigma(r) and r -> sigma(r) ^ r
+    // are permutations of 0..3, so among the four rows of a quarter warp the vectors read in one
+    // instruction differ (window reads: bank quarter = slot parity * 4 + vector) and so do the
+    // swizzled chunks written (chunk = (4 * unit + vector) ^ (row & 7)): no bank conflicts on
+    // either side.
+    const uint32_t q0 = (0x9cu >> (2 * (rr & 3))) & 3u;   // sigma packed two bits per entry: 0, 3, 1, 2
     // operand tile: 16-byte chunk (4 * unit + q) of row r lives at chunk index ^ (r & 7)
     const uint32_t a_row = smem_u32(L.a) + (uint32_t)row0 * 128u;
-    const uint32_t a_c1 = (((uint32_t)(4 * usel) + q1) ^ (uint32_t)(row0 & 7)) << 4;
-    const uint32_t a_c2 = (((uint32_t)(4 * usel) + q2) ^ (uint32_t)(row0 & 7)) << 4;
+    const uint32_t a_c0 = (((uint32_t)(4 * usel) + q0) ^ (uint32_t)(row0 & 7)) << 4;   // vector k: a_c0 ^ (k << 4)
     const char *xpad = reinterpret_cast<const char *>(a.xpad);
     const TIO *off = (const TIO *)a.offset;
     const TIO *msk = (const TIO *)a.mask;
@@ -780,8 +782,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       const uint32_t wbase = win_s + ((c_win_base + hc) & 1u) * wbytes;
       // vectors beyond the unit's channels (a group whose size is not a multiple of 32) are zero;
       // a unit that does not exist has a dead entry and needs nothing here
-      const bool v1_dead = ragged && (int)hc * 32 + 8 * (int)q1 >= g.Cg;
-      const bool v2_dead = ragged && (int)hc * 32 + 8 * (int)q2 >= g.Cg;
+      const int cg_left = ragged ? g.Cg - (int)hc * 32 : 32;   // channels of the unit inside the group
       // ---- the windows of both units of the stage (unit B's is the later one)
       if (kWin) {
         while (ok && win_acq <= c_win_base + c_hcB) {
@@ -800,37 +801,32 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
 #else
       constexpr int abl = 0;
 #endif
-#pragma unroll 1
-      for (int p = 0; p < 2; ++p) {
-        if (abl & 16) break;
-        // the entry of (row0 + 64 p, unit): built by lane (lane & ~1) | p
-        const int src = (lane & ~1) | p;
-        uint32_t w0 = __shfl_sync(0xffffffffu, ew0, src), w1 = __shfl_sync(0xffffffffu, ew1, src);
-        const uint32_t dst = stage_row + (uint32_t)(p * 64 * 128);
+      if (!(abl & 16)) {
+        const uint32_t dst = stage_row;
+        const uint32_t w0 = ew0, w1 = ew1;
         if constexpr (kWin) {
-          // Every lane reads its four corner vectors from the window; a lane whose neighbourhood
-          // lies outside it (rare; the builder asked for those lines a stage ago) reads the padded
-          // copy instead, and a dead sample reads the window's first pixel and stores zeros.
-          // The lanes of unit 0 start with the even 64-byte slot of their left/right pair and
-          // those of unit 1 with the odd one (the window's row pitch is an even number of slots,
-          // so the bottom corners repeat the parity): with the rows' vector order, the eight
-          // lanes of a quarter warp cover all 32 banks.
-          uint32_t ow = __shfl_sync(0xffffffffu, eow, src);
+          // The four corner vectors come from the window; a lane whose neighbourhood lies outside
+          // it (rare; it asked for those lines when it built the entry) reads the padded copy
+          // instead, and a dead sample reads the window's first pixel and stores zeros.  The lanes
+          // of unit 0 start with the even 64-byte slot of their left/right pair and those of unit
+          // 1 with the odd one (the window's row pitch is an even number of slots, so the bottom
+          // corners repeat the parity).
+          uint32_t ow = eow;
           bool miss = ow == kNoWin;
           if (abl & 256) miss = false;
           const bool dead = ow == kDeadWin;
-          uint32_t og = 0;
-          if (__any_sync(0xffffffffu, miss)) og = __shfl_sync(0xffffffffu, eog, src);
           if (ow >= kDeadWin) ow = 0;
           const bool sw = !miss && ((ow >> 6) & 1u) != (uint32_t)usel;
-          if (sw) { w0 = __byte_perm(w0, 0u, 0x1032); w1 = __byte_perm(w1, 0u, 0x1032); }
+          const uint32_t v0 = sw ? __byte_perm(w0, 0u, 0x1032) : w0;
+          const uint32_t v1 = sw ? __byte_perm(w1, 0u, 0x1032) : w1;
           const uint32_t sp = wbase + ow;
           const uint32_t s1 = sw ? sp + 64u : sp, s2 = sw ? sp : sp + 64u;
-          const char *gb = gbase + og;
-          const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
+          const char *gb = gbase + eog;
+          const uint4 wa0 = table_weights<MODE>(make_uint2(v0, v1));
 #pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const uint32_t q16 = 16u * (k ? q2 : q1);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t q = q0 ^ (uint32_t)k;
+            const uint32_t q16 = 16u * q;
             uint32_t tok = 0;
             uint4 X[4];
             if (abl & 2) {
@@ -849,17 +845,18 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
             if (abl & 8) r = X[0];
             else if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
             else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
-            if ((k ? v2_dead : v1_dead) || dead) r = make_uint4(0u, 0u, 0u, 0u);
-            if (!(abl & 128)) sts16(dst + (k ? a_c2 : a_c1), r);
+            if (dead || 8 * (int)q >= cg_left) r = make_uint4(0u, 0u, 0u, 0u);
+            if (!(abl & 128)) sts16(dst + (a_c0 ^ ((uint32_t)k << 4)), r);
           }
         } else {
           // no window: every lane reads the padded copy in global memory (a dead sample reads the
           // all-zero neighbourhood with zero weights)
-          const uint32_t og = __shfl_sync(0xffffffffu, eog, src);
+          const char *gb = gbase + eog;
           const uint4 wa0 = table_weights<MODE>(make_uint2(w0, w1));
 #pragma unroll
-          for (int k = 0; k < 2; ++k) {
-            const char *b = gbase + og + 16u * (k ? q2 : q1);
+          for (int k = 0; k < 4; ++k) {
+            const uint32_t q = q0 ^ (uint32_t)k;
+            const char *b = gb + 16u * q;
             uint32_t tok = 0;
             uint4 X[4];
             X[0] = ld16_global(b, tok); X[1] = ld16_global(b + Cb, tok);
@@ -869,8 +866,8 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
             uint4 r;
             if constexpr (MODE == kModeBf16) r = blend8_bf16(wa, X[0], X[1], X[2], X[3]);
             else r = blend8_f16(wa, X[0], X[1], X[2], X[3]);
-            if (k ? v2_dead : v1_dead) r = make_uint4(0u, 0u, 0u, 0u);
-            sts16(dst + (k ? a_c2 : a_c1), r);
+            if (8 * (int)q >= cg_left) r = make_uint4(0u, 0u, 0u, 0u);
+            sts16(dst + (a_c0 ^ ((uint32_t)k << 4)), r);
           }
         }
       }
