@@ -709,6 +709,9 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
       n_hcB = (mB & 256u) ? (mB & 255u) : n_hcA;
       n_misc = e.w;
       if (!(e.w & 256u)) return;            // no such unit: a dead entry
+#ifdef DCN_TC2_ABLATE
+      if (a.debug_flags & 4) return;        // (timing experiment: bookkeeping only, no element loads)
+#endif
       bh = t_hb + __uint_as_float(e.x);
       bw_ = t_wb + __uint_as_float(e.y);
       if (off) {
@@ -889,7 +892,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
         c_sbase = t_sbase;
       }
       if (nxt.item < items) advance(nxt);
-      if (!(abl & 4)) entry_loads(nxt);
+      entry_loads(nxt);
       if (kWin) {
         // windows before the next stage's first unit go back to the loader (the loads from
         // them have returned: their values were consumed above)
