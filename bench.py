@@ -778,6 +778,11 @@ def main():
                 dm = hmsk[i0:i1].to(dev, non_blocking=True) if hmsk is not None else None
                 ready = torch.cuda.Event()
                 ready.record(s_in)
+            # the chunk was allocated on s_in and is consumed on the compute stream: tell the
+            # allocator, so that the blocks are not handed out again before the kernels have read them
+            for t in (dx, doff, dm):
+                if t is not None:
+                    t.record_stream(stream)
             stream.wait_event(ready)
             if dm is not None:
                 y = modulated_deform_conv2d(dx, doff, dm, w, b, st, pd, dl, wl['g'], wl['dg'])
@@ -788,6 +793,7 @@ def main():
             with torch.cuda.stream(s_out):
                 s_out.wait_event(done)
                 hout[i0:i1].copy_(y, non_blocking=True)
+                y.record_stream(s_out)
             keep.append((dx, doff, dm, y))
         stream.wait_stream(s_in)
         stream.wait_stream(s_out)
