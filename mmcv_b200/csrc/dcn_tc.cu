@@ -779,9 +779,11 @@ dcn_stage_input_cl_16bit(const uint8_t *__restrict__ x, uint8_t *__restrict__ y,
     const uint4 d = *reinterpret_cast<const uint4 *>(&tile[p][(o ^ (p & 7)) << 2]);
     if (q0 + p < HW && c0 + o * 8 < C) {
       const long long q = q0 + p;
-      const int H = (int)(HW / W);
+      // (a sample has fewer than 2^31 pixels: 32-bit divisions)
+      const int qi = (int)q, H = (int)HW / W;
+      const int row = qi / W, col = qi - row * W;
       const long long dq = pad ? (long long)n * (H + 2 * pad) * (W + 2 * pad) +
-                                     (q / W + pad) * (W + 2 * pad) + (q % W + pad)
+                                     (long long)(row + pad) * (W + 2 * pad) + (col + pad)
                                : (long long)n * HW + q;
       *reinterpret_cast<uint4 *>(y + (dq * C + c0 + o * 8) * 2) = d;
     }
