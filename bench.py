@@ -616,7 +616,7 @@ def main():
     ap.add_argument('--steps', type=int, default=10)
     ap.add_argument('--warmup', type=int, default=3)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
-    ap.add_argument('--workload', default='c5', choices=sorted(WORKLOADS) + ['c4'])
+    ap.add_argument('--workload', default='c5', choices=sorted(WORKLOADS) + ['c4', 'msda'])
     ap.add_argument('--batch', type=int, default=0, help='override the total batch size')
     ap.add_argument('--e2e-steps', type=int, default=3)
     ap.add_argument('--no-cpu-baseline', action='store_true')
@@ -648,6 +648,20 @@ def main():
     if args.ablate:
         args.no_shard_check = args.no_per_config = args.no_cpu_baseline = True
     args.warmup = max(args.warmup, 3) if args.impl == 'ours' else args.warmup
+    if args.workload == 'msda':
+        # the sibling sampler alone (one GPU): the two rows the default run's table carries
+        if not torch.cuda.is_available():
+            raise SystemExit('bench.py needs a CUDA device: there is no CPU path')
+        dev = torch.device('cuda', int(os.environ.get('LOCAL_RANK', '0')))
+        torch.cuda.set_device(dev)
+        peaks = json.load(open(os.path.join(ROOT, 'MEASURED_PEAKS.json'))) if os.path.exists(
+            os.path.join(ROOT, 'MEASURED_PEAKS.json')) else {}
+        if int(os.environ.get('RANK', '0')) == 0:
+            rows = {dt: measure_msda(dev, dt, peaks) for dt in ('bf16', 'fp32')}
+            print(json.dumps(dict(metric='msda_forward_ms', value=rows['bf16']['ms_per_step'], unit='ms',
+                                  n_gpus=1, higher_is_better=False, dtype='bf16', data='synthetic',
+                                  config=dict(workload=rows['bf16']['workload']), rows=rows)), flush=True)
+        return
     if args.workload == 'c4':
         if args.impl == 'reference':
             raise SystemExit('the reference arm is quoted on the single-layer workloads')
