@@ -7,13 +7,14 @@
 // mmcv/ops/csrc/pytorch/modulated_deform_conv.cpp:108-137), with a different producer side:
 //
 //   * gather warps (16, in two groups that fill alternate k-stages): a warp covers 16 rows of
-//     a stage (two passes of eight), i.e. 32 (row, unit) pairs, and each of its lanes turns
-//     the offsets and mask of ONE of them into a tap entry -- four 16-bit corner weights with
-//     the modulation folded in, and the byte offset of the top-left corner -- one own stage
-//     ahead, from loads issued another stage earlier; the lanes that gather a pair fetch its
-//     entry by warp shuffle.  A lane fetches the four corners, blends them on packed 16-bit
-//     FMAs and writes the 128-byte-swizzled operand tile tcgen05.mma reads; it blends 16
-//     channels of one (row, unit).  No tap table exists in memory.  The input is a
+//     a stage, i.e. 32 (row, unit) pairs, and each of its lanes owns ONE of them: it turns the
+//     pair's offsets and mask into a tap entry -- four 16-bit corner weights with the
+//     modulation folded in, and the byte offset of the top-left corner -- one own stage ahead,
+//     from loads issued another stage earlier, and then fetches the four corners of the unit's
+//     four 16-byte vectors, blends them on packed 16-bit FMAs and writes the 128-byte-swizzled
+//     operand tile tcgen05.mma reads.  An entry never leaves its lane and no tap table exists
+//     in memory.  Everything else a unit needs comes from a small lookup table built once per
+//     block (tap displacement, offset / mask channel, half-chunk, channel byte offset).  The input is a
 //     channels-last copy with a one-pixel zero border around every sample: a corner outside
 //     the image reads zeros, a sample outside the sampling gate points at an all-zero
 //     neighbourhood with zero weights, so the loads carry no predicates and a corner inside
@@ -24,9 +25,11 @@
 //     margin) is brought into shared memory by one tensor-map copy (cp.async.bulk.tensor, zero
 //     fill outside the tensor) per half-chunk, double-buffered; entries whose 2x2 neighbourhood
 //     lies inside that window are read from shared memory (64 bytes per pixel; which of the
-//     left/right corners and which of its two 16-byte vectors a lane reads first depends on
-//     the slot's and the row's parity, so that the eight lanes of a quarter warp never meet in
-//     a bank), the others from global memory.
+//     left/right corners a lane reads first depends on the slot's parity and the order of its
+//     four vectors on the row number, so that the eight lanes of a quarter warp never meet in
+//     a bank, neither reading the window nor writing the swizzled operand rows), the others
+//     from the padded copy in global memory, whose lines the lane requested when it built the
+//     entry.
 //
 // MMA issue, weight loader (cp.async.bulk + mbarrier complete_tx) and the accumulator
 // double-buffering in tensor memory are as in dcn_fwd_tc.  Every mbarrier wait is bounded.
@@ -51,7 +54,7 @@ constexpr int kFirstGatherWarp = 8;
 constexpr int kGatherWarps = 16;
 constexpr int kThreads2 = (kFirstGatherWarp + kGatherWarps) * 32;  // 768: six warps per scheduler, 80 registers per thread
 constexpr int kGroups2 = 2;                              // gather groups; group i fills k-stages i, i + 2, ...
-constexpr int kWarpsPerGroup = kGatherWarps / kGroups2;  // 8 warps: 64 rows per pass, two passes per stage
+constexpr int kWarpsPerGroup = kGatherWarps / kGroups2;  // 8 warps x 16 rows: the 128 rows of a stage
 
 // Register budget per role (setmaxnreg works on warpgroups of four consecutive warps; the
 // block starts with 80 registers per thread): the two warpgroups that hold the epilogue and the
@@ -748,7 +751,7 @@ __global__ void __launch_bounds__(kThreads2, 1) dcn_fwd_tc2(const __grid_constan
           if (wy < (uint32_t)(tp.win_h - 1) && wx < (uint32_t)(tp.win_w - 1)) {
             eow = (wy * (uint32_t)tp.win_w + wx) * 64u;
           } else {
-            // outside the window (rare): the two lanes that gather this (row, unit) will read the
+            // outside the window (rare): this lane will read the
             // padded copy a stage from now; ask for its four 64-byte corner runs now
             const char *b = t_sbase + (n_misc >> 9) + eog;
             prefetch_l1(b); prefetch_l1(b + 32); prefetch_l1(b + Cb); prefetch_l1(b + Cb + 32);
