@@ -224,6 +224,11 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   if ((long long)g.groups * 2 * t.S * 16 > 3072 || t.KH > 255 || (long long)g.dg * g.T > 32767 ||
       g.C >= (1 << 22))
     return;
+  // A 1x1 kernel makes every K unit a half-chunk of its own: a gather group would then pass whole
+  // input windows without touching them and hand several back at once, which the two-buffer
+  // window ring (one arrival per warp, window and phase) does not allow.  Such layers stay on
+  // the first-generation kernel.
+  if (g.T < 2) return;
   t.ndu = 1;
   t.tab_span = t.tab_slots = t.tab_slot_blocks = 0;
   // Epilogue through the tensor-copy engine: needs 16-byte multiples everywhere and tiles
