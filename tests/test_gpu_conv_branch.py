@@ -28,6 +28,13 @@ def _rand(shape, gen, scale=1.0, dtype=torch.bfloat16):
     (64, 64, 17, 19, 1, 1, 0, 1),      # 1x1, no padding
     (192, 32, 16, 16, 5, 1, 2, 1),     # 5x5
     (40, 27, 12, 12, 3, 1, 1, 1),      # channels not a multiple of 64: last chunk zero-filled
+    (64, 300, 9, 11, 3, 1, 1, 1),      # more output channels than one tile holds
+    (64, 1, 8, 8, 3, 1, 1, 1),         # a single output channel
+    (128, 27, 3, 3, 3, 1, 1, 1),       # an image smaller than a tile
+    (64, 27, 31, 5, 3, 3, 1, 1),       # stride 3, narrow image
+    (64, 54, 16, 16, 3, 1, 0, 1),      # no padding
+    (64, 27, 10, 10, 3, 1, 3, 1),      # padding beyond the copy's one-pixel border
+    (64, 27, 10, 10, 3, 2, 4, 3),      # stride, dilation and wide padding together
 ])
 @pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float16])
 def test_tensor_map_convolution_matches_fp32_convolution(C, Co, H, W, k, s, p, d, dtype):

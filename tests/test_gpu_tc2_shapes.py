@@ -33,6 +33,12 @@ CASES = {
     'far_and_nonfinite_offsets': (2, 64, 16, 16, 64, 3, 1, 1, 2, 6.0, 'far nonfinite'),
     'nonfinite_input': (1, 128, 13, 15, 32, 3, 1, 1, 4, 2.0, 'input_nonfinite int'),
     'wide_image_overhang': (1, 64, 9, 37, 24, 3, 1, 1, 1, 3.0, ''),
+    'dilation_2': (2, 64, 19, 23, 32, 3, 2, 1, 2, 2.0, 'dil2'),
+    'dilation_3_small_image': (1, 64, 7, 9, 16, 3, 3, 1, 2, 1.0, 'dil3'),
+    'tiny_image_many_samples': (37, 32, 3, 5, 8, 3, 1, 1, 1, 1.0, ''),
+    'tall_narrow': (2, 64, 70, 3, 16, 3, 1, 1, 2, 2.0, 'far'),
+    'no_padding_shrinks': (1, 64, 16, 18, 16, 3, 0, 1, 2, 1.5, ''),
+    'big_padding_grows': (1, 32, 8, 8, 16, 3, 3, 1, 1, 1.5, ''),
 }
 
 
@@ -41,7 +47,8 @@ def make(name):
     kh, kw = (k, k) if isinstance(k, int) else k
     ph, pw = (p, p) if isinstance(p, int) else p
     gen = torch.Generator().manual_seed(sum(map(ord, name)))
-    Ho, Wo = oracle.out_size(H, ph, 1, kh, 1), oracle.out_size(W, pw, 1, kw, 1)
+    dil = 2 if 'dil2' in special else (3 if 'dil3' in special else 1)
+    Ho, Wo = oracle.out_size(H, ph, dil, kh, 1), oracle.out_size(W, pw, dil, kw, 1)
     x = torch.randn(N, C, H, W, generator=gen)
     off = torch.randn(N, dg * 2 * kh * kw, Ho, Wo, generator=gen) * sigma
     if 'int' in special:
@@ -61,7 +68,7 @@ def make(name):
     w = torch.randn(Co, C // g, kh, kw, generator=gen) * (1.0 / (C // g * kh * kw)) ** 0.5
     b = torch.randn(Co, generator=gen) * 0.1
     t = dict(x=x, offset=off, mask=msk, weight=w, bias=b)
-    m = dict(stride=(1, 1), padding=(ph, pw), dilation=(1, 1), groups=g, deform_groups=dg)
+    m = dict(stride=(1, 1), padding=(ph, pw), dilation=(dil, dil), groups=g, deform_groups=dg)
     return m, t
 
 
@@ -70,7 +77,9 @@ def make(name):
 def test_table_free_kernel_corner_shapes(name, dtype):
     m, t = make(name)
     info = plan_path(t['x'], t['weight'], m, dtype)
-    assert info.path == _lib.PATH_TCGEN05 and info.kernel_version == 2, (info.path, info.kernel_version)
+    assert info.path == _lib.PATH_TCGEN05, info.path
+    if 'dil3' not in CASES[name][10]:   # (a window around a 3-dilated footprint does not fit: either kernel may take it)
+        assert info.kernel_version == 2, info.kernel_version
     r = rounded(t, dtype)
     ref = oracle.best_forward(r['x'], r['offset'], r['mask'], r['weight'], r['bias'], m['stride'],
                               m['padding'], m['dilation'], m['groups'], m['deform_groups'])
