@@ -196,3 +196,34 @@ def test_layer_of_this_package_matches_the_checker():
         loc = refp[:, :, None, :, None, :2] + off / 3 * refp[:, :, None, :, None, 2:] * 0.5
         ref = layer.output_proj(msda_forward(value, shapes, loc, aw)) + q
     assert torch.allclose(gpu.detach().cpu(), ref, rtol=1e-4, atol=1e-5)
+
+
+@pytest.mark.parametrize('dtype', [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize('D', [48, 24, 16])
+def test_head_widths_that_take_the_other_reduction_paths(D, dtype):
+    """16-byte vectors with a number of lanes per head that is not a power of two (D = 48: 12 fp32
+    or 6 bf16 lanes, atomic adds for the location / weight gradients), and small heads."""
+    from mmcv_b200.ops import MultiScaleDeformableAttnFunction
+    gen = torch.Generator().manual_seed(D)
+    B, M, Q, P = 2, 3, 41, 2
+    shapes = torch.tensor([[9, 7], [4, 5], [2, 2]])
+    S = int(shapes.prod(1).sum())
+    value = torch.rand(B, S, M, D, generator=gen).to(dtype)
+    loc = (torch.rand(B, Q, M, 3, P, 2, generator=gen) * 1.3 - 0.15).to(dtype)
+    attn = torch.rand(B, Q, M, 3 * P, generator=gen).softmax(-1).view(B, Q, M, 3, P).to(dtype)
+    gout = torch.randn(B, Q, M * D, generator=gen).to(dtype)
+    v = value.cuda().requires_grad_(True)
+    l = loc.cuda().requires_grad_(True)
+    a = attn.cuda().requires_grad_(True)
+    out = MultiScaleDeformableAttnFunction.apply(v, shapes.cuda(), starts_of(shapes).cuda(), l, a, 64)
+    out.backward(gout.cuda())
+    v64 = value.double().requires_grad_(True)
+    l64 = loc.double().requires_grad_(True)
+    a64 = attn.double().requires_grad_(True)
+    ref = msda_forward(v64, shapes, l64, a64)
+    ref.backward(gout.double())
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert rel_l2(out, ref.detach().float()) <= tol
+    assert rel_l2(v.grad, v64.grad.float()) <= tol
+    assert rel_l2(a.grad, a64.grad.float()) <= tol
+    assert rel_l2(l.grad, l64.grad.float()) <= 2 * tol
