@@ -489,12 +489,14 @@ def run_c4(args, rank, world, local, dist_ready=False, emit=True):
             per_layer_ms=per_kind, parity=parity, parity_ok=all(v['ok'] for v in parity.values()),
             roofline=dict(bound='tensor', achieved=fl_r / (ms * 1e-3) / 1e12, peak=peak_tf,
                           unit='TFLOP/s', frac=fl_r / (ms * 1e-3) / 1e12 / peak_tf, traffic=None,
-                          kernel='dcn_fwd_tc_bf16 (whole stack incl. layout copies, the offset-branch convolutions and weight tiling)'),
+                          kernel='dcn_fwd_tc / dcn_fwd_tc2 / dcn_conv_tma (whole stack incl. the zero-bordered copies and weight tiling)'),
             e2e=dict(value=fl / (e2e_ms * 1e-3) / 1e12, unit='TFLOP/s',
                      h2d_bytes_per_step=sum(h.numel() * 2 for h in hin),
                      d2h_bytes_per_step=hout.numel() * 2, ms_per_step=e2e_ms,
                      api='mmcv_b200.ops.ModulatedDeformConv2dPack'),
-            gpu_launches=args.steps * 13 * (3 if args.frozen_weights else 4), clocks=clocks)
+            # per layer: zero-bordered copy (border + interior), branch convolution (status clear,
+            # weight tiling, dcn_conv_tma), deformable kernel (status clear, weight tiling, main)
+            gpu_launches=args.steps * 13 * (6 if args.frozen_weights else 8), clocks=clocks)
         if emit:
             print(json.dumps(line), flush=True)
     else:

@@ -475,7 +475,9 @@ int make_plan(const DcnFwdParams *p, int sms, Plan *pl) {
     return fail(DCN_ERR_ARG, "padded_input must be %zu bytes and 256-byte aligned (got %lld)",
                 padded_copy_bytes(pl->g), (long long)p->padded_input_bytes);
   pl->have_image = pl->tc && p->weight_image != nullptr;
-  pl->launches = pl->tc ? (2 + (pl->have_image ? 0 : 1) + (pl->stage ? 1 : 0)) : 2;
+  // status clear + main kernel, + weight tiling, + input staging (two launches when the copy
+  // carries the zero border: border, interior)
+  pl->launches = pl->tc ? (2 + (pl->have_image ? 0 : 1) + (pl->stage ? (pl->tp.version == 2 ? 2 : 1) : 0)) : 2;
   return DCN_OK;
 }
 
