@@ -255,6 +255,7 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
   const bool auto_win = g.stride_h == 1 && g.stride_w == 1;
   const int m_max = kn.window < 0 ? (auto_win ? 6 : 0) : kn.window;
   bool found = false;
+  const int epi_wanted = t.epi_tma;
   for (int m = m_max; m >= 0 && !found; --m) {
     t.win_h = m ? fh + 2 * m : 0;
     t.win_w = m ? (fw + 2 * m + 1) / 2 * 2 : 0;
@@ -266,10 +267,15 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     for (int bi = (m || kn.small_l1) ? 1 : 0; bi < 2 && !found; ++bi)
       for (int as = 4; as >= 2 && !found; --as) {
         if (kn.a_stages && as != kn.a_stages) continue;
-        t.a_stages = as;
-        t.b_stages = kn.b_stages ? kn.b_stages : 2;
-        t.smem = tc2_smem_bytes(t);
-        found = t.smem <= budgets[bi];
+        // A deeper operand ring is worth more than tensor stores in the epilogue (c5: a fourth
+        // stage -5.5 %, the store kind +-0): give up the stores' staging memory before a stage.
+        for (int epi = epi_wanted; epi >= (kn.epi_tma == 1 ? 1 : 0) && !found; --epi) {
+          t.epi_tma = epi;
+          t.a_stages = as;
+          t.b_stages = kn.b_stages ? kn.b_stages : 2;
+          t.smem = tc2_smem_bytes(t);
+          found = t.smem <= budgets[bi];
+        }
       }
   }
   if (!found) return;
