@@ -62,6 +62,7 @@ struct Knobs {
   int window;      // -1: planner's choice, 0: no shared-memory input window, n: margin n
   int epi_tma;     // -1: planner's choice, 0/1
   int small_l1;    // 1: give the kernel the largest shared-memory configuration
+  int a2_max;      // deepest operand ring the table-free kernel may take
 };
 const Knobs &knobs() {
   static Knobs k;
@@ -77,6 +78,7 @@ const Knobs &knobs() {
     k.window = env_int("DCN_B200_WINDOW", -1, -1, 16);
     k.epi_tma = env_int("DCN_B200_EPI_TMA", -1, -1, 1);
     k.small_l1 = env_int("DCN_B200_SMALL_L1", 0, 0, 1);
+    k.a2_max = env_int("DCN_B200_A2_MAX", 6, 2, 8);
   });
   return k;
 }
@@ -265,8 +267,8 @@ void plan_tc2(const DcnFwdParams *p, const Geom &g, TcPlan *tp) {
     // configuration if possible
     const size_t budgets[2] = {167936 - 1024, kMaxSmemOptin};
     for (int bi = (m || kn.small_l1) ? 1 : 0; bi < 2 && !found; ++bi)
-      for (int as = 4; as >= 2 && !found; --as) {
-        if (kn.a_stages && as != kn.a_stages) continue;
+      for (int as = kn.a2_max; as >= 2 && !found; --as) {
+        if (kn.a_stages && as != kn.a_stages && !(kn.a_stages >= 4 && as > 4)) continue;
         // A deeper operand ring is worth more than tensor stores in the epilogue (c5: a fourth
         // stage -5.5 %, the store kind +-0): give up the stores' staging memory before a stage.
         for (int epi = epi_wanted; epi >= (kn.epi_tma == 1 ? 1 : 0) && !found; --epi) {
